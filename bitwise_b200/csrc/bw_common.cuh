@@ -1,0 +1,63 @@
+// Shared declarations of the kernel libraries: error reporting, the exported-symbol macro,
+// and the arithmetic that must give the same bits on the host and on the device.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define BW_API extern "C" __attribute__((visibility("default")))
+
+// Every exported function returns 0 on success. A non-zero value is either a CUDA error
+// code (> 0) or an argument error (< 0); bw_last_error() gives the text of the latter.
+namespace bw {
+
+void set_error(const char* fmt, ...);
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_error("CUDA launch failed: %s", cudaGetErrorString(e));
+  return static_cast<int>(e);
+}
+
+// exp(x) written only with IEEE multiply, add and fused multiply-add, each rounded to
+// nearest, so that the same sequence on a CPU gives the same bits. The reference calls
+// libm's expf (src/kernels.cpp:296,326; src/engine.cpp:56); libm is not reproducible
+// across machines, this is. Range reduction x = n*ln2 + r with a two-part ln2, a degree-5
+// polynomial for (exp(r) - 1 - r) / r^2 (Cephes expf coefficients), scaling by 2^n through
+// the exponent field. Inputs below -87 give 0, above 88 give +inf. Constants are given as
+// bit patterns so that no decimal parsing can differ between compilers.
+__device__ __forceinline__ float det_expf(float x) {
+  if (x < -87.0f) return 0.0f;
+  if (x > 88.0f) return __int_as_float(0x7f800000);
+  const float t = __fmul_rn(x, __int_as_float(0x3fb8aa3b));           // x * log2(e)
+  const float magic = __int_as_float(0x4b400000);                     // 1.5 * 2^23
+  const float n = __fsub_rn(__fadd_rn(t, magic), magic);              // round to nearest even
+  float r = __fmaf_rn(n, __int_as_float(0xbf318000), x);              // - n * 0.693359375
+  r = __fmaf_rn(n, __int_as_float(0x395e8083), r);                    // + n * 2.12194440e-4
+  float p = __int_as_float(0x39506967);
+  p = __fmaf_rn(p, r, __int_as_float(0x3ab743ce));
+  p = __fmaf_rn(p, r, __int_as_float(0x3c088908));
+  p = __fmaf_rn(p, r, __int_as_float(0x3d2aa9c1));
+  p = __fmaf_rn(p, r, __int_as_float(0x3e2aaaaa));
+  p = __fmaf_rn(p, r, __int_as_float(0x3f000000));
+  const float z = __fmul_rn(r, r);
+  float y = __fmaf_rn(p, z, r);
+  y = __fadd_rn(y, 1.0f);
+  const int ni = static_cast<int>(n);
+  return __fmul_rn(y, __int_as_float((ni + 127) << 23));
+}
+
+// The reference's in-vector reduction tree (src/kernels.cpp:57-64): after 16 lane-wise
+// chains, s8[i] = l[i] + l[i+8], s4[i] = s8[i] + s8[i+4], then (s4[0]+s4[2]) + (s4[1]+s4[3]).
+// Written for one thread that holds all 16 lanes.
+__device__ __forceinline__ float tree16(const float* l) {
+  float s8[8], s4[4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s8[i] = __fadd_rn(l[i], l[i + 8]);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s4[i] = __fadd_rn(s8[i], s8[i + 4]);
+  return __fadd_rn(__fadd_rn(s4[0], s4[2]), __fadd_rn(s4[1], s4[3]));
+}
+
+}  // namespace bw

@@ -1,0 +1,189 @@
+// Kernels that both precisions share: embedding gather into the 32-bit residual stream,
+// sampling from 32-bit logits, and the logits fingerprint.
+#include <cstdarg>
+#include <cstdio>
+
+#include "bw_common.cuh"
+
+namespace bw {
+static thread_local char g_error[512] = "";
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+}  // namespace bw
+
+BW_API const char* bw_last_error() { return bw::g_error; }
+
+// ---------------------------------------------------------------------------------------
+// Embedding: x[r][:] = E[token_r][:], widened to float (src/model.cpp:233-239,274).
+
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                  float* __restrict__ out, int n, int width) {
+  const int r = blockIdx.x;
+  const T* src = table + static_cast<size_t>(tokens[r]) * width;
+  float* dst = out + static_cast<size_t>(r) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = static_cast<float>(src[i]);
+}
+
+BW_API int bw_embed_rows(const void* table, int table_is_bf16, const int* tokens, float* out, int n,
+                         int width, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_is_bf16)
+    embed_rows_kernel<<<n, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(table), tokens, out, n, width);
+  else
+    embed_rows_kernel<<<n, threads, 0, stream>>>(static_cast<const float*>(table), tokens, out, n, width);
+  return bw::launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// Sampling. One block per logits row.
+//   temperature <= 0: the first index of the maximum (src/engine.cpp:40-45).
+//   otherwise: w_i = exp((l_i - max) / T) in 32-bit, total and running sums in 64-bit in
+//   vocabulary order, the first i with cum > u * total, skipping w_i <= 0, else the last
+//   positive one (src/engine.cpp:50-80).  The 64-bit sums are formed per contiguous
+//   segment of the vocabulary (one per thread) and chained over the segments in order; the
+//   reference adds strictly one by one, which differs from this by 64-bit rounding only.
+constexpr int kSampleThreads = 512;
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+                   const double* __restrict__ uniform, int* __restrict__ out_token) {
+  const int row = blockIdx.x;
+  const float* l = logits + static_cast<size_t>(row) * vocab;
+  const int tid = threadIdx.x;
+  __shared__ float s_val[kSampleThreads];
+  __shared__ int s_idx[kSampleThreads];
+  __shared__ double s_sum[kSampleThreads];
+  __shared__ double s_total;
+  __shared__ int s_pick;
+  __shared__ int s_last;
+
+  // maximum and its first index
+  float best = -INFINITY;
+  int best_i = -1;
+  for (int i = tid; i < vocab; i += kSampleThreads) {
+    const float v = l[i];
+    if (best_i < 0 || v > best) {  // indices come in increasing order: ">" keeps the first maximum
+      best = v;
+      best_i = i;
+    }
+  }
+  s_val[tid] = best;
+  s_idx[tid] = best_i;
+  __syncthreads();
+  for (int s = kSampleThreads / 2; s > 0; s >>= 1) {
+    if (tid < s) {
+      const float ov = s_val[tid + s];
+      const int oi = s_idx[tid + s];
+      const int mi = s_idx[tid];
+      if (oi >= 0 && (mi < 0 || ov > s_val[tid] || (ov == s_val[tid] && oi < mi))) {
+        s_val[tid] = ov;
+        s_idx[tid] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  const float mx = s_val[0];
+  const int arg = s_idx[0];
+  __syncthreads();  // s_idx is reused below
+  const float temp = temperature[row];
+  if (!(temp > 0.0f)) {
+    if (tid == 0) out_token[row] = arg;
+    return;
+  }
+
+  // contiguous segment of this thread
+  const int seg = (vocab + kSampleThreads - 1) / kSampleThreads;
+  const int lo = min(vocab, tid * seg), hi = min(vocab, lo + seg);
+  double local = 0.0;
+  int last_pos = -1;
+  for (int i = lo; i < hi; ++i) {
+    const float w = bw::det_expf(__fdiv_rn(__fsub_rn(l[i], mx), temp));
+    if (w > 0.0f) last_pos = i;
+    local += static_cast<double>(w);
+  }
+  s_sum[tid] = local;
+  s_idx[tid] = last_pos;
+  if (tid == 0) s_pick = 0x7fffffff;
+  __syncthreads();
+  if (tid == 0) {  // exclusive prefix over segments, in order
+    double run = 0.0;
+    int lastp = 0;
+    for (int t = 0; t < kSampleThreads; ++t) {
+      const double v = s_sum[t];
+      s_sum[t] = run;
+      run += v;
+      if (s_idx[t] >= 0) lastp = s_idx[t];
+    }
+    s_last = lastp;
+    s_total = run;
+  }
+  __syncthreads();
+  const double total = s_total;
+  const double target = uniform[row] * total;
+  double cum = s_sum[tid];
+  for (int i = lo; i < hi; ++i) {
+    const float w = bw::det_expf(__fdiv_rn(__fsub_rn(l[i], mx), temp));
+    if (w <= 0.0f) continue;
+    cum += static_cast<double>(w);
+    if (cum > target) {
+      atomicMin(&s_pick, i);
+      break;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) out_token[row] = (s_pick != 0x7fffffff) ? s_pick : s_last;
+}
+
+BW_API int bw_sample_rows(const float* logits, int rows, int vocab, const float* temperature,
+                          const double* uniform, int* out_token, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) {
+    bw::set_error("sample_rows: vocabulary size %d", vocab);
+    return -1;
+  }
+  sample_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, temperature, uniform, out_token);
+  return bw::launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// Logits fingerprint: the reference chains an FNV-style hash over the raw bits of every
+// sampled-from logits row (src/engine.cpp:18-29): for each 8-byte word h = (h ^ w) * prime,
+// trailing bytes one by one, then the splitmix64 finaliser.  The chain is serial by
+// definition; one thread per row walks it.  state[slot[r]] holds the running hash.
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__global__ void fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab,
+                                        const int* __restrict__ slot, unsigned long long* __restrict__ state) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(logits + static_cast<size_t>(r) * vocab);
+  uint64_t h = state[slot[r]];
+  const uint64_t prime = 1099511628211ull;
+  int i = 0;
+  for (; i + 2 <= vocab; i += 2) {
+    const uint64_t word = static_cast<uint64_t>(w[i]) | (static_cast<uint64_t>(w[i + 1]) << 32);
+    h = (h ^ word) * prime;
+  }
+  if (i < vocab) {
+    const uint32_t v = w[i];
+    for (int b = 0; b < 4; ++b) h = (h ^ ((v >> (8 * b)) & 0xffu)) * prime;
+  }
+  state[slot[r]] = mix64(h);
+}
+
+BW_API int bw_fingerprint_rows(const float* logits, int rows, int vocab, const int* slot,
+                               unsigned long long* state, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  fingerprint_rows_kernel<<<(rows + 31) / 32, 32, 0, stream>>>(logits, rows, vocab, slot, state);
+  return bw::launch_status();
+}

@@ -1,0 +1,223 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+In the manner of the reference's ``Runner::forward`` (src/model.cpp:267-322) and of the
+row building in its engine (src/engine.cpp:386-402): a batch is a flat list of rows, each
+a token at a position of some request; portions of prompts stand beside single decoded
+tokens, cut anywhere.  Keys and values of every row are stored in the cache before
+attention runs, and attention reads the cache only, so the logits at a position do not
+depend on how the tokens were cut into steps or on what else is in the batch.  Only the
+tokens given are run; logits come back for the wanted rows only.
+
+The host side of a step is one packed int32 buffer (tokens, positions, the row -> sequence
+map, per-sequence arrays, the block tables of every cache group, query tiles) copied to
+the device in one transfer from pinned memory; every kernel of the step reads its
+indices from there, which also keeps the step replayable as a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import FREED, CacheError, CacheManager
+from ..cache.storage import CacheStorage
+from ..parts.base import StepContext, Workspace
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepError(RuntimeError):
+    pass
+
+
+class OutOfPages(StepError):
+    pass
+
+
+def query_tile_rows(model) -> List[int]:
+    """The distinct query-tile heights that the model's mixers ask for."""
+    sizes = set()
+    for b in model.blocks:
+        fn = getattr(b.mixer, "query_tile_rows", None)
+        if fn is not None:
+            sizes.add(int(fn()))
+    return sorted(sizes) or [16]
+
+
+class _Layout:
+    """Offsets (in int32 elements) of the sections of the packed step buffer."""
+
+    def __init__(self, max_rows: int, max_seqs: int, max_blocks: Sequence[int], tile_rows: Sequence[int]):
+        self.max_rows, self.max_seqs = max_rows, max_seqs
+        self.max_blocks = list(max_blocks)
+        self.tile_rows = list(tile_rows)
+        off = 0
+
+        def take(n):
+            nonlocal off
+            start = off
+            off += (n + 3) // 4 * 4  # keep every section 16-byte aligned
+            return start
+
+        self.tokens = take(max_rows)
+        self.pos = take(max_rows)
+        self.row_seq = take(max_rows)
+        self.seq_row0 = take(max_seqs + 1)
+        self.seq_pos0 = take(max_seqs)
+        self.seq_slot = take(max_seqs)
+        self.logit_rows = take(max_rows)
+        self.tiles = {}
+        for tr in self.tile_rows:
+            cap = max_rows // tr + max_seqs + 1
+            self.tiles[tr] = (take(cap), take(cap), take(cap), cap)
+        self.tables = [take(max_seqs * mb) for mb in self.max_blocks]
+        self.total = off
+
+
+class Stepper:
+    """Owns the step's device buffers and runs steps for one model and one cache."""
+
+    def __init__(self, model, manager: CacheManager, storage: CacheStorage, ops, max_rows: int,
+                 max_seqs: int, max_tokens_per_request: int):
+        self.model, self.manager, self.storage, self.ops = model, manager, storage, ops
+        self.device = model.device
+        self.max_rows, self.max_seqs = max_rows, max_seqs
+        page = manager.page_size
+        mb = (max_tokens_per_request + page - 1) // page
+        self.layout = _Layout(max_rows, max_seqs, [mb] * len(manager.groups), query_tile_rows(model))
+        pin = self.device is not None and torch.device(self.device).type == "cuda"
+        self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=pin)
+        self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
+        self.workspace = Workspace(self.device, max_rows)
+        self.vocab = model.head.vocab
+        model.reserve_positions(mb * page)
+        self.steps = 0
+        self.h2d_bytes = 0
+        self._copy_done = torch.cuda.Event() if pin else None
+        self._copy_pending = False
+
+    # -- building the batch ------------------------------------------------------------
+    def _section(self, t: torch.Tensor, start: int, n: int) -> torch.Tensor:
+        return t[start:start + n]
+
+    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+        """Allocate pages, fill the packed buffer, copy it, and return the step's context
+        together with (request, new length) for the bookkeeping after the run."""
+        L, mgr = self.layout, self.manager
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if self._copy_pending:  # the pinned buffer is rewritten only after its last copy is done
+            self._copy_done.synchronize()
+            self._copy_pending = False
+        if len(entries) > self.max_seqs:
+            raise StepError(f"{len(entries)} requests in one step; the stepper was built for {self.max_seqs}")
+        seen = set()
+        n = 0
+        h = self.host.numpy()
+        seq_rows: List[Tuple[int, int]] = []
+        seq_pos0: List[int] = []
+        seq_slot: List[int] = []
+        after: List[Tuple[Hashable, int]] = []
+        logit_rows: List[int] = []
+        max_keys = 0
+        for s, e in enumerate(entries):
+            if e.rid in seen:
+                raise StepError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            cnt = len(e.tokens)
+            if cnt == 0:
+                raise StepError(f"request {e.rid!r} brings no tokens")
+            if n + cnt > self.max_rows:
+                raise StepError(f"step of more than {self.max_rows} rows")
+            if not mgr.has(e.rid):
+                mgr.begin(e.rid)
+            rc = mgr.get(e.rid)
+            start = rc.length
+            for g, mbg in enumerate(L.max_blocks):
+                if (start + cnt + mgr.page_size - 1) // mgr.page_size > mbg:
+                    raise StepError(f"request {e.rid!r} would hold {start + cnt} tokens; the block table "
+                                    f"covers {mbg * mgr.page_size}")
+            if not mgr.ensure(e.rid, start + cnt):
+                raise OutOfPages(f"no free page for request {e.rid!r} ({start} + {cnt} tokens)")
+            toks = list(e.tokens)
+            for t in toks:
+                if not (0 <= t < self.vocab):
+                    raise StepError(f"token id {t} outside the vocabulary of {self.vocab}")
+            h[L.tokens + n:L.tokens + n + cnt] = toks
+            h[L.pos + n:L.pos + n + cnt] = range(start, start + cnt)
+            h[L.row_seq + n:L.row_seq + n + cnt] = s
+            h[L.seq_row0 + s] = n
+            h[L.seq_pos0 + s] = start
+            h[L.seq_slot + s] = rc.slot
+            for w in e.want:
+                if not (0 <= w < cnt):
+                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its {cnt} tokens")
+                logit_rows.append(n + w)
+            for g, table in enumerate(rc.tables):
+                base = L.tables[g] + s * L.max_blocks[g]
+                h[base:base + len(table)] = [p if p != FREED else 0 for p in table]
+            seq_rows.append((n, cnt))
+            seq_pos0.append(start)
+            seq_slot.append(rc.slot)
+            after.append((e.rid, start + cnt))
+            max_keys = max(max_keys, start + cnt)
+            n += cnt
+        num_seqs = len(entries)
+        h[L.seq_row0 + num_seqs] = n
+        c = len(logit_rows)
+        h[L.logit_rows:L.logit_rows + c] = logit_rows
+        tiles = {}
+        for tr, (o_seq, o_row0, o_rows, cap) in L.tiles.items():
+            t = 0
+            for s, (r0, cnt) in enumerate(seq_rows):
+                for a in range(0, cnt, tr):
+                    h[o_seq + t] = s
+                    h[o_row0 + t] = r0 + a
+                    h[o_rows + t] = min(tr, cnt - a)
+                    t += 1
+            tiles[tr] = t
+        self.dev.copy_(self.host, non_blocking=True)
+        if self._copy_done is not None:
+            self._copy_done.record()
+            self._copy_pending = True
+        self.h2d_bytes = self.host.numel() * 4
+        d = self.dev
+        first_tr = L.tile_rows[0]
+        ctx = StepContext(
+            ops=self.ops, workspace=self.workspace, n=n, num_seqs=num_seqs,
+            tokens=d[L.tokens:L.tokens + n], pos=d[L.pos:L.pos + n], row_seq=d[L.row_seq:L.row_seq + n],
+            seq_row0=d[L.seq_row0:L.seq_row0 + num_seqs + 1], seq_pos0=d[L.seq_pos0:L.seq_pos0 + num_seqs],
+            seq_slot=d[L.seq_slot:L.seq_slot + num_seqs], logit_rows=d[L.logit_rows:L.logit_rows + c],
+            num_logit_rows=c, max_keys=max_keys,
+            host_seq_rows=seq_rows, host_seq_pos0=seq_pos0, host_seq_slot=seq_slot)
+        ctx.tile_sets = {tr: (d[o[0]:o[0] + tiles[tr]], d[o[1]:o[1] + tiles[tr]], d[o[2]:o[2] + tiles[tr]],
+                              tiles[tr]) for tr, o in L.tiles.items()}
+        ctx.tile_seq, ctx.tile_row0, ctx.tile_rows, ctx.num_tiles = ctx.tile_sets[first_tr]
+        ctx.block_tables = [d[L.tables[g]:L.tables[g] + num_seqs * L.max_blocks[g]].view(num_seqs, L.max_blocks[g])
+                            for g in range(len(L.max_blocks))]
+        return ctx, after
+
+    # -- running -----------------------------------------------------------------------
+    def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one step; returns float32 logits [wanted, vocab] on the device (a view of
+        the stepper's buffer, valid until the next step) or None when nothing is wanted."""
+        ctx, after = self.prepare(entries)
+        views = self.storage.views(ctx.block_tables, ctx.seq_slot)
+        logits = self.model.forward(ctx, views)
+        for rid, length in after:
+            self.manager.advance(rid, length)
+        self.steps += 1
+        self.last_context = ctx
+        return logits
+
+    def finish(self, rid: Hashable) -> None:
+        """The request is over: everything it holds goes back."""
+        if self.manager.has(rid):
+            self.manager.release(rid)

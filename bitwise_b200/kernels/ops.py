@@ -1,0 +1,227 @@
+"""The kernel library as the parts see it: one object per precision, bound with ctypes.
+
+``KernelOps("float32")`` loads the exact 32-bit kernels, ``KernelOps("bfloat16")`` the
+serving kernels; both offer the same operations on torch tensors.  There is no CPU
+implementation behind these names: if the CUDA library cannot be compiled or loaded the
+constructor raises, and every call checks that its tensors live on a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_ptr = ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _need(t: torch.Tensor, dtype, what: str, dims: Optional[int] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}; the kernels run on a CUDA device only")
+    if t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: tensor is not contiguous")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{what}: expected {dims} dimensions, got {tuple(t.shape)}")
+
+
+class KernelOps:
+    """Operations of one precision.  ``act_dtype`` is the dtype of activations between
+    kernels (the residual stream, logits and norm weights are float32 in both)."""
+
+    def __init__(self, dtype: str, verbose_build: bool = True):
+        if dtype not in ("float32", "bfloat16"):
+            raise KernelError(f"unknown dtype {dtype!r} (float32 or bfloat16)")
+        self.dtype = dtype
+        self.act_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+        self.kind = "f32" if dtype == "float32" else "bf16"
+        path = build.ensure_built(self.kind, (), verbose_build)
+        try:
+            self.lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from None
+        self.library_path = path
+        self.lib.bw_last_error.restype = ctypes.c_char_p
+        self.launches = 0  # kernels launched through this object (counted per call)
+        self._attn_libs = {}
+
+    # -- plumbing ----------------------------------------------------------------------
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _check(self, rc: int, name: str) -> None:
+        if rc != 0:
+            msg = self.lib.bw_last_error().decode("utf-8", "replace")
+            raise KernelError(f"{name} failed ({rc}): {msg}")
+
+    def _call(self, name: str, *args, lib=None, launches: int = 1) -> None:
+        fn = getattr(lib or self.lib, name)
+        fn.restype = _c_int
+        self._check(fn(*args), name)
+        self.launches += launches
+
+    # -- shared kernels ----------------------------------------------------------------
+    def embed_rows(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+        """out[r] = table[tokens[r]] widened to float32."""
+        n, width = out.shape
+        _need(tokens, torch.int32, "embed_rows tokens")
+        _need(out, torch.float32, "embed_rows out", 2)
+        if table.dtype not in (torch.float32, torch.bfloat16) or table.shape[1] != width:
+            raise KernelError("embed_rows: table must be float32 or bfloat16 of the output's width")
+        _need(table, table.dtype, "embed_rows table", 2)
+        self._call("bw_embed_rows", _p(table), _c_int(int(table.dtype == torch.bfloat16)), _p(tokens), _p(out),
+                   _c_int(n), _c_int(width), self._stream())
+
+    def sample_rows(self, logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+                    out_tokens: torch.Tensor) -> None:
+        rows, vocab = logits.shape
+        _need(logits, torch.float32, "sample_rows logits", 2)
+        _need(temperature, torch.float32, "sample_rows temperature")
+        _need(uniform, torch.float64, "sample_rows uniform")
+        _need(out_tokens, torch.int32, "sample_rows out")
+        self._call("bw_sample_rows", _p(logits), _c_int(rows), _c_int(vocab), _p(temperature), _p(uniform),
+                   _p(out_tokens), self._stream())
+
+    def fingerprint_rows(self, logits: torch.Tensor, slot: torch.Tensor, state: torch.Tensor) -> None:
+        """state[slot[r]] = chained hash of logits row r's raw bits (one row per slot per call)."""
+        rows, vocab = logits.shape
+        _need(logits, torch.float32, "fingerprint_rows logits", 2)
+        _need(slot, torch.int32, "fingerprint_rows slot")
+        _need(state, torch.int64, "fingerprint_rows state")
+        self._call("bw_fingerprint_rows", _p(logits), _c_int(rows), _c_int(vocab), _p(slot), _p(state),
+                   self._stream())
+
+    # -- per-precision kernels ---------------------------------------------------------
+    def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+        """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x and weight float32, out act_dtype."""
+        n, width = out.shape
+        _need(x, torch.float32, "rmsnorm x", 2)
+        _need(weight, torch.float32, "rmsnorm weight", 1)
+        _need(out, self.act_dtype, "rmsnorm out", 2)
+        if x.shape[1] != width or weight.shape[0] != width:
+            raise KernelError("rmsnorm: widths differ")
+        if rows is not None:
+            _need(rows, torch.int32, "rmsnorm rows")
+        self._call(f"bw_{self.kind}_rmsnorm", _p(x), _p(weight), _p(out), _p(rows), _c_int(n), _c_int(width),
+                   _c_float(eps), self._stream())
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+               residual: Optional[torch.Tensor] = None) -> None:
+        """out = x @ w.T (+ residual).  x [M,K] and w [N,K] in act_dtype; out act_dtype or
+        float32; with a float32 residual the sum is formed in 32-bit (out float32, may alias)."""
+        m, k = x.shape
+        n = w.shape[0]
+        _need(x, self.act_dtype, "linear x", 2)
+        _need(w, self.act_dtype, "linear w", 2)
+        if w.shape[1] != k or tuple(out.shape) != (m, n):
+            raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+        if residual is not None:
+            _need(residual, torch.float32, "linear residual", 2)
+            _need(out, torch.float32, "linear out", 2)
+            if tuple(residual.shape) != (m, n):
+                raise KernelError("linear: residual shape differs from the output's")
+        if self.kind == "f32":
+            _need(out, torch.float32, "linear out", 2)
+            self._call("bw_f32_linear", _p(x), _p(w), _p(out), _p(residual), _c_int(m), _c_int(n), _c_int(k),
+                       self._stream())
+        else:
+            if out.dtype not in (torch.float32, torch.bfloat16):
+                raise KernelError("linear: out must be float32 or bfloat16")
+            _need(out, out.dtype, "linear out", 2)
+            self._call("bw_bf16_linear", _p(x), _p(w), _p(out), _c_int(int(out.dtype == torch.float32)),
+                       _p(residual), _c_int(m), _c_int(n), _c_int(k), self._stream())
+
+    def rope_cache(self, qkv: torch.Tensor, pos: torch.Tensor, row_seq: torch.Tensor,
+                   cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], block_table: torch.Tensor,
+                   kcache: torch.Tensor, vcache: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                   write_kv: bool = True) -> None:
+        """Rotate q (in place) and k by the table rows of ``pos``; store k and v in the pages
+        ``block_table[row_seq[r]][pos[r] // page]``.  kcache / vcache: [pages, kv_heads, page, hd]."""
+        n = qkv.shape[0]
+        _need(qkv, self.act_dtype, "rope_cache qkv", 2)
+        _need(pos, torch.int32, "rope_cache pos")
+        _need(row_seq, torch.int32, "rope_cache row_seq")
+        _need(block_table, torch.int32, "rope_cache block_table", 2)
+        _need(kcache, self.act_dtype, "rope_cache kcache", 4)
+        _need(vcache, self.act_dtype, "rope_cache vcache", 4)
+        if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+            raise KernelError("rope_cache: row width is not (heads + 2 kv_heads) * head_dim")
+        if tuple(kcache.shape[1:]) != (kv_heads, kcache.shape[2], head_dim) or kcache.shape != vcache.shape:
+            raise KernelError("rope_cache: cache shape is not [pages, kv_heads, page, head_dim]")
+        if cos is not None:
+            _need(cos, torch.float32, "rope_cache cos", 2)
+            _need(sin, torch.float32, "rope_cache sin", 2)
+            if cos.shape[1] != head_dim // 2 or cos.shape != sin.shape:
+                raise KernelError("rope_cache: table width is not head_dim / 2")
+        self._call(f"bw_{self.kind}_rope_cache", _p(qkv), _c_int(qkv.shape[1]), _p(pos), _p(row_seq), _p(cos),
+                   _p(sin), _p(block_table), _c_int(block_table.shape[1]), _p(kcache), _p(vcache), _c_int(n),
+                   _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(kcache.shape[2]),
+                   _c_int(int(write_kv)), self._stream())
+
+    def attention(self, qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                  block_table: torch.Tensor, row_seq: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
+                  heads: int, kv_heads: int, head_dim: int, window: int, max_keys: int, scale: float,
+                  batch=None) -> None:
+        """out[r, h] = softmax(q k^T * scale) v over the cached keys lo..pos[r] of row r's
+        sequence (lo = max(0, pos - window + 1) when window > 0).  q is read from the first
+        heads*head_dim columns of qkv.  ``batch`` carries the step's per-sequence arrays for
+        kernels that tile queries by sequence."""
+        n = qkv.shape[0]
+        _need(qkv, self.act_dtype, "attention qkv", 2)
+        _need(out, self.act_dtype, "attention out", 2)
+        _need(kcache, self.act_dtype, "attention kcache", 4)
+        _need(vcache, self.act_dtype, "attention vcache", 4)
+        _need(block_table, torch.int32, "attention block_table", 2)
+        _need(row_seq, torch.int32, "attention row_seq")
+        _need(pos, torch.int32, "attention pos")
+        if out.shape[1] != heads * head_dim or out.shape[0] != n:
+            raise KernelError("attention: output shape is not [rows, heads * head_dim]")
+        page = kcache.shape[2]
+        if self.kind == "f32":
+            self._call("bw_f32_attention", _p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
+                       _c_int(block_table.shape[1]), _p(row_seq), _p(pos), _p(out), _c_int(out.shape[1]), _c_int(n),
+                       _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window),
+                       _c_int(max_keys), _c_float(scale), self._stream())
+        else:
+            if batch is None:
+                raise KernelError("attention (bfloat16): the step's sequence arrays are required")
+            self._call("bw_bf16_attention", _p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
+                       _c_int(block_table.shape[1]), _p(batch.tile_seq), _p(batch.tile_row0), _p(batch.tile_rows),
+                       _c_int(batch.num_tiles), _p(batch.seq_pos0), _p(batch.seq_row0), _p(out),
+                       _c_int(out.shape[1]), _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+                       _c_int(page), _c_int(window), _c_float(scale), self._stream())
+
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        """out = silu(gate) * up for rows laid out [gate | up]."""
+        n, inter = out.shape
+        _need(gate_up, self.act_dtype, "swiglu gate_up", 2)
+        _need(out, self.act_dtype, "swiglu out", 2)
+        if gate_up.shape[1] != 2 * inter or gate_up.shape[0] != n:
+            raise KernelError("swiglu: input is not [rows, 2 * intermediate]")
+        self._call(f"bw_{self.kind}_swiglu", _p(gate_up), _p(out), _c_int(n), _c_int(inter), self._stream())
+
+
+_OPS = {}
+
+
+def get_ops(dtype: str) -> KernelOps:
+    """The shared KernelOps of a precision (libraries are loaded once per process)."""
+    if dtype not in _OPS:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine has no CPU path")
+        _OPS[dtype] = KernelOps(dtype)
+    return _OPS[dtype]
