@@ -133,9 +133,10 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
   const int half = hd >> 1;
   const int p = pos[r];
   float* row = qkv + static_cast<size_t>(r) * row_stride;
-  const float* c = cos_t + static_cast<size_t>(p) * half;
-  const float* s = sin_t + static_cast<size_t>(p) * half;
-  const int q_items = heads * half;
+  const bool rotate = cos_t != nullptr;  // a null table leaves q and k as they are
+  const float* c = rotate ? cos_t + static_cast<size_t>(p) * half : nullptr;
+  const float* s = rotate ? sin_t + static_cast<size_t>(p) * half : nullptr;
+  const int q_items = rotate ? heads * half : 0;
   for (int it = threadIdx.x; it < q_items; it += blockDim.x) {
     const int h = it / half, i = it - h * half;
     float* v = row + h * hd;
@@ -153,8 +154,8 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
     const int h = it / half, i = it - h * half;
     const size_t dst = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd;
     const float x1 = k[h * hd + i], x2 = k[h * hd + i + half];
-    kcache[dst + i] = __fsub_rn(__fmul_rn(x1, c[i]), __fmul_rn(x2, s[i]));
-    kcache[dst + i + half] = __fadd_rn(__fmul_rn(x2, c[i]), __fmul_rn(x1, s[i]));
+    kcache[dst + i] = rotate ? __fsub_rn(__fmul_rn(x1, c[i]), __fmul_rn(x2, s[i])) : x1;
+    kcache[dst + i + half] = rotate ? __fadd_rn(__fmul_rn(x2, c[i]), __fmul_rn(x1, s[i])) : x2;
     vcache[dst + i] = vv[h * hd + i];
     vcache[dst + i + half] = vv[h * hd + i + half];
   }

@@ -28,8 +28,13 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # kernel set -> list of (source file, extra flags)
 KERNEL_SETS: Dict[str, List[tuple]] = {
     "f32": [("common.cu", []), ("exact_f32.cu", ["-fmad=false"])],
-    "bf16": [("common.cu", []), ("bf16_ops.cu", []), ("bf16_gemm.cu", []), ("bf16_attention.cu", [])],
+    "bf16": [("common.cu", []), ("bf16_ops.cu", []), ("bf16_gemm.cu", [])],
+    # compiled once per head size, with -DBW_HEAD_DIM=<n>
+    "bf16_attn": [("common.cu", []), ("bf16_attention.cu", [])],
 }
+
+# head sizes whose attention library a full build prepares (others are compiled when a model asks)
+DEFAULT_HEAD_DIMS = (16, 32, 64, 128)
 
 
 class BuildError(RuntimeError):
@@ -153,4 +158,6 @@ def ensure_built(kind: str, defines: Sequence[str] = (), verbose: bool = True) -
 
 def build_all(verbose: bool = True) -> List[str]:
     """Compile every kernel set (what a 'does it build' check wants)."""
-    return [ensure_built(k, (), verbose) for k in KERNEL_SETS]
+    out = [ensure_built(k, (), verbose) for k in ("f32", "bf16")]
+    out += [ensure_built("bf16_attn", (f"BW_HEAD_DIM={hd}",), verbose) for hd in DEFAULT_HEAD_DIMS]
+    return out

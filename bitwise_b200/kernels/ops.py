@@ -57,6 +57,12 @@ class KernelOps:
         self.lib.bw_last_error.restype = ctypes.c_char_p
         self.launches = 0  # kernels launched through this object (counted per call)
         self._attn_libs = {}
+        self._verbose_build = verbose_build
+        self._partials: Optional[torch.Tensor] = None  # scratch of the split products (bfloat16 path)
+        self._counters: Optional[torch.Tensor] = None
+        if self.kind == "bf16":
+            self.lib.bw_bf16_linear_scratch_floats.restype = ctypes.c_longlong
+            self._split_rows = int(self.lib.bw_bf16_linear_split_rows())
 
     # -- plumbing ----------------------------------------------------------------------
     def _stream(self):
@@ -142,8 +148,42 @@ class KernelOps:
             if out.dtype not in (torch.float32, torch.bfloat16):
                 raise KernelError("linear: out must be float32 or bfloat16")
             _need(out, out.dtype, "linear out", 2)
+            partials = counters = None
+            if m <= self._split_rows:
+                partials, counters = self._linear_scratch(x.device, n, k)
             self._call("bw_bf16_linear", _p(x), _p(w), _p(out), _c_int(int(out.dtype == torch.float32)),
-                       _p(residual), _c_int(m), _c_int(n), _c_int(k), self._stream())
+                       _p(residual), _c_int(m), _c_int(n), _c_int(k), _p(partials), _p(counters), self._stream())
+
+    def _linear_scratch(self, device, n: int, k: int):
+        """Scratch of a product that is split along k: chunk sums for up to ``_split_rows``
+        rows, and one counter per output tile (zero between launches).  It grows when a
+        larger product appears and is otherwise reused by every product of the stream."""
+        floats = int(self.lib.bw_bf16_linear_scratch_floats(_c_int(self._split_rows), _c_int(n), _c_int(k)))
+        tiles = int(self.lib.bw_bf16_linear_counters(_c_int(n)))
+        if self._partials is None or self._partials.numel() < floats:
+            self._partials = torch.empty(floats, dtype=torch.float32, device=device)
+        if self._counters is None or self._counters.numel() < tiles:
+            self._counters = torch.zeros(max(tiles, 1024), dtype=torch.int32, device=device)
+        return self._partials, self._counters
+
+    def attention_tile_rows(self, heads: int, kv_heads: int) -> int:
+        """Query rows per attention tile: the bfloat16 kernel stacks the heads of a group
+        with the rows, 64 stacked rows per thread block."""
+        if self.kind == "f32":
+            return 16
+        return max(1, 64 // max(1, heads // kv_heads))
+
+    def _attention_lib(self, head_dim: int):
+        lib = self._attn_libs.get(head_dim)
+        if lib is None:
+            path = build.ensure_built("bf16_attn", (f"BW_HEAD_DIM={head_dim}",), self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the attention library {path}: {e}") from None
+            lib.bw_last_error.restype = ctypes.c_char_p
+            self._attn_libs[head_dim] = lib
+        return lib
 
     def rope_cache(self, qkv: torch.Tensor, pos: torch.Tensor, row_seq: torch.Tensor,
                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], block_table: torch.Tensor,
@@ -199,11 +239,21 @@ class KernelOps:
         else:
             if batch is None:
                 raise KernelError("attention (bfloat16): the step's sequence arrays are required")
-            self._call("bw_bf16_attention", _p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
-                       _c_int(block_table.shape[1]), _p(batch.tile_seq), _p(batch.tile_row0), _p(batch.tile_rows),
-                       _c_int(batch.num_tiles), _p(batch.seq_pos0), _p(batch.seq_row0), _p(out),
-                       _c_int(out.shape[1]), _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-                       _c_int(page), _c_int(window), _c_float(scale), self._stream())
+            if head_dim % 16 or not (16 <= head_dim <= 256):
+                raise KernelError(f"attention (bfloat16): head size {head_dim} is not a multiple of 16 up to 256")
+            lib = self._attention_lib(head_dim)
+            t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.attention_tile_rows(heads, kv_heads))
+            fn = lib.bw_bf16_attention
+            fn.restype = _c_int
+            rc = fn(_p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
+                    _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
+                    _p(batch.seq_pos0), _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(n), _c_int(heads),
+                    _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale),
+                    self._stream())
+            if rc != 0:
+                raise KernelError(f"bw_bf16_attention failed ({rc}): "
+                                  + lib.bw_last_error().decode("utf-8", "replace"))
+            self.launches += 1
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         """out = silu(gate) * up for rows laid out [gate | up]."""

@@ -39,6 +39,12 @@ class GQAAttention(Mixer):
     def cache_need(self):
         return PagedKVNeed(self.kv_heads, self.head_dim, self.window)
 
+    def query_tile_rows(self, ops=None) -> int:
+        """Height of the query tiles this mixer's attention kernel wants (rows of one
+        sequence per thread block); the stepper prepares tiles of every height asked for."""
+        group = self.heads // self.kv_heads
+        return max(1, 64 // group)
+
     def param_specs(self, prefix: str) -> List[ParamSpec]:
         q, k, v, o = self.names
         return [ParamSpec(f"{prefix}.{q}.weight", (self.q_dim, self.width), MATRIX),

@@ -1,0 +1,395 @@
+"""Each CUDA kernel alone against the plain implementation, at sizes other than the engine's.
+
+float32 kernels must equal the plain implementation (reproducible exp) bit for bit.
+bfloat16 kernels are compared with the plain float32 result of the same bfloat16 inputs,
+within the tolerances stated beside each test.
+"""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops(dtype):
+    from bitwise_b200.kernels.ops import get_ops
+    return get_ops(dtype)
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def assert_same_bits(got, want, what):
+    got = np.asarray(got, dtype=np.float32)
+    want = np.asarray(want, dtype=np.float32)
+    bad = _bits(got) != _bits(want)
+    assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.size} values differ in bits; max abs diff "
+                           f"{np.abs(got - want).max():.3e}; first at {np.argwhere(bad)[0].tolist()}")
+
+
+def t(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV).to(dtype)
+
+
+def rnd(rng, *shape, scale=1.0):
+    return (rng.standard_normal(shape) * scale).astype(np.float32)
+
+
+# ----------------------------------------------------------------------------------------
+# float32: bit equality
+
+@pytest.mark.parametrize("n,width", [(1, 16), (5, 100), (9, 257), (3, 2048)])
+def test_f32_rmsnorm(n, width):
+    rng = np.random.default_rng(width)
+    x, w = rnd(rng, n, width), (1 + 0.1 * rnd(rng, width)).astype(np.float32)
+    out = torch.empty(n, width, device=DEV)
+    _ops("float32").rmsnorm(t(x), t(w), 1e-5, out)
+    assert_same_bits(out.cpu().numpy(), P.rmsnorm(x, w, 1e-5), "rmsnorm")
+    rows = np.array([n - 1, 0], dtype=np.int32)
+    out2 = torch.empty(2, width, device=DEV)
+    _ops("float32").rmsnorm(t(x), t(w), 1e-6, out2, rows=torch.from_numpy(rows).to(DEV))
+    assert_same_bits(out2.cpu().numpy(), P.rmsnorm(x[rows], w, 1e-6), "rmsnorm with gathered rows")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (1, 100, 33), (7, 15, 16), (17, 64, 172), (70, 130, 96), (16, 65, 600)])
+def test_f32_linear(m, n, k):
+    rng = np.random.default_rng(m * 1000 + n + k)
+    x, w = rnd(rng, m, k), rnd(rng, n, k, scale=0.1)
+    out = torch.empty(m, n, device=DEV)
+    _ops("float32").linear(t(x), t(w), out)
+    want = P.linear(x, w)
+    assert_same_bits(out.cpu().numpy(), want, "linear")
+    res = rnd(rng, m, n)
+    acc = t(res).clone()
+    _ops("float32").linear(t(x), t(w), acc, residual=acc)
+    assert_same_bits(acc.cpu().numpy(), (res + want).astype(np.float32), "linear with residual in place")
+
+
+def test_f32_linear_row_alone_equals_row_in_batch():
+    rng = np.random.default_rng(5)
+    x, w = rnd(rng, 50, 200), rnd(rng, 77, 200)
+    ops = _ops("float32")
+    full = torch.empty(50, 77, device=DEV)
+    ops.linear(t(x), t(w), full)
+    for r in (0, 13, 49):
+        one = torch.empty(1, 77, device=DEV)
+        ops.linear(t(x[r:r + 1]), t(w), one)
+        assert_same_bits(one.cpu().numpy(), full[r:r + 1].cpu().numpy(), f"row {r}")
+
+
+def test_f32_swiglu():
+    rng = np.random.default_rng(2)
+    gu = rnd(rng, 9, 2 * 172, scale=3.0)
+    gu[0, :4] = [-100.0, 100.0, 0.0, -87.5]
+    out = torch.empty(9, 172, device=DEV)
+    _ops("float32").swiglu(t(gu), out)
+    assert_same_bits(out.cpu().numpy(), P.swiglu(gu, 172, exp="det"), "swiglu")
+
+
+def _paged(rng, lens, kv_heads, hd, page, dtype=np.float32, spare=3):
+    """A scrambled paged cache for sequences of the given lengths: (k, v, table, per-seq k/v)."""
+    blocks = [(n + page - 1) // page for n in lens]
+    total = sum(blocks) + spare
+    perm = rng.permutation(total)
+    table = np.zeros((len(lens), max(blocks)), dtype=np.int32)
+    k = rnd(rng, total, kv_heads, page, hd)
+    v = rnd(rng, total, kv_heads, page, hd)
+    at = 0
+    seq_k, seq_v = [], []
+    for s, nb in enumerate(blocks):
+        table[s, :nb] = perm[at:at + nb]
+        at += nb
+        kk = np.concatenate([k[b] for b in table[s, :nb]], axis=1)[:, :lens[s]]  # [kvh, len, hd]
+        vv = np.concatenate([v[b] for b in table[s, :nb]], axis=1)[:, :lens[s]]
+        seq_k.append(np.transpose(kk, (1, 0, 2)))
+        seq_v.append(np.transpose(vv, (1, 0, 2)))
+    return k, v, table, seq_k, seq_v
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 8, 0), (5, 5, 48, 16, 0),
+                                                           (4, 2, 16, 16, 7), (6, 2, 64, 32, 40)])
+def test_f32_attention(heads, kv_heads, hd, page, window):
+    rng = np.random.default_rng(heads * 100 + hd + window)
+    lens = [37, 1, 70]
+    k, v, table, seq_k, seq_v = _paged(rng, lens, kv_heads, hd, page)
+    # rows: for every sequence a few query positions, batched together
+    rows = [(0, 36), (0, 5), (1, 0), (2, 69), (2, 68), (2, 16), (2, 15)]
+    q = rnd(rng, len(rows), heads, hd)
+    qkv = np.zeros((len(rows), (heads + 2 * kv_heads) * hd), dtype=np.float32)
+    qkv[:, :heads * hd] = q.reshape(len(rows), -1)
+    out = torch.empty(len(rows), heads * hd, device=DEV)
+    ops = _ops("float32")
+    ops.attention(t(qkv), t(k), t(v), torch.from_numpy(table).to(DEV),
+                  torch.tensor([r[0] for r in rows], dtype=torch.int32, device=DEV),
+                  torch.tensor([r[1] for r in rows], dtype=torch.int32, device=DEV), out, heads, kv_heads, hd,
+                  window, max(r[1] for r in rows) + 1, 1.0 / np.sqrt(np.float32(hd)).item())
+    got = out.cpu().numpy().reshape(len(rows), heads, hd)
+    for i, (s, p) in enumerate(rows):
+        # plain attention of the whole prefix with the query placed at position p
+        T = p + 1
+        qq = np.zeros((T, heads, hd), dtype=np.float32)
+        qq[p] = q[i]
+        want = P.attention(qq, seq_k[s][:T], seq_v[s][:T], exp="det", window=window)[p]
+        assert_same_bits(got[i], want, f"attention row {i} (seq {s}, pos {p})")
+
+
+def test_f32_rope_and_cache_write():
+    rng = np.random.default_rng(3)
+    heads, kv_heads, hd, page = 3, 1, 32, 8
+    from bitwise_b200.parts.rope import RotaryEncoding
+    rot = RotaryEncoding(hd, 500000.0, None, positions=64)
+    cos, sin = rot.rotary_tables(DEV)
+    pos = np.array([0, 1, 17, 63, 9], dtype=np.int32)
+    seq = np.array([0, 0, 1, 1, 2], dtype=np.int32)
+    table = np.array([[5, 0, 0, 0, 0, 0, 0, 0], [1, 2, 3, 4, 6, 7, 8, 9], [10, 11, 0, 0, 0, 0, 0, 0]], dtype=np.int32)
+    qkv = rnd(rng, 5, (heads + 2 * kv_heads) * hd)
+    k = torch.zeros(12, kv_heads, page, hd, device=DEV)
+    v = torch.zeros(12, kv_heads, page, hd, device=DEV)
+    buf = t(qkv).clone()
+    _ops("float32").rope_cache(buf, t(pos, torch.int32), t(seq, torch.int32), cos, sin, t(table, torch.int32), k, v,
+                               heads, kv_heads, hd)
+    inv = P.rope_inv_freq(hd, 500000.0)
+    want_q = P.rope(qkv[:, :heads * hd].reshape(5, heads, hd), pos, inv)
+    want_k = P.rope(qkv[:, heads * hd:(heads + kv_heads) * hd].reshape(5, kv_heads, hd), pos, inv)
+    assert_same_bits(buf.cpu().numpy()[:, :heads * hd].reshape(5, heads, hd), want_q, "rotated q")
+    kc, vc = k.cpu().numpy(), v.cpu().numpy()
+    for r in range(5):
+        blk, slot = table[seq[r], pos[r] // page], pos[r] % page
+        assert_same_bits(kc[blk, :, slot], want_k[r], f"cached k of row {r}")
+        assert_same_bits(vc[blk, :, slot], qkv[r, (heads + kv_heads) * hd:].reshape(kv_heads, hd), f"cached v of row {r}")
+    assert int((kc != 0).any(axis=(1, 3)).sum()) == 5, "keys were written to other slots too"
+
+
+def test_embed_rows_both_table_dtypes():
+    rng = np.random.default_rng(4)
+    table = rnd(rng, 50, 72)
+    toks = np.array([3, 49, 0, 3], dtype=np.int32)
+    out = torch.empty(4, 72, device=DEV)
+    _ops("float32").embed_rows(t(table), t(toks, torch.int32), out)
+    assert_same_bits(out.cpu().numpy(), table[toks], "embed float32")
+    tb = P.bf16_round(table)
+    _ops("float32").embed_rows(t(tb, torch.bfloat16), t(toks, torch.int32), out)
+    assert_same_bits(out.cpu().numpy(), tb[toks], "embed bfloat16 table")
+
+
+def test_sample_rows_greedy_and_temperature():
+    rng = np.random.default_rng(6)
+    vocab = 1003  # no power of two, not a multiple of the block size
+    logits = rnd(rng, 6, vocab, scale=2.0)
+    logits[0, 17] = logits[0, 900] = 50.0  # tie: the first maximum wins
+    temps = np.array([0.0, 0.8, 1.3, 0.0, 0.05, 2.0], dtype=np.float32)
+    us = np.array([0.3, 0.999999, 0.0, 0.5, 0.41, 0.73], dtype=np.float64)
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    _ops("float32").sample_rows(t(logits), t(temps), torch.from_numpy(us).to(DEV), out)
+    got = out.cpu().numpy()
+    for r in range(6):
+        want = P.argmax_row(logits[r]) if temps[r] <= 0 else P.sample_row(logits[r], temps[r], us[r], exp="det")
+        assert got[r] == want, f"row {r}: sampled {got[r]}, plain sampler says {want}"
+    assert got[0] == 17
+
+
+def test_fingerprint_rows():
+    rng = np.random.default_rng(7)
+    for vocab in (256, 385):
+        logits = rnd(rng, 3, vocab)
+        state = torch.full((5,), 0, dtype=torch.int64, device=DEV)
+        seed = 1469598103934665603
+        state[:] = seed
+        slot = torch.tensor([4, 0, 2], dtype=torch.int32, device=DEV)
+        ops = _ops("float32")
+        ops.fingerprint_rows(t(logits), slot, state)
+        ops.fingerprint_rows(t(logits[::-1].copy()), slot, state)
+        got = [int(x) & ((1 << 64) - 1) for x in state.cpu().numpy()]
+        for i, s in enumerate([4, 0, 2]):
+            want = P.fingerprint(P.fingerprint(seed, logits[i]), logits[::-1][i])
+            assert got[s] == want
+
+
+# ----------------------------------------------------------------------------------------
+# bfloat16
+
+def bf(a):
+    return P.bf16_round(np.asarray(a, dtype=np.float32))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (5, 100, 96), (64, 344, 64), (65, 130, 172), (200, 256, 1100),
+                                   (8, 2048, 2048), (33, 72, 520)])
+def test_bf16_linear(m, n, k):
+    """Tolerance: float32 accumulation of exact bfloat16 products; the result may differ from
+    the float64 sum by accumulation rounding only: 1e-4 of the largest output (float32 out),
+    plus one bfloat16 rounding (2^-8 relative) when the output is bfloat16."""
+    rng = np.random.default_rng(m + n + k)
+    x, w = bf(rnd(rng, m, k)), bf(rnd(rng, n, k, scale=0.1))
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    ops = _ops("bfloat16")
+    out32 = torch.empty(m, n, device=DEV)
+    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), out32)
+    assert np.abs(out32.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
+    out16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), out16)
+    got = out16.float().cpu().numpy()
+    assert (np.abs(got - want) <= 2.0 ** -8 * np.abs(want) + 1e-4 * np.abs(want).max()).all()
+    res = rnd(rng, m, n)
+    acc = t(res).clone()
+    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), acc, residual=acc)
+    assert np.abs(acc.cpu().numpy() - (res + want)).max() <= 1e-4 * np.abs(want).max() + 1e-6
+
+
+def test_bf16_linear_row_bits_do_not_depend_on_the_batch():
+    """The summation order is the same for every batch size: a row gives the same bits
+    alone, in a small batch (split along k) and in a large one (one block walks k)."""
+    rng = np.random.default_rng(8)
+    for n, k in ((96, 2048), (2048, 1536), (64, 200)):
+        x, w = bf(rnd(rng, 200, k)), bf(rnd(rng, n, k, scale=0.05))
+        ops = _ops("bfloat16")
+        full = torch.empty(200, n, device=DEV)
+        ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), full)
+        for rows in ((0, 1), (3, 11), (0, 64), (100, 165), (7, 136)):
+            part = torch.empty(rows[1] - rows[0], n, device=DEV)
+            ops.linear(t(x[rows[0]:rows[1]], torch.bfloat16), t(w, torch.bfloat16), part)
+            assert_same_bits(part.cpu().numpy(), full[rows[0]:rows[1]].cpu().numpy(), f"rows {rows} of [{n}x{k}]")
+
+
+def test_bf16_rmsnorm_and_swiglu():
+    """Tolerance: one bfloat16 rounding of a float32 result (2^-8 relative) plus 1e-6 absolute."""
+    rng = np.random.default_rng(9)
+    x, w = rnd(rng, 7, 960), (1 + 0.1 * rnd(rng, 960)).astype(np.float32)
+    out = torch.empty(7, 960, device=DEV, dtype=torch.bfloat16)
+    ops = _ops("bfloat16")
+    ops.rmsnorm(t(x), t(w), 1e-5, out)
+    want = P.rmsnorm(x, w, 1e-5)
+    assert (np.abs(out.float().cpu().numpy() - want) <= 2.0 ** -8 * np.abs(want) + 1e-6).all()
+    gu = bf(rnd(rng, 5, 2 * 172, scale=2.0))
+    h = torch.empty(5, 172, device=DEV, dtype=torch.bfloat16)
+    ops.swiglu(t(gu, torch.bfloat16), h)
+    want = P.swiglu(gu, 172, exp="det")
+    assert (np.abs(h.float().cpu().numpy() - want) <= 2.0 ** -8 * np.abs(want) + 1e-6).all()
+
+
+def _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window):
+    """rows_by_seq: list of (first position, count) per sequence; q: [rows, heads, hd] (bfloat16 values)."""
+    ops = _ops("bfloat16")
+    n = q.shape[0]
+    qkv = np.zeros((n, (heads + 2 * kv_heads) * hd), dtype=np.float32)
+    qkv[:, :heads * hd] = q.reshape(n, -1)
+
+    class Batch:
+        pass
+    b = Batch()
+    tr = ops.attention_tile_rows(heads, kv_heads)
+    seq_row0, seq_pos0, tiles, r = [], [], [], 0
+    pos, row_seq = [], []
+    for s, (p0, cnt) in enumerate(rows_by_seq):
+        seq_row0.append(r)
+        seq_pos0.append(p0)
+        for a in range(0, cnt, tr):
+            tiles.append((s, r + a, min(tr, cnt - a)))
+        pos += list(range(p0, p0 + cnt))
+        row_seq += [s] * cnt
+        r += cnt
+    seq_row0.append(r)
+    I = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    b.seq_row0, b.seq_pos0 = I(seq_row0), I(seq_pos0)
+    sets = (I([x[0] for x in tiles]), I([x[1] for x in tiles]), I([x[2] for x in tiles]), len(tiles))
+    b.query_tiles = lambda rows: sets
+    out = torch.empty(n, heads * hd, device=DEV, dtype=torch.bfloat16)
+    ops.attention(t(qkv, torch.bfloat16), t(k, torch.bfloat16), t(v, torch.bfloat16), I(table), I(row_seq), I(pos),
+                  out, heads, kv_heads, hd, window, max(pos) + 1, 1.0 / float(np.sqrt(hd)), batch=b)
+    return out.float().cpu().numpy().reshape(n, heads, hd), pos, row_seq
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 8, 0), (5, 5, 48, 16, 0),
+                                                           (8, 2, 64, 64, 0), (2, 2, 128, 32, 0), (6, 2, 64, 16, 50),
+                                                           (4, 4, 80, 16, 0)])
+def test_bf16_attention(heads, kv_heads, hd, page, window):
+    """Against plain attention of the same bfloat16 q, k, v with the softmax weights rounded
+    to bfloat16 before the value product.  Tolerance: the output is one bfloat16 rounding
+    (2^-8 relative) of a sum whose weights carry a bfloat16 rounding each relative to a
+    running instead of the final maximum: 2^-7 of the largest |v| of the sequence."""
+    rng = np.random.default_rng(heads * 100 + hd + window)
+    lens = [150, 1, 70, 200]
+    k, v, table, seq_k, seq_v = _paged(rng, lens, kv_heads, hd, page)
+    k, v = bf(k), bf(v)
+    seq_k, seq_v = [bf(a) for a in seq_k], [bf(a) for a in seq_v]
+    rows_by_seq = [(0, 150), (0, 1), (69, 1), (130, 70)]  # a whole prompt, a first token, a decode, a late portion
+    n = sum(c for _, c in rows_by_seq)
+    q = bf(rnd(rng, n, heads, hd))
+    got, pos, row_seq = _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window)
+    r = 0
+    for s, (p0, cnt) in enumerate(rows_by_seq):
+        T = p0 + cnt
+        qq = np.zeros((T, heads, hd), dtype=np.float32)
+        qq[p0:] = q[r:r + cnt]
+        want = P.attention(qq, seq_k[s][:T], seq_v[s][:T], exp="det", window=window, round_bf16=True)[p0:]
+        tol = 2.0 ** -7 * np.abs(seq_v[s]).max()
+        err = np.abs(got[r:r + cnt] - want).max()
+        assert err <= tol, f"sequence {s}: max error {err:.4f} > {tol:.4f}"
+        r += cnt
+
+
+def test_bf16_attention_finds_a_far_key_and_the_window_edge():
+    """One key among hundreds is made to stand out by scaling it along the query: the output
+    must be that key's value.  With a window that ends one position after it, it must vanish."""
+    rng = np.random.default_rng(11)
+    heads, kv_heads, hd, page = 2, 1, 64, 16
+    L = 500
+    k, v, table, seq_k, seq_v = _paged(rng, [L], kv_heads, hd, page)
+    k, v = bf(k * 0.1), bf(v)
+    q = bf(rnd(rng, 1, heads, hd))
+    far = 3  # the far key's position
+    blk, slot = table[0, far // page], far % page
+    k[blk, 0, slot] = bf(q[0, 0] * 4.0)  # score ~ 4 |q|^2 / 8 = about 32 above the rest
+    got, _, _ = _run_bf16_attention(q, [(L - 1, 1)], k, v, table, heads, kv_heads, hd, 0)
+    assert np.abs(got[0, 0] - v[blk, 0, slot]).max() < 2e-2, "head 0 should return the far key's value"
+    window = L - 1 - far  # keys far+1 .. L-1: the far key is just outside
+    got_w, _, _ = _run_bf16_attention(q, [(L - 1, 1)], k, v, table, heads, kv_heads, hd, window)
+    assert np.abs(got_w[0, 0] - v[blk, 0, slot]).max() > 0.3, "the far key must be outside the window"
+    got_in, _, _ = _run_bf16_attention(q, [(L - 1, 1)], k, v, table, heads, kv_heads, hd, window + 1)
+    assert np.abs(got_in[0, 0] - v[blk, 0, slot]).max() < 2e-2, "one more position and it is inside"
+
+
+def test_bf16_attention_row_bits_do_not_depend_on_the_tile():
+    """A query row gives the same bits alone (a decode step) and inside a long portion."""
+    rng = np.random.default_rng(12)
+    heads, kv_heads, hd, page = 4, 2, 64, 16
+    k, v, table, _, _ = _paged(rng, [300], kv_heads, hd, page)
+    k, v = bf(k), bf(v)
+    q = bf(rnd(rng, 300, heads, hd))
+    full, _, _ = _run_bf16_attention(q, [(0, 300)], k, v, table, heads, kv_heads, hd, 0)
+    for p in (0, 63, 64, 255, 299):
+        one, _, _ = _run_bf16_attention(q[p:p + 1], [(p, 1)], k, v, table, heads, kv_heads, hd, 0)
+        assert_same_bits(one[0], full[p], f"position {p}")
+    part, _, _ = _run_bf16_attention(q[100:171], [(100, 71)], k, v, table, heads, kv_heads, hd, 0)
+    assert_same_bits(part, full[100:171], "portion 100..170")
+
+
+def test_bf16_rope_and_cache_write():
+    rng = np.random.default_rng(13)
+    heads, kv_heads, hd, page = 4, 2, 16, 16
+    from bitwise_b200.parts.rope import RotaryEncoding
+    rot = RotaryEncoding(hd, 10000.0, None, positions=40)
+    cos, sin = rot.rotary_tables(DEV)
+    pos = np.array([0, 39, 16], dtype=np.int32)
+    seq = np.array([0, 0, 1], dtype=np.int32)
+    table = np.array([[2, 0, 1], [3, 4, 0]], dtype=np.int32)
+    qkv = bf(rnd(rng, 3, (heads + 2 * kv_heads) * hd))
+    k = torch.zeros(5, kv_heads, page, hd, device=DEV, dtype=torch.bfloat16)
+    v = torch.zeros_like(k)
+    buf = t(qkv, torch.bfloat16).clone()
+    _ops("bfloat16").rope_cache(buf, t(pos, torch.int32), t(seq, torch.int32), cos, sin, t(table, torch.int32), k, v,
+                                heads, kv_heads, hd)
+    inv = P.rope_inv_freq(hd, 10000.0)
+    want_q = bf(P.rope(qkv[:, :heads * hd].reshape(3, heads, hd), pos, inv))
+    want_k = bf(P.rope(qkv[:, heads * hd:(heads + kv_heads) * hd].reshape(3, kv_heads, hd), pos, inv))
+    got_q = buf.float().cpu().numpy()[:, :heads * hd].reshape(3, heads, hd)
+    # the kernel may fuse the two products of a rotation: at most one bfloat16 step apart
+    assert (np.abs(got_q - want_q) <= 2.0 ** -7 * np.abs(want_q) + 1e-6).all()
+    kc = k.float().cpu().numpy()
+    for r in range(3):
+        blk, slot = table[seq[r], pos[r] // page], pos[r] % page
+        assert (np.abs(kc[blk, :, slot] - want_k[r]) <= 2.0 ** -7 * np.abs(want_k[r]) + 1e-6).all()
