@@ -1,0 +1,264 @@
+"""``Engine``: requests in, tokens out, through the scheduler and the step function.
+
+The surface follows the reference's engine and its Python binding (src/engine.h:96-113;
+python/bindings.cpp:110-125): ``add_request(prompt, params) -> id``, ``step() ->
+[StepEvent]``, ``cancel``, ``idle``, ``result(id)``, ``stats``, ``free_blocks``,
+``num_running``, ``num_waiting``, ``now``.  ``EngineConfig`` keeps the reference's names
+where it has them (``num_blocks``, ``max_batched_tokens``, ``max_num_seqs``,
+``fingerprint_logits``; src/engine.h:38-50) and adds ``block_size`` (the reference fixes
+16, src/block_manager.h:20).  Prefix caching, speculative decoding, static batching and
+fault injection are not part of this engine.
+
+One step (src/engine.cpp:304-488): plan, build one batch, run it, sample the rows whose
+request reached its last known token (on the device, keyed by the position the new token
+will take), append, finish and free.  The logits fingerprint of a request
+(src/engine.cpp:18-29,246) is chained on the device in the request's state slot.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence as Seq
+
+import torch
+
+from ..cache.storage import FINGERPRINT_SEED, build_cache
+from ..model import _TORCH_DTYPE, Model
+from ..sampling.rng import counter_uniform
+from ..sampling.sampler import SamplingParams
+from .scheduler import Planned, Scheduler, Sequence
+from .step import StepEntry, Stepper
+
+
+@dataclass
+class EngineConfig:
+    num_blocks: int = 512
+    block_size: int = 16
+    max_batched_tokens: int = 256
+    max_num_seqs: int = 32
+    fingerprint_logits: bool = True
+    max_model_len: Optional[int] = None  # longest request (prompt + output); default: what the pool holds
+
+
+@dataclass
+class RequestResult:
+    tokens: List[int] = field(default_factory=list)
+    finished: bool = False
+    cancelled: bool = False
+    logits_fingerprint: int = FINGERPRINT_SEED
+    preemptions: int = 0
+    arrival: float = 0.0
+    first_token: float = -1.0
+    finish: float = -1.0
+    token_times: List[float] = field(default_factory=list)
+
+
+@dataclass
+class StepEvent:
+    id: int
+    tokens: List[int]
+    finished: bool
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_rows: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+    forward_seconds: float = 0.0
+
+
+def _signed64(v: int) -> int:
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+class Engine:
+    def __init__(self, model: Model, config: Optional[EngineConfig] = None):
+        self.model = model
+        self.config = config or EngineConfig()
+        c = self.config
+        self.manager, self.storage = build_cache(model.decoder, c.num_blocks, c.block_size, c.max_num_seqs,
+                                                 _TORCH_DTYPE[model.dtype], model.device)
+        pool_tokens = c.num_blocks * c.block_size
+        self.max_len = min(c.max_model_len or pool_tokens, pool_tokens)
+        self.stepper = Stepper(model.decoder, self.manager, self.storage, model.ops,
+                               max_rows=c.max_batched_tokens, max_seqs=c.max_num_seqs,
+                               max_tokens_per_request=self.max_len)
+        self.scheduler = Scheduler(self.manager, c.max_batched_tokens, c.max_num_seqs)
+        self.scheduler.on_preempt = self._save_fingerprint
+        self.vocab = model.decoder.head.vocab
+        self.eos_id = getattr(model.config, "eos_token_id", -1)
+        self.seqs: Dict[int, Sequence] = {}
+        self.results: Dict[int, RequestResult] = {}
+        self.stats = EngineStats()
+        self._next_id = 0
+        self._start = time.perf_counter()
+        dev = model.device
+        pin = torch.device(dev).type == "cuda"
+        m = c.max_num_seqs
+        # sampler inputs of a step, one pinned buffer: uniforms (f64), temperatures (f32), slots (i32)
+        self._samp_host = torch.zeros(m * 16, dtype=torch.uint8, pin_memory=pin)
+        self._samp_dev = torch.zeros(m * 16, dtype=torch.uint8, device=dev)
+        self._u_h, self._t_h, self._s_h = self._samp_views(self._samp_host, m)
+        self._u_d, self._t_d, self._s_d = self._samp_views(self._samp_dev, m)
+        self._tok_dev = torch.zeros(m, dtype=torch.int32, device=dev)
+        self._tok_host = torch.zeros(m, dtype=torch.int32, pin_memory=pin)
+        self.d2h_bytes = 0
+        self._fp_live = set()  # requests whose fingerprint chain sits in their current slot
+
+    @staticmethod
+    def _samp_views(buf: torch.Tensor, m: int):
+        return (buf[:m * 8].view(torch.float64), buf[m * 8:m * 12].view(torch.float32),
+                buf[m * 12:m * 16].view(torch.int32))
+
+    # -- the reference's surface -----------------------------------------------------------
+    def now(self) -> float:
+        return time.perf_counter() - self._start
+
+    def add_request(self, prompt: Seq[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("empty prompt")
+        if any(t < 0 or t >= self.vocab for t in prompt):
+            raise ValueError("token id out of range")
+        worst = len(prompt) + params.max_new_tokens + 1
+        if worst > self.config.num_blocks * self.config.block_size or worst > self.max_len + 1:
+            raise ValueError("request can never fit in the KV cache")
+        seq = Sequence(self._next_id, prompt, len(prompt), params)
+        self._next_id += 1
+        self.seqs[seq.id] = seq
+        self.results[seq.id] = RequestResult(arrival=self.now())
+        self.scheduler.add(seq)
+        return seq.id
+
+    def cancel(self, rid: int) -> None:
+        seq = self.seqs.get(rid)
+        if seq is None or seq.done:
+            return
+        self._finish(seq, cancelled=True)
+
+    def idle(self) -> bool:
+        return self.scheduler.idle()
+
+    @property
+    def num_running(self) -> int:
+        return len(self.scheduler.running)
+
+    @property
+    def num_waiting(self) -> int:
+        return len(self.scheduler.waiting)
+
+    @property
+    def free_blocks(self) -> int:
+        return self.manager.min_available()
+
+    def result(self, rid: int) -> RequestResult:
+        return self.results[rid]
+
+    # -- internals -------------------------------------------------------------------------
+    def _save_fingerprint(self, seq: Sequence) -> None:
+        """Before a request loses its slot, bring its fingerprint to the host."""
+        self._save_fingerprint_final(seq)
+        if seq.running:
+            self.results[seq.id].preemptions += 1
+
+    def _finish(self, seq: Sequence, cancelled: bool) -> None:
+        self._save_fingerprint_final(seq)
+        self.scheduler.finish(seq)
+        r = self.results[seq.id]
+        r.finished, r.cancelled, r.finish = True, cancelled, self.now()
+        del self.seqs[seq.id]
+
+    def _save_fingerprint_final(self, seq: Sequence) -> None:
+        if self.config.fingerprint_logits and seq.id in self._fp_live and self.manager.has(seq.id):
+            slot = self.manager.get(seq.id).slot
+            self.results[seq.id].logits_fingerprint = int(self.storage.fingerprints[slot].item()) & ((1 << 64) - 1)
+        self._fp_live.discard(seq.id)
+
+    def step(self) -> List[StepEvent]:
+        events: List[StepEvent] = []
+        self.stats.steps += 1
+        plan = self.scheduler.plan()
+        self.stats.preemptions = self.scheduler.stats.preemptions
+        if not plan:
+            return events
+        entries: List[StepEntry] = []
+        sampled: List[Planned] = []
+        for p in plan:
+            s = p.seq
+            last = s.computed + p.n == len(s.tokens)
+            entries.append(StepEntry(s.id, s.tokens[s.computed:s.computed + p.n], [p.n - 1] if last else []))
+            if last:
+                sampled.append(p)
+            if p.n == 1 and s.computed == len(s.tokens) - 1 and s.generated > 0:
+                self.stats.decode_rows += 1
+            else:
+                self.stats.prefill_tokens += p.n
+            if self.config.fingerprint_logits and s.id not in self._fp_live:
+                # a request that just got its slot: start (or, after preemption, continue) its chain
+                slot = self.manager.get(s.id).slot
+                self.storage.fingerprints[slot] = _signed64(self.results[s.id].logits_fingerprint)
+                self._fp_live.add(s.id)
+        t0 = time.perf_counter()
+        logits = self.stepper.run(entries)
+        c = len(sampled)
+        if c:
+            for i, p in enumerate(sampled):
+                s = p.seq
+                self._u_h[i] = counter_uniform(s.params.seed, len(s.tokens))
+                self._t_h[i] = s.params.temperature
+                self._s_h[i] = self.manager.get(s.id).slot
+            self._samp_dev.copy_(self._samp_host, non_blocking=True)
+            ops = self.model.ops
+            ops.sample_rows(logits, self._t_d[:c], self._u_d[:c], self._tok_dev[:c])
+            if self.config.fingerprint_logits:
+                ops.fingerprint_rows(logits, self._s_d[:c], self.storage.fingerprints)
+            self._tok_host[:c].copy_(self._tok_dev[:c], non_blocking=True)
+            if torch.device(self.model.device).type == "cuda":
+                torch.cuda.current_stream().synchronize()
+            self.d2h_bytes = c * 4
+        self.stats.forward_seconds += time.perf_counter() - t0
+        toks = self._tok_host[:c].tolist() if c else []
+        cursor = 0
+        finished: List[Sequence] = []
+        for p in plan:
+            s = p.seq
+            s.computed += p.n
+            if s.computed != len(s.tokens):
+                continue
+            token = int(toks[cursor])
+            cursor += 1
+            r = self.results[s.id]
+            s.tokens.append(token)
+            r.tokens.append(token)
+            t = self.now()
+            if r.first_token < 0:
+                r.first_token = t
+            r.token_times.append(t)
+            self.stats.generated_tokens += 1
+            done = (not s.params.ignore_eos and token == self.eos_id) or s.generated >= s.params.max_new_tokens
+            events.append(StepEvent(s.id, [token], done))
+            if done:
+                finished.append(s)
+        for s in finished:
+            self._finish(s, cancelled=False)
+        return events
+
+    def generate(self, prompts: Seq[Seq[int]], params: Optional[SamplingParams] = None,
+                 max_steps: int = 1_000_000) -> List[List[int]]:
+        """Convenience: run the given prompts to the end and return their generated tokens."""
+        if isinstance(params, (list, tuple)):
+            plist = list(params)
+        else:
+            plist = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, q) for p, q in zip(prompts, plist)]
+        steps = 0
+        while not self.idle():
+            self.step()
+            steps += 1
+            if steps > max_steps:
+                raise RuntimeError("the engine did not go idle (step limit reached)")
+        return [self.results[i].tokens for i in ids]

@@ -1,0 +1,83 @@
+"""The plain implementation against tkran2/bitwise's own model code.
+
+tests/golden/*.logits.f32 were produced by tests/golden/make_golden.py, which compiles the
+reference's src/*.cpp unmodified and runs its Runner and Engine on the tiny models of
+tests/tiny_configs.py.  The plain implementation (libm exp, float32) must reproduce those
+logits, the generated tokens and the logits fingerprint bit for bit.  Anchored on formulas
+only, not on the reference's code: the llama3 rescaling of the rotary frequencies (the
+golden run takes the rescaled table as an input), the random-weights generator, and the
+reproducible exp (compared here with libm's within 2 units in the last place).
+"""
+import ctypes
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+from tiny_configs import TINY
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_fma_emulation_is_exact():
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal(20000).astype(np.float32)
+    b = rng.standard_normal(20000).astype(np.float32)
+    c = (-(a.astype(np.float64) * b.astype(np.float64))).astype(np.float32)  # heavy cancellation
+    c[::2] = rng.standard_normal(10000).astype(np.float32) * 1e-3
+    got = P.fma32(a, b, c)
+    want = np.array([P._libm.fmaf(float(x), float(y), float(z)) for x, y, z in zip(a, b, c)], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_reproducible_exp_is_close_to_libm():
+    x = np.linspace(-87, 88, 20001).astype(np.float32)
+    d, l = P.exp_det(x).astype(np.float64), P.exp_libm(x).astype(np.float64)
+    assert (np.abs(d - l) / l).max() < 2.5 * 2.0 ** -24
+    assert P.exp_det(np.float32(-100.0)) == 0.0 and np.isinf(P.exp_det(np.float32(89.0)))
+    assert P.exp_det(np.float32(0.0)) == 1.0
+
+
+def test_dot16_is_the_written_out_tree():
+    rng = np.random.default_rng(1)
+    for n in (1, 5, 16, 31, 64, 100):  # tests/test_main.cpp:122-135
+        a, b = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+        lane = [np.float32(0)] * 16
+        for i in range(n):
+            lane[i % 16] = np.float32(P._libm.fmaf(float(a[i]), float(b[i]), float(lane[i % 16])))
+        s8 = [np.float32(lane[i] + lane[i + 8]) for i in range(8)]
+        s4 = [np.float32(s8[i] + s8[i + 4]) for i in range(4)]
+        want = np.float32(np.float32(s4[0] + s4[2]) + np.float32(s4[1] + s4[3]))
+        assert P.dot16(a, b).view(np.uint32) == want.view(np.uint32)
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_plain_reproduces_the_reference_bit_for_bit(name, tiny_folders):
+    meta = json.load(open(os.path.join(GOLD, name + ".json")))
+    digest = hashlib.sha256(open(os.path.join(tiny_folders[name], "model.safetensors"), "rb").read()).hexdigest()
+    assert digest == meta["model_sha256"], "the random-weights mode no longer writes the file the golden run saw"
+    gold = np.fromfile(os.path.join(GOLD, name + ".logits.f32"), dtype="<f4").reshape(len(meta["tokens"]), -1)
+    model = P.PlainLlama(tiny_folders[name], exp="libm")
+    got = model.logits(meta["tokens"])
+    assert np.array_equal(got.view(np.uint32), gold.view(np.uint32)), (
+        f"max abs diff {np.abs(got - gold).max()}")
+    g = meta["generate"]
+    toks, fp = P.generate(model, meta["tokens"][:g["prompt_len"]], g["new"], g["temperature"], g["seed"],
+                          ignore_eos=True)
+    assert toks == g["tokens"] and fp == g["fingerprint"]
+    # the reproducible exp changes logits by rounding only
+    det = P.PlainLlama(tiny_folders[name], exp="det").logits(meta["tokens"])
+    assert np.abs(det - gold).max() < 2e-6
+
+
+def test_counter_uniform_known_values():
+    # a pure function of (seed, position, stream), in [0, 1) (src/engine.cpp:35-38)
+    u = [P.counter_uniform(7, p) for p in range(1000)]
+    assert all(0.0 <= x < 1.0 for x in u) and len(set(u)) == 1000
+    assert P.counter_uniform(7, 5) == P.counter_uniform(7, 5) != P.counter_uniform(8, 5)
+    assert P.counter_uniform(7, 5, 0) != P.counter_uniform(7, 5, 1)
+    from bitwise_b200.sampling import counter_uniform
+    assert [counter_uniform(3, p) for p in range(50)] == [P.counter_uniform(3, p) for p in range(50)]
