@@ -1,0 +1,320 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, with roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default workload: the SmolLM2-1.7B shape (24 layers, hidden 2048, 32/32 heads, head size
+64, SwiGLU 8192, vocabulary 49152, tied embeddings), random N(0, 0.02) bfloat16 weights,
+synthetic prompt ids uniform over the vocabulary; batch of 8 requests decoding at a
+2,048-token context.  A "step" is one decode step of the whole batch.  Prints ONE JSON line:
+
+  value        decoded tokens per second, timed on the device with CUDA events
+  e2e          the same through the Python entry point (Engine.step): host tokens in from
+               pinned memory, sampled tokens read back to the host, every step
+  prefill      one step of 2,048 prompt tokens; frac = flops / time / bf16 peak
+  roofline     decode step: bytes it must read (every weight once + the cache of the live
+               requests) / time, against the copy bandwidth
+  points       decode tokens per second at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when present ("of measured"), else
+from the fallback figures of an earlier measurement on this kind of GPU ("of fallback").
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+REFERENCE_DECODE_TOKS = 7.26  # tkran2/bitwise README.md:142, SmolLM2-1.7B single stream on a 4-core AVX-512 VM
+
+
+def peaks():
+    path = os.path.join(HERE, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            flat = {}
+
+            def walk(x):
+                if isinstance(x, dict):
+                    for k, v in x.items():
+                        if isinstance(v, (int, float)):
+                            flat.setdefault(k, float(v))
+                        else:
+                            walk(v)
+            walk(d)
+            hbm = flat.get("hbm_gbs")
+            tf = flat.get("bf16_tflops")
+            tfs = flat.get("bf16_tflops_sustained", tf)
+            if hbm and tf:
+                return dict(hbm_gbs=hbm, bf16_tflops=tf, bf16_tflops_sustained=tfs, source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=FALLBACK_HBM_GBS, bf16_tflops=FALLBACK_BF16_TFLOPS, bf16_tflops_sustained=1400.0,
+                source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-i", "0", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            p = [x.strip() for x in line.split(",")]
+            if len(p) >= 6 and p[0].isdigit():
+                self.samples.append(p)
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(int(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def model_config(layers):
+    from bitwise_b200 import LlamaConfig
+    return LlamaConfig(vocab_size=49152, hidden_size=2048, num_hidden_layers=layers, num_attention_heads=32,
+                       num_key_value_heads=32, head_dim=64, intermediate_size=8192, rope_theta=130000.0,
+                       rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=8192)
+
+
+def matrix_params(c):
+    per_layer = (c.q_dim + 2 * c.kv_dim) * c.hidden_size + c.hidden_size * c.q_dim + 3 * c.hidden_size * c.intermediate_size
+    return per_layer * c.num_hidden_layers, c.vocab_size * c.hidden_size
+
+
+def decode_bytes(c, batch, ctx, elt):
+    body, head = matrix_params(c)
+    kv = batch * ctx * c.num_hidden_layers * 2 * c.kv_dim * elt
+    return (body + head) * elt + kv + batch * c.hidden_size * elt
+
+
+def prefill_flops(c, tokens):
+    body, head = matrix_params(c)
+    attn = c.num_hidden_layers * 2 * 2 * c.q_dim * (tokens * (tokens + 1) // 2)
+    return 2.0 * tokens * body + 2.0 * head + attn
+
+
+def run_decode(model, batch, ctx, steps, warmup, page, seed=0):
+    """Device-timed decode: `batch` requests, each with `ctx` tokens in the cache, one new
+    token each per step, sampled greedily on the device."""
+    import numpy as np
+    import torch
+    from bitwise_b200.cache.storage import build_cache
+    from bitwise_b200.engine.step import StepEntry, Stepper
+    c = model.config
+    total = ctx + warmup + steps + 1
+    pages_per = (total + page - 1) // page
+    manager, storage = build_cache(model.decoder, pages_per * batch, page, batch, torch.bfloat16 if
+                                   model.dtype == "bfloat16" else torch.float32, model.device)
+    chunk = 2048
+    st = Stepper(model.decoder, manager, storage, model.ops, max_rows=max(chunk, batch), max_seqs=batch,
+                 max_tokens_per_request=pages_per * page)
+    rng = np.random.default_rng(seed)
+    for b in range(batch):  # fill the contexts by real prefill
+        toks = rng.integers(0, c.vocab_size, ctx - 1).tolist()
+        for i in range(0, len(toks), chunk):
+            st.run([StepEntry(b, toks[i:i + chunk], [])])
+    nxt = rng.integers(0, c.vocab_size, batch).tolist()
+    temps = torch.zeros(batch, device=model.device)
+    us = torch.zeros(batch, dtype=torch.float64, device=model.device)
+    out = torch.zeros(batch, dtype=torch.int32, device=model.device)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def one_step():
+        logits = st.run([StepEntry(b, [nxt[b]], [0]) for b in range(batch)])
+        model.ops.sample_rows(logits, temps, us, out)
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    l0 = model.ops.launches
+    ev0.record()
+    for _ in range(steps):
+        one_step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    launches = model.ops.launches - l0
+    del st, manager, storage
+    torch.cuda.empty_cache()
+    return ms, launches
+
+
+def run_prefill(model, tokens, reps, warmup, page):
+    import numpy as np
+    import torch
+    from bitwise_b200.cache.storage import build_cache
+    from bitwise_b200.engine.step import StepEntry, Stepper
+    c = model.config
+    pages = (tokens + page - 1) // page
+    manager, storage = build_cache(model.decoder, pages, page, 1, torch.bfloat16 if model.dtype == "bfloat16"
+                                   else torch.float32, model.device)
+    st = Stepper(model.decoder, manager, storage, model.ops, max_rows=tokens, max_seqs=1,
+                 max_tokens_per_request=pages * page)
+    toks = np.random.default_rng(1).integers(0, c.vocab_size, tokens).tolist()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for i in range(warmup + reps):
+        torch.cuda.synchronize()
+        ev0.record()
+        st.run([StepEntry("p", toks, [tokens - 1])])
+        ev1.record()
+        torch.cuda.synchronize()
+        st.finish("p")
+        if i >= warmup:
+            times.append(ev0.elapsed_time(ev1))
+    del st, manager, storage
+    torch.cuda.empty_cache()
+    return sorted(times)[len(times) // 2]
+
+
+def run_e2e(model, batch, ctx, steps, warmup, page):
+    """Through Engine.step(): prompts of ctx-1 tokens are prefilled by the engine itself, then
+    `steps` decode steps are timed by the host clock, each with its host-to-device copy of the
+    step's inputs and the device-to-host read of the sampled tokens."""
+    import numpy as np
+    import torch
+    from bitwise_b200 import Engine, EngineConfig, SamplingParams
+    c = model.config
+    total = ctx + warmup + steps + 2
+    pages_per = (total + page - 1) // page
+    eng = Engine(model, EngineConfig(num_blocks=pages_per * batch, block_size=page, max_batched_tokens=2048,
+                                     max_num_seqs=batch, fingerprint_logits=False, max_model_len=pages_per * page))
+    rng = np.random.default_rng(2)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 1, ignore_eos=True)
+    for b in range(batch):
+        eng.add_request(rng.integers(0, c.vocab_size, ctx - 1).tolist(), sp)
+    guard = 0
+    while eng.stats.generated_tokens < batch:  # until every request has left its prompt behind
+        eng.step()
+        guard += 1
+        assert guard < 10000
+    for _ in range(warmup - 1):
+        eng.step()
+    torch.cuda.synchronize()
+    g0 = eng.stats.generated_tokens
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    made = eng.stats.generated_tokens - g0
+    h2d = eng.stepper.h2d_bytes + eng._samp_host.numel()
+    d2h = eng.d2h_bytes
+    del eng
+    torch.cuda.empty_cache()
+    return made / dt, h2d, d2h
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=24, help="layers to run (the shape has 24)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling runs)")
+    ap.add_argument("--skip-prefill", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "tkran2/bitwise has neither setup.py nor pyproject.toml, so pip cannot install it "
+                          "(a CMake C++ project, CPU only)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    from bitwise_b200 import Model
+    pk = peaks()
+    cfg = model_config(args.layers)
+    model = Model.random(cfg, seed=0, dtype=args.dtype, device="cuda:0", fast=True)
+    elt = 2 if args.dtype == "bfloat16" else 4
+
+    with ClockSampler() as clocks:
+        ms, launches = run_decode(model, args.batch, args.ctx, args.steps, warmup, args.page)
+    value = args.batch / (ms / 1e3)
+    bytes_step = decode_bytes(cfg, args.batch, args.ctx, elt)
+    achieved = bytes_step / (ms / 1e3) / 1e9
+
+    line = {
+        "metric": "decode tok/s at batch 8, 2,048-token context (SmolLM2-1.7B shape)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / REFERENCE_DECODE_TOKS, 1), "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary",
+        "impl": "ours",
+        "config": {"model": "SmolLM2-1.7B shape", "layers": cfg.num_hidden_layers, "layers_run": args.layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied_embeddings": True, "global_batch": args.batch, "seq_len": args.ctx,
+                   "page_size": args.page, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights + cache read per step exceed 126 MB)",
+                   "peaks": "of " + pk["source"]},
+        "clocks": clocks.summary(),
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": bytes_step},
+    }
+    if args.layers != 24:
+        line["config"]["layers"] = 24
+    if not args.skip_prefill:
+        pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
+        fl = prefill_flops(cfg, 2048)
+        line["prefill"] = {"value": round(2048 / (pms / 1e3), 1), "tokens": 2048, "ms": round(pms, 3),
+                           "frac": round(fl / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4), "flops": fl}
+    if not args.skip_points:
+        pts = {}
+        for b in (1, 64):
+            pm, _ = run_decode(model, b, args.ctx, max(10, args.steps // 2), 3, args.page)
+            pts[f"decode_b{b}"] = round(b / (pm / 1e3), 1)
+            pts[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, args.ctx, elt) / (pm / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+        line["points"] = pts
+        e, h2d, d2h = run_e2e(model, args.batch, args.ctx, args.steps, warmup, args.page)
+        line["e2e"] = {"value": round(e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
