@@ -276,6 +276,11 @@ int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32
 
 }  // namespace
 
+// The tcgen05 / TMA variant for large batches (bf16_gemm_tc.cu), same summation order.
+BW_API int bw_bf16_linear_tc_usable(const void* x, const void* w, int k);
+BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
+                             const float* residual, int m, int n, int k, cudaStream_t stream);
+
 // Rows up to which a product is run with one thread block per chunk, and the scratch that
 // this needs: chunk sums [chunks][m][n] float32 and one counter per output tile.
 constexpr int kSplitMaxRows = 64;
@@ -300,7 +305,12 @@ BW_API int bw_bf16_linear(const __nv_bfloat16* x, const __nv_bfloat16* w, void* 
     bw::set_error("linear: inner size %d", k);
     return -1;
   }
-  if (m > kSplitMaxRows) return launch<128, 128, 4, 4, 3, false>(x, w, y, y_is_f32, residual, m, n, k, nullptr, nullptr, stream);
+  if (m > kSplitMaxRows) {
+    // rows that start on 16 bytes go through TMA to the tcgen05 tensor cores; other shapes
+    // (an inner size that is no multiple of 8) take the legacy tensor-core tile
+    if (bw_bf16_linear_tc_usable(x, w, k)) return bw_bf16_linear_tc(x, w, y, y_is_f32, residual, m, n, k, stream);
+    return launch<128, 128, 4, 4, 3, false>(x, w, y, y_is_f32, residual, m, n, k, nullptr, nullptr, stream);
+  }
   const int chunks = (k + kChunk - 1) / kChunk;
   const int tiles = (n + kSplitBN - 1) / kSplitBN;
   const bool split = chunks > 1 && tiles < 2 * 148 && partials != nullptr && counters != nullptr;

@@ -1,0 +1,401 @@
+// The bfloat16 matrix product on the fifth-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands brought into shared memory by TMA, for batches of
+// more than 64 rows (prefill portions). Same summation order as every other variant of the
+// product: chunks of 512 along k at fixed positions, inside a chunk the tensor core
+// accumulates in steps of 16 along k, the chunk sums are added in float32 in ascending order.
+//
+// One thread block computes one 128 x 128 output tile with six warps:
+//   warp 0   one thread issues the TMA loads of the x tile and the W tile, 64 k-elements per
+//            stage (128-byte rows, 128-byte swizzle), into a ring of stages
+//   warp 1   one thread issues tcgen05.mma (M 128, N 128, K 16, four per stage) into one of
+//            two accumulators in tensor memory; a commit frees the stage, and at the end of a
+//            chunk another commit hands the accumulator to the epilogue
+//   warps 2-5  read the finished chunk sum from tensor memory (each thread one row, 32 columns
+//            at a time) and add it to the running total in registers, while the tensor core
+//            already works on the next chunk in the other accumulator; after the last chunk
+//            they add the residual and store.
+// The kernel is persistent: one block per SM (6 stages of 32 KB) takes output tiles round-robin,
+// and because loads, MMAs and the epilogue each walk the tile sequence on their own, the store
+// of one tile overlaps the main loop of the next.
+//
+// Every wait on an mbarrier is bounded: after a limit the thread raises a flag in global
+// memory and the block drains and returns instead of hanging; the host reports the flag.
+#include <cuda.h>
+
+#include "bw_common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int kChunk = 512;
+constexpr int kTilesPerChunk = kChunk / BK;
+constexpr int kStages = 6;
+constexpr int kStageBytes = (BM + BN) * BK * 2;  // 32 KB
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;  // two accumulators of 128 columns
+constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
+
+struct __align__(8) Barriers {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: false when the limit ran out (or another thread of the block already gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* failed) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && *failed) return false;
+  }
+  *failed = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, written by
+// TMA with the 128-byte swizzle: start address / 16 in bits 0-13, leading byte offset (unused
+// for swizzled K-major layouts, set to 1) in bits 16-29, stride byte offset 1024 / 16 (eight
+// rows of 128 bytes) in bits 32-45, descriptor version 1 in bits 46-47, layout type 2
+// (128-byte swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor of kind::f16: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9
+// and 10-12 = 1), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                (static_cast<uint32_t>(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
+               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // the swizzled tiles want 1024-byte alignment
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(tiles + kStages * kStageBytes);
+  volatile uint32_t* failed = &bars->failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = (K + BK - 1) / BK;          // k-tiles of one output tile
+  const int num_chunks = (K + kChunk - 1) / kChunk;
+  const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
+  const int out_tiles = m_blocks * n_blocks;
+  // Output tiles are dealt round-robin to the resident blocks; tile t covers rows of block
+  // t % m_blocks and columns of block t / m_blocks, so blocks that run at the same time share
+  // W tiles through L2. The three roles below walk the same sequence of tiles.
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    bars->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // this warp owns the tensor-memory allocation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "n"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;  // k-tiles issued so far, over all output tiles of this block
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_blocks) * BM, n0 = (tile / m_blocks) * BN;
+        for (int kt = 0; kt < num_tiles; ++kt, ++it) {
+          const int s = it % kStages;
+          const uint32_t round = it / kStages;
+          if (round > 0 && !mbar_wait(&bars->empty[s], (round - 1) & 1, failed)) {
+            ok = false;
+            break;
+          }
+          unsigned char* a = tiles + s * kStageBytes;
+          mbar_expect_tx(&bars->full[s], kStageBytes);
+          tma_load_2d(a, &map_x, kt * BK, m0, &bars->full[s]);
+          tma_load_2d(a + BM * BK * 2, &map_w, kt * BK, n0, &bars->full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, gc = 0;  // k-tiles and chunks consumed so far
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
+        for (int c = 0; c < num_chunks && ok; ++c, ++gc) {
+          const int buf = gc & 1;
+          const uint32_t use = gc >> 1;  // how often this accumulator was used before
+          if (use > 0 && !mbar_wait(&bars->acc_empty[buf], (use - 1) & 1, failed)) {
+            ok = false;
+            break;
+          }
+          fence_after_sync();
+          const uint32_t d = tmem_base + buf * BN;
+          const int t_begin = c * kTilesPerChunk, t_end = min(num_tiles, t_begin + kTilesPerChunk);
+          for (int kt = t_begin; kt < t_end; ++kt, ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait(&bars->full[s], (it / kStages) & 1, failed)) {
+              ok = false;
+              break;
+            }
+            fence_after_sync();
+            const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
+            const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + BM * BK * 2);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              // 16 k-elements are 32 bytes: the start address field moves by 2 (units of 16 bytes)
+              umma(d, adesc + 2 * k, bdesc + 2 * k, (kt > t_begin || k > 0) ? 1u : 0u);
+            }
+            umma_commit(&bars->empty[s]);  // the stage may be refilled once these MMAs are done
+          }
+          if (ok) umma_commit(&bars->acc_full[buf]);
+        }
+      }
+    }
+  } else {
+    // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int quarter = warp & 3;
+    float total[BN];
+    uint32_t gc = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % m_blocks) * BM, n0 = (tile / m_blocks) * BN;
+      const int row = m0 + quarter * 32 + lane;
+      for (int c = 0; c < num_chunks && ok; ++c, ++gc) {
+        const int buf = gc & 1;
+        if (!mbar_wait(&bars->acc_full[buf], (gc >> 1) & 1, failed)) {
+          ok = false;
+          break;
+        }
+        fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll
+        for (int g = 0; g < BN / 32; ++g) {
+          float v[32];
+          tmem_ld32(taddr + g * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) total[g * 32 + j] = (c == 0) ? v[j] : total[g * 32 + j] + v[j];
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+      }
+      if (!ok || row >= M) continue;
+      const size_t base = static_cast<size_t>(row) * N + n0;
+      const int cols = min(BN, N - n0);
+      if (y_is_f32) {
+        float* out = static_cast<float*>(Y) + base;
+        const float* res = residual ? residual + base : nullptr;
+        if (cols == BN && (N & 3) == 0) {
+#pragma unroll
+          for (int j = 0; j < BN; j += 4) {
+            float4 o = make_float4(total[j], total[j + 1], total[j + 2], total[j + 3]);
+            if (res) {
+              const float4 r = *reinterpret_cast<const float4*>(res + j);
+              o.x = r.x + o.x, o.y = r.y + o.y, o.z = r.z + o.z, o.w = r.w + o.w;
+            }
+            *reinterpret_cast<float4*>(out + j) = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN; ++j)  // static indices keep the totals in registers
+            if (j < cols) out[j] = res ? res[j] + total[j] : total[j];
+        }
+      } else {
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + base;
+        if (cols == BN && (N & 7) == 0) {
+#pragma unroll
+          for (int j = 0; j < BN; j += 8) {
+            __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(total[j + 2 * e], total[j + 2 * e + 1]);
+            *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN; ++j)
+            if (j < cols) out[j] = __float2bfloat16_rn(total[j]);
+        }
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && bars->failed) atomicExch(error_flag, 1);
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+
+// rows x k bf16, row-major; box of 128 rows x 64 k-elements, 128-byte swizzle, zero fill outside
+bool make_map(CUtensorMap* map, const void* base, int rows, int k) {
+  EncodeTiled enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {BK, BM};
+  const cuuint32_t elem[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int* g_error_flag = nullptr;  // one word of device memory, allocated on first use
+
+}  // namespace
+
+// Whether this product can run on the tcgen05 path: rows that start on 16 bytes (TMA).
+BW_API int bw_bf16_linear_tc_usable(const void* x, const void* w, int k) {
+  return (k % 8 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
+         encoder() != nullptr;
+}
+
+// Reads and clears the flag that a kernel raises when one of its bounded waits ran out.
+BW_API int bw_bf16_linear_tc_failed() {
+  if (!g_error_flag) return 0;
+  int v = 0;
+  cudaMemcpy(&v, g_error_flag, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(g_error_flag, 0, sizeof(int));
+  return v;
+}
+
+BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
+                             const float* residual, int m, int n, int k, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (!bw_bf16_linear_tc_usable(x, w, k)) {
+    bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
+    return -1;
+  }
+  if (!g_error_flag) {
+    cudaError_t e = cudaMalloc(&g_error_flag, sizeof(int));
+    if (e != cudaSuccess) {
+      bw::set_error("linear (tcgen05): cannot allocate the error word: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    cudaMemset(g_error_flag, 0, sizeof(int));
+  }
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, x, m, k) || !make_map(&map_w, w, n, k)) {
+    bw::set_error("linear (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
+    return -1;
+  }
+  constexpr int smem = kStages * kStageBytes + sizeof(Barriers) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    configured = true;
+  }
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const long long out_tiles = static_cast<long long>((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  const unsigned grid = static_cast<unsigned>(out_tiles < sm_count ? out_tiles : sm_count);
+  gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, g_error_flag);
+  return bw::launch_status();
+}

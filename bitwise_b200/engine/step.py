@@ -84,8 +84,11 @@ class _Layout:
 class Stepper:
     """Owns the step's device buffers and runs steps for one model and one cache."""
 
+    GRAPH_MAX_ROWS = 256   # steps up to this many rows are replayed as CUDA graphs
+    GRAPH_CACHE = 64       # graphs kept (one per batch shape)
+
     def __init__(self, model, manager: CacheManager, storage: CacheStorage, ops, max_rows: int,
-                 max_seqs: int, max_tokens_per_request: int):
+                 max_seqs: int, max_tokens_per_request: int, use_graphs: Optional[bool] = None):
         self.model, self.manager, self.storage, self.ops = model, manager, storage, ops
         self.device = model.device
         self.max_rows, self.max_seqs = max_rows, max_seqs
@@ -102,6 +105,18 @@ class Stepper:
         self.h2d_bytes = 0
         self._copy_done = torch.cuda.Event() if pin else None
         self._copy_pending = False
+        # Small steps are bound by launch overhead: after a batch shape has been run once
+        # eagerly (which allocates every buffer it needs), its kernel sequence is captured
+        # into a CUDA graph and replayed.  All indices live in the packed device buffer, so
+        # a replay differs from another only by the data copied before it.  Only the serving
+        # precision does this (the 32-bit attention sizes its shared memory on the host),
+        # and only models whose parts all say they are safe to capture.
+        if use_graphs is None:
+            use_graphs = pin and getattr(ops, "kind", "") == "bf16"
+        self.use_graphs = bool(use_graphs) and getattr(model, "graph_safe", lambda: False)()
+        self._graphs: Dict[tuple, tuple] = {}
+        self._seen: Dict[tuple, int] = {}
+        self.graph_replays = 0
 
     # -- building the batch ------------------------------------------------------------
     def _section(self, t: torch.Tensor, start: int, n: int) -> torch.Tensor:
@@ -210,7 +225,27 @@ class Stepper:
         the stepper's buffer, valid until the next step) or None when nothing is wanted."""
         ctx, after = self.prepare(entries)
         views = self.storage.views(ctx.block_tables, ctx.seq_slot)
-        logits = self.model.forward(ctx, views)
+        key = None
+        if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:
+            key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows) + tuple(t[3] for t in ctx.tile_sets.values())
+        if key is not None and key in self._graphs:
+            graph, logits, launches = self._graphs[key]
+            graph.replay()
+            self.ops.launches += launches
+            self.graph_replays += 1
+        elif key is not None and self._seen.get(key, 0) >= 1 and len(self._graphs) < self.GRAPH_CACHE:
+            before = self.ops.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, views)
+            launches = self.ops.launches - before
+            self._graphs[key] = (graph, logits, launches)
+            graph.replay()
+            self.graph_replays += 1
+        else:
+            logits = self.model.forward(ctx, views)
+            if key is not None:
+                self._seen[key] = self._seen.get(key, 0) + 1
         for rid, length in after:
             self.manager.advance(rid, length)
         self.steps += 1

@@ -60,6 +60,7 @@ class KernelOps:
         self._verbose_build = verbose_build
         self._partials: Optional[torch.Tensor] = None  # scratch of the split products (bfloat16 path)
         self._counters: Optional[torch.Tensor] = None
+        self._retired = []
         if self.kind == "bf16":
             self.lib.bw_bf16_linear_scratch_floats.restype = ctypes.c_longlong
             self._split_rows = int(self.lib.bw_bf16_linear_split_rows())
@@ -161,10 +162,19 @@ class KernelOps:
         floats = int(self.lib.bw_bf16_linear_scratch_floats(_c_int(self._split_rows), _c_int(n), _c_int(k)))
         tiles = int(self.lib.bw_bf16_linear_counters(_c_int(n)))
         if self._partials is None or self._partials.numel() < floats:
+            self._retired.append(self._partials)  # a captured graph may still point at the old one
             self._partials = torch.empty(floats, dtype=torch.float32, device=device)
         if self._counters is None or self._counters.numel() < tiles:
+            self._retired.append(self._counters)
             self._counters = torch.zeros(max(tiles, 1024), dtype=torch.int32, device=device)
         return self._partials, self._counters
+
+    def device_failure(self) -> bool:
+        """True (once) when a kernel gave up a bounded wait since the last call.  This reads a
+        word from the device, so callers ask now and then, not every step."""
+        if self.kind != "bf16":
+            return False
+        return bool(self.lib.bw_bf16_linear_tc_failed())
 
     def attention_tile_rows(self, heads: int, kv_heads: int) -> int:
         """Query rows per attention tile: the bfloat16 kernel stacks the heads of a group

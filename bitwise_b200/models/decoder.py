@@ -94,6 +94,14 @@ class DecoderModel:
     def param_bytes(self) -> int:
         return self.embedding.param_bytes() + sum(b.param_bytes() for b in self.blocks) + self.head.param_bytes()
 
+    def graph_safe(self) -> bool:
+        """True when every part runs kernels only (no host decisions inside forward), so a
+        step's launches can be captured into a CUDA graph."""
+        parts = [self.embedding, self.head, self.head.norm] + list(self.position_encodings)
+        for b in self.blocks:
+            parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     def reserve_positions(self, positions: int) -> None:
         for pe in self.position_encodings:
             if hasattr(pe, "reserve"):

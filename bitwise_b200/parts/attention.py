@@ -20,6 +20,8 @@ from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, StepContext
 
 
 class GQAAttention(Mixer):
+    graph_safe = True  # kernels only: a step through this part can be captured
+
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int,
                  position: Optional[PositionEncoding] = None, window: Optional[int] = None,
                  names=("q_proj", "k_proj", "v_proj", "o_proj")):

@@ -16,6 +16,8 @@ from .base import FeedForward, Mixer, Norm, Part, StepContext
 
 
 class PreNormBlock(Part):
+    graph_safe = True  # kernels only: a step through this part can be captured
+
     def __init__(self, width: int, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm,
                  names: Dict[str, str]):
         self.width = width

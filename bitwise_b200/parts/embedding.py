@@ -16,6 +16,8 @@ from .base import Norm, Part, StepContext
 
 
 class TokenEmbedding(Part):
+    graph_safe = True  # kernels only: a step through this part can be captured
+
     def __init__(self, vocab: int, width: int, name: str = "embed_tokens"):
         self.vocab, self.width, self.name = vocab, width, name
         self.table: Optional[torch.Tensor] = None
@@ -34,6 +36,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True  # kernels only: a step through this part can be captured
+
     def __init__(self, vocab: int, width: int, norm: Norm, tied_to: Optional[TokenEmbedding] = None,
                  norm_name: str = "model.norm", head_name: str = "lm_head"):
         self.vocab, self.width = vocab, width

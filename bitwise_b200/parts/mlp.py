@@ -13,6 +13,8 @@ from .base import FeedForward, StepContext, register_feed_forward
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True  # kernels only: a step through this part can be captured
+
     def __init__(self, width: int, intermediate: int, names=("gate_proj", "up_proj", "down_proj")):
         self.width, self.intermediate = width, intermediate
         self.names = names

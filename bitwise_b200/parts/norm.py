@@ -11,6 +11,8 @@ from .base import Norm, StepContext, register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True  # kernels only: a step through this part can be captured
+
     def __init__(self, width: int, eps: float):
         self.width = width
         self.eps = float(eps)

@@ -58,6 +58,8 @@ def inverse_frequencies(head_dim: int, theta: float, scaling=None) -> np.ndarray
 
 class RotaryEncoding(PositionEncoding):
     """cos / sin tables [positions, head_dim / 2] in float32, grown on demand."""
+    graph_safe = True  # kernels only: a step through this part can be captured
+
 
     def __init__(self, head_dim: int, theta: float, scaling=None, positions: int = 0):
         if head_dim % 2:
@@ -67,6 +69,7 @@ class RotaryEncoding(PositionEncoding):
         self._cos = np.empty((0, head_dim // 2), dtype=np.float32)
         self._sin = np.empty((0, head_dim // 2), dtype=np.float32)
         self._device_tables = {}
+        self._retired = []
         if positions:
             self.reserve(positions)
 
@@ -87,7 +90,8 @@ class RotaryEncoding(PositionEncoding):
                 cos[p, i] = cosf(a)
                 sin[p, i] = sinf(a)
         self._cos, self._sin = cos, sin
-        self._device_tables.clear()
+        self._retired.append(self._device_tables)  # captured graphs may still read the old tables
+        self._device_tables = {}
 
     def max_positions(self) -> Optional[int]:
         return self._cos.shape[0]

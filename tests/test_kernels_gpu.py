@@ -218,7 +218,8 @@ def bf(a):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (5, 100, 96), (64, 344, 64), (65, 130, 172), (200, 256, 1100),
-                                   (8, 2048, 2048), (33, 72, 520)])
+                                   (8, 2048, 2048), (33, 72, 520), (65, 64, 64), (130, 100, 96), (200, 256, 1104),
+                                   (300, 2112, 2048), (1000, 136, 520)])
 def test_bf16_linear(m, n, k):
     """Tolerance: float32 accumulation of exact bfloat16 products; the result may differ from
     the float64 sum by accumulation rounding only: 1e-4 of the largest output (float32 out),
@@ -238,6 +239,7 @@ def test_bf16_linear(m, n, k):
     acc = t(res).clone()
     ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), acc, residual=acc)
     assert np.abs(acc.cpu().numpy() - (res + want)).max() <= 1e-4 * np.abs(want).max() + 1e-6
+    assert not ops.device_failure(), "a kernel gave up a bounded wait"
 
 
 def test_bf16_linear_row_bits_do_not_depend_on_the_batch():
