@@ -276,41 +276,49 @@ int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32
 
 }  // namespace
 
-// The tcgen05 / TMA variant for large batches (bf16_gemm_tc.cu), same summation order.
+// The tcgen05 / TMA variant (bf16_gemm_tc.cu), same summation order, for every shape whose
+// rows start on 16 bytes.
 BW_API int bw_bf16_linear_tc_usable(const void* x, const void* w, int k);
+BW_API int bw_bf16_linear_tc_splits(int m, int n, int k);
+BW_API long long bw_bf16_linear_tc_scratch_floats(int m, int n, int k);
+BW_API int bw_bf16_linear_tc_counters(int n);
 BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
-                             const float* residual, int m, int n, int k, cudaStream_t stream);
+                             const float* residual, int m, int n, int k, float* partials, int* counters,
+                             cudaStream_t stream);
 
-// Rows up to which a product is run with one thread block per chunk, and the scratch that
-// this needs: chunk sums [chunks][m][n] float32 and one counter per output tile.
+// Rows up to which the legacy tile runs with one thread block per chunk.
 constexpr int kSplitMaxRows = 64;
 constexpr int kSplitBN = 64;
 
-BW_API int bw_bf16_linear_split_rows() { return kSplitMaxRows; }
-
+// Scratch that a product of this shape may need (chunk sums and per-tile counters), whichever
+// variant runs it: the caller provides at least this much.
 BW_API long long bw_bf16_linear_scratch_floats(int m, int n, int k) {
   const long long chunks = (k + kChunk - 1) / kChunk;
-  return chunks * m * n;
+  const bool tc = bw_bf16_linear_tc_splits(m, n, k) != 0;
+  const bool legacy = m <= kSplitMaxRows && chunks > 1 && (n + kSplitBN - 1) / kSplitBN < 2 * 148;
+  return (tc || legacy) ? chunks * m * n : 0;
 }
 
 BW_API int bw_bf16_linear_counters(int n) { return (n + kSplitBN - 1) / kSplitBN; }
 
-// The caller provides the scratch (`partials` may be null when no product of this shape
-// is split, i.e. m > 64, a single chunk, or more than 2 * 148 output tiles without it).
+BW_API int bw_bf16_linear_split_rows() { return 128; }
+
+// One entry for every bfloat16 product. `use_legacy` != 0 forces the mma.sync tile (tests
+// compare the two variants bit for bit); otherwise the tcgen05 kernel runs whenever the rows
+// start on 16 bytes, and the legacy tile takes the remaining shapes (an inner size that is no
+// multiple of 8).
 BW_API int bw_bf16_linear(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
                           const float* residual, int m, int n, int k, float* partials, int* counters,
-                          cudaStream_t stream) {
+                          int use_legacy, cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0) {
     bw::set_error("linear: inner size %d", k);
     return -1;
   }
-  if (m > kSplitMaxRows) {
-    // rows that start on 16 bytes go through TMA to the tcgen05 tensor cores; other shapes
-    // (an inner size that is no multiple of 8) take the legacy tensor-core tile
-    if (bw_bf16_linear_tc_usable(x, w, k)) return bw_bf16_linear_tc(x, w, y, y_is_f32, residual, m, n, k, stream);
+  if (!use_legacy && bw_bf16_linear_tc_usable(x, w, k))
+    return bw_bf16_linear_tc(x, w, y, y_is_f32, residual, m, n, k, partials, counters, stream);
+  if (m > kSplitMaxRows)
     return launch<128, 128, 4, 4, 3, false>(x, w, y, y_is_f32, residual, m, n, k, nullptr, nullptr, stream);
-  }
   const int chunks = (k + kChunk - 1) / kChunk;
   const int tiles = (n + kSplitBN - 1) / kSplitBN;
   const bool split = chunks > 1 && tiles < 2 * 148 && partials != nullptr && counters != nullptr;

@@ -1,8 +1,12 @@
 // The bfloat16 matrix product on the fifth-generation tensor cores: tcgen05.mma with the
-// accumulator in tensor memory, operands brought into shared memory by TMA, for batches of
-// more than 64 rows (prefill portions). Same summation order as every other variant of the
-// product: chunks of 512 along k at fixed positions, inside a chunk the tensor core
-// accumulates in steps of 16 along k, the chunk sums are added in float32 in ascending order.
+// accumulator in tensor memory, operands brought into shared memory by TMA. One summation
+// order for every batch size: chunks of 512 along k at fixed positions, inside a chunk the
+// tensor core accumulates in steps of 16 along k, the chunk sums are added in float32 in
+// ascending order. A product with many output tiles walks the chunks of a tile inside one
+// block ("whole" mode). A product with few output tiles and few rows (decode steps) gives
+// every (tile, chunk) pair to a block as a work item of its own ("split" mode), so that the
+// weights stream from all SMs; the chunk sums go to scratch memory and a second small kernel
+// adds them in the same ascending order.
 //
 // One thread block computes one 128 x 128 output tile with six warps:
 //   warp 0   one thread issues the TMA loads of the x tile and the W tile, 64 k-elements per
@@ -115,28 +119,50 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Second half of split mode: y[m][n] = residual + ((p0 + p1) + p2) + ..., the chunk sums taken
+// in ascending order. One thread per output; the loads of eight chunks are issued together,
+// the additions stay in order.
+__global__ void reduce_chunks_kernel(const float* __restrict__ partials, int num_chunks, void* Y, int y_is_f32,
+                                     const float* residual, int M, int N) {
+  const size_t total = static_cast<size_t>(M) * N;
+  const size_t o = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (o >= total) return;
+  float v = 0.0f;
+  for (int c0 = 0; c0 < num_chunks; c0 += 8) {
+    float p[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = (c0 + e < num_chunks) ? __ldcg(partials + (c0 + e) * total + o) : 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (c0 + e < num_chunks) v = (c0 + e == 0) ? p[e] : v + p[e];
+  }
+  if (residual) v = residual[o] + v;
+  if (y_is_f32)
+    static_cast<float*>(Y)[o] = v;
+  else
+    static_cast<__nv_bfloat16*>(Y)[o] = __float2bfloat16_rn(v);
+}
+
+template <bool SPLIT>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
-               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag) {
+               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzled tiles want 1024-byte alignment
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -147,10 +173,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int num_tiles = (K + BK - 1) / BK;          // k-tiles of one output tile
   const int num_chunks = (K + kChunk - 1) / kChunk;
   const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
-  const int out_tiles = m_blocks * n_blocks;
-  // Output tiles are dealt round-robin to the resident blocks; tile t covers rows of block
-  // t % m_blocks and columns of block t / m_blocks, so blocks that run at the same time share
-  // W tiles through L2. The three roles below walk the same sequence of tiles.
+  // Work items are dealt round-robin to the resident blocks and the three roles below walk
+  // the same sequence of items. Whole mode: item t is the output tile with rows of block
+  // t % m_blocks and columns of block t / m_blocks, all its chunks (blocks that run at the same
+  // time share W tiles through L2). Split mode (one block of rows): item t is chunk
+  // t % num_chunks of the output tile with columns of block t / num_chunks.
+  const int out_tiles = SPLIT ? n_blocks * num_chunks : m_blocks * n_blocks;
+  auto item_m0 = [&](int t) { return SPLIT ? 0 : (t % m_blocks) * BM; };
+  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * BN : (t / m_blocks) * BN; };
+  auto item_c0 = [&](int t) { return SPLIT ? t % num_chunks : 0; };
+  auto item_c1 = [&](int t) { return SPLIT ? t % num_chunks + 1 : num_chunks; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -180,8 +212,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       uint32_t it = 0;  // k-tiles issued so far, over all output tiles of this block
       bool ok = true;
       for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_blocks) * BM, n0 = (tile / m_blocks) * BN;
-        for (int kt = 0; kt < num_tiles; ++kt, ++it) {
+        const int m0 = item_m0(tile), n0 = item_n0(tile);
+        const int kt0 = item_c0(tile) * kTilesPerChunk, kt1 = min(num_tiles, item_c1(tile) * kTilesPerChunk);
+        for (int kt = kt0; kt < kt1; ++kt, ++it) {
           const int s = it % kStages;
           const uint32_t round = it / kStages;
           if (round > 0 && !mbar_wait(&bars->empty[s], (round - 1) & 1, failed)) {
@@ -200,7 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       uint32_t it = 0, gc = 0;  // k-tiles and chunks consumed so far
       bool ok = true;
       for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
-        for (int c = 0; c < num_chunks && ok; ++c, ++gc) {
+        for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
           const int buf = gc & 1;
           const uint32_t use = gc >> 1;  // how often this accumulator was used before
           if (use > 0 && !mbar_wait(&bars->acc_empty[buf], (use - 1) & 1, failed)) {
@@ -233,34 +266,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   } else {
     // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
+    const int et = quarter * 32 + lane;  // 0..127: this thread's row of the tile
     float total[BN];
     uint32_t gc = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % m_blocks) * BM, n0 = (tile / m_blocks) * BN;
-      const int row = m0 + quarter * 32 + lane;
-      for (int c = 0; c < num_chunks && ok; ++c, ++gc) {
+      const int m0 = item_m0(tile), n0 = item_n0(tile);
+      const int row = m0 + et;
+      const int cols = min(BN, N - n0);
+      for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
         const int buf = gc & 1;
         if (!mbar_wait(&bars->acc_full[buf], (gc >> 1) & 1, failed)) {
           ok = false;
           break;
         }
         fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+        if (!SPLIT || quarter * 32 < M) {  // in split mode warps whose rows are all padding read nothing
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
 #pragma unroll
-        for (int g = 0; g < BN / 32; ++g) {
-          float v[32];
-          tmem_ld32(taddr + g * 32, v);
+          for (int g = 0; g < BN / 16; ++g) {
+            float v[16];
+            tmem_ld16(taddr + g * 16, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) total[g * 32 + j] = (c == 0) ? v[j] : total[g * 32 + j] + v[j];
+            for (int j = 0; j < 16; ++j)
+              total[g * 16 + j] = (SPLIT || c == 0) ? v[j] : total[g * 16 + j] + v[j];
+          }
         }
         fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
       }
-      if (!ok || row >= M) continue;
+      if (!ok) break;
+      if (SPLIT && num_chunks > 1) {
+        // this item's chunk sum goes to scratch; a second kernel adds the chunk sums in order
+        const int chunk = item_c0(tile);
+        if (row < M) {
+          float* mine = partials + (static_cast<size_t>(chunk) * M + row) * N + n0;
+          if (cols == BN && (N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < BN; j += 4)
+              __stcg(reinterpret_cast<float4*>(mine + j), make_float4(total[j], total[j + 1], total[j + 2], total[j + 3]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN; ++j)
+              if (j < cols) __stcg(mine + j, total[j]);
+          }
+        }
+        continue;
+      }
+      if (row >= M) continue;
       const size_t base = static_cast<size_t>(row) * N + n0;
-      const int cols = min(BN, N - n0);
       if (y_is_f32) {
         float* out = static_cast<float*>(Y) + base;
         const float* res = residual ? residual + base : nullptr;
@@ -357,8 +412,22 @@ BW_API int bw_bf16_linear_tc_failed() {
   return v;
 }
 
+// Scratch of split mode: chunk sums [chunks][m][n] float32 and one counter per column block.
+BW_API long long bw_bf16_linear_tc_scratch_floats(int m, int n, int k) {
+  return static_cast<long long>((k + kChunk - 1) / kChunk) * m * n;
+}
+BW_API int bw_bf16_linear_tc_counters(int n) { return (n + BN - 1) / BN; }
+
+// Split mode is chosen from the shape alone: one block of rows, more than one chunk, and too
+// few output tiles to occupy the machine. Both modes give the same bits.
+BW_API int bw_bf16_linear_tc_splits(int m, int n, int k) {
+  const int n_blocks = (n + BN - 1) / BN;
+  return m <= BM && k > kChunk && n_blocks < 100;
+}
+
 BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
-                             const float* residual, int m, int n, int k, cudaStream_t stream) {
+                             const float* residual, int m, int n, int k, float* partials, int* counters,
+                             cudaStream_t stream) {
   if (m <= 0 || n <= 0) return 0;
   if (!bw_bf16_linear_tc_usable(x, w, k)) {
     bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
@@ -380,7 +449,9 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
   constexpr int smem = kStages * kStageBytes + sizeof(Barriers) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
       bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
       return static_cast<int>(e);
@@ -394,8 +465,20 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const long long out_tiles = static_cast<long long>((n + BN - 1) / BN) * ((m + BM - 1) / BM);
-  const unsigned grid = static_cast<unsigned>(out_tiles < sm_count ? out_tiles : sm_count);
-  gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, g_error_flag);
+  const int n_blocks = (n + BN - 1) / BN, m_blocks = (m + BM - 1) / BM, chunks = (k + kChunk - 1) / kChunk;
+  const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
+  (void)counters;
+  const long long items = split ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
+  const unsigned grid = static_cast<unsigned>(items < sm_count ? items : sm_count);
+  if (split) {
+    gemm_tc_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, g_error_flag,
+                                                           partials);
+    const size_t outputs = static_cast<size_t>(m) * n;
+    reduce_chunks_kernel<<<static_cast<unsigned>((outputs + 255) / 256), 256, 0, stream>>>(partials, chunks, y, y_is_f32,
+                                                                                          residual, m, n);
+  } else {
+    gemm_tc_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, g_error_flag,
+                                                            nullptr);
+  }
   return bw::launch_status();
 }

@@ -39,7 +39,9 @@ rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __
 // ---------------------------------------------------------------------------------------
 // Rotary encoding (rotate-half pairs, src/kernels.cpp:273-289) in float32 on bfloat16
 // values, rounded once; then K and V of the row go into the paged cache
-// (src/model.cpp:285-297). With a null table nothing is rotated.
+// (src/model.cpp:285-297). With a null table nothing is rotated. One thread per pair of
+// elements: blockIdx.x is the row, blockIdx.y * blockDim.x + threadIdx.x the pair, first the
+// pairs of the query heads, then those of the key heads (which also carry the values).
 __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const int* __restrict__ pos,
                                        const int* __restrict__ row_seq, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, const int* __restrict__ block_table,
@@ -47,56 +49,80 @@ __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const
                                        int kv_heads, int hd, int page, int write_kv) {
   const int r = blockIdx.x;
   const int half = hd >> 1;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  const int q_items = heads * half, k_items = write_kv ? kv_heads * half : 0;
+  if (item >= q_items + k_items) return;
   const int p = pos[r];
   __nv_bfloat16* row = qkv + static_cast<size_t>(r) * row_stride;
-  const float* c = cos_t ? cos_t + static_cast<size_t>(p) * half : nullptr;
-  const float* s = sin_t ? sin_t + static_cast<size_t>(p) * half : nullptr;
-  if (c) {
-    const int q_items = heads * half;
-    for (int it = threadIdx.x; it < q_items; it += blockDim.x) {
-      const int h = it / half, i = it - h * half;
-      __nv_bfloat16* v = row + h * hd;
-      const float x1 = __bfloat162float(v[i]), x2 = __bfloat162float(v[i + half]);
-      v[i] = __float2bfloat16_rn(x1 * c[i] - x2 * s[i]);
-      v[i + half] = __float2bfloat16_rn(x2 * c[i] + x1 * s[i]);
-    }
+  const bool is_q = item < q_items;
+  const int local = is_q ? item : item - q_items;
+  const int h = local / half, i = local - h * half;
+  float c = 1.0f, s = 0.0f;
+  if (cos_t) {
+    c = cos_t[static_cast<size_t>(p) * half + i];
+    s = sin_t[static_cast<size_t>(p) * half + i];
   }
-  if (!write_kv) return;
+  if (is_q) {
+    if (!cos_t) return;
+    __nv_bfloat16* v = row + h * hd;
+    const float x1 = __bfloat162float(v[i]), x2 = __bfloat162float(v[i + half]);
+    v[i] = __float2bfloat16_rn(x1 * c - x2 * s);
+    v[i + half] = __float2bfloat16_rn(x2 * c + x1 * s);
+    return;
+  }
   const int blk = block_table[static_cast<size_t>(row_seq[r]) * max_blocks + p / page];
   const int slot = p % page;
-  const __nv_bfloat16* k = row + heads * hd;
+  const __nv_bfloat16* k = row + heads * hd + h * hd;
   const __nv_bfloat16* vv = k + kv_heads * hd;
-  const int k_items = kv_heads * half;
-  for (int it = threadIdx.x; it < k_items; it += blockDim.x) {
-    const int h = it / half, i = it - h * half;
-    const size_t dst = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd;
-    const float x1 = __bfloat162float(k[h * hd + i]), x2 = __bfloat162float(k[h * hd + i + half]);
-    if (c) {
-      kcache[dst + i] = __float2bfloat16_rn(x1 * c[i] - x2 * s[i]);
-      kcache[dst + i + half] = __float2bfloat16_rn(x2 * c[i] + x1 * s[i]);
-    } else {
-      kcache[dst + i] = k[h * hd + i];
-      kcache[dst + i + half] = k[h * hd + i + half];
-    }
-    vcache[dst + i] = vv[h * hd + i];
-    vcache[dst + i + half] = vv[h * hd + i + half];
+  const size_t dst = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd;
+  if (cos_t) {
+    const float x1 = __bfloat162float(k[i]), x2 = __bfloat162float(k[i + half]);
+    kcache[dst + i] = __float2bfloat16_rn(x1 * c - x2 * s);
+    kcache[dst + i + half] = __float2bfloat16_rn(x2 * c + x1 * s);
+  } else {
+    kcache[dst + i] = k[i];
+    kcache[dst + i + half] = k[i + half];
   }
+  vcache[dst + i] = vv[i];
+  vcache[dst + i + half] = vv[i + half];
 }
 
 // ---------------------------------------------------------------------------------------
 // SwiGLU on rows laid out [gate | up]: h = (g * sigmoid(g)) * u in float32 (src/kernels.cpp:291-298).
-__global__ void swiglu_bf16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                   int n, int inter) {
-  const size_t total = static_cast<size_t>(n) * inter;
-  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t r = idx / inter;
-    const int i = static_cast<int>(idx - r * inter);
-    const float g = __bfloat162float(gate_up[r * 2 * inter + i]);
-    const float u = __bfloat162float(gate_up[r * 2 * inter + inter + i]);
-    const float sig = 1.0f / (1.0f + bw::det_expf(-g));
-    out[idx] = __float2bfloat16_rn((g * sig) * u);
+// blockIdx.y is the row; a thread handles 8 consecutive columns when the row width allows
+// 16-byte accesses, else one column.
+__device__ __forceinline__ float swiglu_one(float g, float u) {
+  const float sig = 1.0f / (1.0f + bw::det_expf(-g));
+  return (g * sig) * u;
+}
+
+__global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                       int inter) {
+  const int r = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= inter) return;
+  const __nv_bfloat16* g = gate_up + static_cast<size_t>(r) * 2 * inter + c;
+  const uint4 gv = *reinterpret_cast<const uint4*>(g);
+  const uint4 uv = *reinterpret_cast<const uint4*>(g + inter);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
+    o[e] = __floats2bfloat162_rn(swiglu_one(gf.x, uf.x), swiglu_one(gf.y, uf.y));
   }
+  *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * inter + c) = *reinterpret_cast<const uint4*>(o);
+}
+
+__global__ void swiglu_bf16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                   int inter) {
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= inter) return;
+  const __nv_bfloat16* g = gate_up + static_cast<size_t>(r) * 2 * inter + c;
+  out[static_cast<size_t>(r) * inter + c] =
+      __float2bfloat16_rn(swiglu_one(__bfloat162float(g[0]), __bfloat162float(g[inter])));
 }
 
 }  // namespace
@@ -121,15 +147,39 @@ BW_API int bw_bf16_rope_cache(__nv_bfloat16* qkv, int row_stride, const int* pos
     bw::set_error("rope: head size %d is odd", hd);
     return -1;
   }
-  rope_cache_bf16_kernel<<<n, 128, 0, stream>>>(qkv, row_stride, pos, row_seq, cos_t, sin_t, block_table, max_blocks,
-                                                kcache, vcache, heads, kv_heads, hd, page, write_kv);
+  const int items = (heads + (write_kv ? kv_heads : 0)) * (hd / 2);
+  const int threads = 256;
+  dim3 grid(n, (items + threads - 1) / threads);
+  if (grid.y > 65535u) {
+    bw::set_error("rope: %d heads exceed the grid limit", heads);
+    return -1;
+  }
+  rope_cache_bf16_kernel<<<grid, threads, 0, stream>>>(qkv, row_stride, pos, row_seq, cos_t, sin_t, block_table,
+                                                       max_blocks, kcache, vcache, heads, kv_heads, hd, page, write_kv);
   return bw::launch_status();
 }
 
 BW_API int bw_bf16_swiglu(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int n, int inter, cudaStream_t stream) {
   if (n <= 0 || inter <= 0) return 0;
-  const size_t total = static_cast<size_t>(n) * inter;
-  const unsigned blocks = static_cast<unsigned>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
-  swiglu_bf16_kernel<<<blocks, 256, 0, stream>>>(gate_up, out, n, inter);
+  if (n > 65535) {  // rows ride on blockIdx.y; split very tall inputs
+    for (int r = 0; r < n; r += 65535) {
+      const int cnt = n - r < 65535 ? n - r : 65535;
+      const int rc = bw_bf16_swiglu(gate_up + static_cast<size_t>(r) * 2 * inter, out + static_cast<size_t>(r) * inter,
+                                    cnt, inter, stream);
+      if (rc) return rc;
+    }
+    return 0;
+  }
+  const bool vec = inter % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  if (vec) {
+    const int threads = 128;
+    dim3 grid((inter / 8 + threads - 1) / threads, n);
+    swiglu_bf16_vec_kernel<<<grid, threads, 0, stream>>>(gate_up, out, inter);
+  } else {
+    const int threads = 256;
+    dim3 grid((inter + threads - 1) / threads, n);
+    swiglu_bf16_kernel<<<grid, threads, 0, stream>>>(gate_up, out, inter);
+  }
   return bw::launch_status();
 }

@@ -85,7 +85,7 @@ class Stepper:
     """Owns the step's device buffers and runs steps for one model and one cache."""
 
     GRAPH_MAX_ROWS = 256   # steps up to this many rows are replayed as CUDA graphs
-    GRAPH_CACHE = 64       # graphs kept (one per batch shape)
+    GRAPH_CACHE = 256      # graphs kept (one per batch shape and context length in steps of 256)
 
     def __init__(self, model, manager: CacheManager, storage: CacheStorage, ops, max_rows: int,
                  max_seqs: int, max_tokens_per_request: int, use_graphs: Optional[bool] = None):
@@ -227,7 +227,10 @@ class Stepper:
         views = self.storage.views(ctx.block_tables, ctx.seq_slot)
         key = None
         if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:
-            key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows) + tuple(t[3] for t in ctx.tile_sets.values())
+            # the longest context enters in steps of 256 keys: the attention kernel of a decode
+            # step launches one thread block per chunk of 256 keys
+            key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows, (ctx.max_keys + 255) // 256) + tuple(
+                t[3] for t in ctx.tile_sets.values())
         if key is not None and key in self._graphs:
             graph, logits, launches = self._graphs[key]
             graph.replay()

@@ -61,6 +61,7 @@ class KernelOps:
         self._partials: Optional[torch.Tensor] = None  # scratch of the split products (bfloat16 path)
         self._counters: Optional[torch.Tensor] = None
         self._retired = []
+        self._attn_scratch: Optional[torch.Tensor] = None
         if self.kind == "bf16":
             self.lib.bw_bf16_linear_scratch_floats.restype = ctypes.c_longlong
             self._split_rows = int(self.lib.bw_bf16_linear_split_rows())
@@ -127,7 +128,7 @@ class KernelOps:
                    _c_float(eps), self._stream())
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-               residual: Optional[torch.Tensor] = None) -> None:
+               residual: Optional[torch.Tensor] = None, legacy: bool = False) -> None:
         """out = x @ w.T (+ residual).  x [M,K] and w [N,K] in act_dtype; out act_dtype or
         float32; with a float32 residual the sum is formed in 32-bit (out float32, may alias)."""
         m, k = x.shape
@@ -153,15 +154,18 @@ class KernelOps:
             if m <= self._split_rows:
                 partials, counters = self._linear_scratch(x.device, n, k)
             self._call("bw_bf16_linear", _p(x), _p(w), _p(out), _c_int(int(out.dtype == torch.float32)),
-                       _p(residual), _c_int(m), _c_int(n), _c_int(k), _p(partials), _p(counters), self._stream())
+                       _p(residual), _c_int(m), _c_int(n), _c_int(k), _p(partials), _p(counters),
+                       _c_int(int(legacy)), self._stream())
 
     def _linear_scratch(self, device, n: int, k: int):
         """Scratch of a product that is split along k: chunk sums for up to ``_split_rows``
         rows, and one counter per output tile (zero between launches).  It grows when a
         larger product appears and is otherwise reused by every product of the stream."""
-        floats = int(self.lib.bw_bf16_linear_scratch_floats(_c_int(self._split_rows), _c_int(n), _c_int(k)))
+        # sized for the largest batch that may be split, so that the address stays the same
+        floats = max(int(self.lib.bw_bf16_linear_scratch_floats(_c_int(r), _c_int(n), _c_int(k)))
+                     for r in (64, self._split_rows))
         tiles = int(self.lib.bw_bf16_linear_counters(_c_int(n)))
-        if self._partials is None or self._partials.numel() < floats:
+        if floats and (self._partials is None or self._partials.numel() < floats):
             self._retired.append(self._partials)  # a captured graph may still point at the old one
             self._partials = torch.empty(floats, dtype=torch.float32, device=device)
         if self._counters is None or self._counters.numel() < tiles:
@@ -182,6 +186,17 @@ class KernelOps:
         if self.kind == "f32":
             return 16
         return max(1, 64 // max(1, heads // kv_heads))
+
+    def _attention_scratch(self, lib, device, n: int, heads: int, max_keys: int) -> torch.Tensor:
+        """Scratch of the split attention: one (output, maximum, sum) record per row, head and
+        chunk of 256 keys.  Sized for contexts rounded up to 2048 keys so that it seldom grows."""
+        lib.bw_bf16_attention_scratch_floats.restype = ctypes.c_longlong
+        keys = (max_keys + 2047) // 2048 * 2048
+        floats = int(lib.bw_bf16_attention_scratch_floats(_c_int(n), _c_int(heads), _c_int(keys)))
+        if self._attn_scratch is None or self._attn_scratch.numel() < floats:
+            self._retired.append(self._attn_scratch)  # a captured graph may still point at the old one
+            self._attn_scratch = torch.empty(floats, dtype=torch.float32, device=device)
+        return self._attn_scratch
 
     def _attention_lib(self, head_dim: int):
         lib = self._attn_libs.get(head_dim)
@@ -253,17 +268,21 @@ class KernelOps:
                 raise KernelError(f"attention (bfloat16): head size {head_dim} is not a multiple of 16 up to 256")
             lib = self._attention_lib(head_dim)
             t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.attention_tile_rows(heads, kv_heads))
+            scratch = None
+            split = t_count == n and max_keys > 256  # a decode step: one chunk of keys per thread block
+            if split:
+                scratch = self._attention_scratch(lib, qkv.device, n, heads, max_keys)
             fn = lib.bw_bf16_attention
             fn.restype = _c_int
             rc = fn(_p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
                     _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
-                    _p(batch.seq_pos0), _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(n), _c_int(heads),
-                    _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale),
-                    self._stream())
+                    _p(batch.seq_pos0), _p(batch.seq_row0), _p(pos), _p(out), _c_int(out.shape[1]), _c_int(n),
+                    _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale),
+                    _c_int(max_keys), _p(scratch), self._stream())
             if rc != 0:
                 raise KernelError(f"bw_bf16_attention failed ({rc}): "
                                   + lib.bw_last_error().decode("utf-8", "replace"))
-            self.launches += 1
+            self.launches += 2 if split else 1
 
     def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         """out = silu(gate) * up for rows laid out [gate | up]."""

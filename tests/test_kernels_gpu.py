@@ -257,6 +257,24 @@ def test_bf16_linear_row_bits_do_not_depend_on_the_batch():
             assert_same_bits(part.cpu().numpy(), full[rows[0]:rows[1]].cpu().numpy(), f"rows {rows} of [{n}x{k}]")
 
 
+def test_bf16_linear_tensor_core_generations_agree_bit_for_bit():
+    """The tcgen05 kernel (whole and split mode) and the legacy mma.sync tile implement the
+    same summation order: equal bits for the same rows."""
+    rng = np.random.default_rng(14)
+    ops = _ops("bfloat16")
+    for m, n, k in ((8, 2048, 2048), (1, 6144, 2048), (64, 2048, 8192), (100, 320, 1536), (128, 16384, 512),
+                    (300, 200, 1032), (17, 136, 520)):
+        x, w = bf(rnd(rng, m, k)), bf(rnd(rng, n, k, scale=0.05))
+        res = rnd(rng, m, n)
+        a, b = t(res).clone(), t(res).clone()
+        ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), a, residual=a)
+        ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), b, residual=b, legacy=True)
+        assert_same_bits(a.cpu().numpy(), b.cpu().numpy(), f"[{m}x{k}] x [{n}x{k}]")
+        want = res + x.astype(np.float64) @ w.astype(np.float64).T
+        assert np.abs(a.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
+    assert not ops.device_failure()
+
+
 def test_bf16_rmsnorm_and_swiglu():
     """Tolerance: one bfloat16 rounding of a float32 result (2^-8 relative) plus 1e-6 absolute."""
     rng = np.random.default_rng(9)
@@ -368,6 +386,30 @@ def test_bf16_attention_row_bits_do_not_depend_on_the_tile():
         assert_same_bits(one[0], full[p], f"position {p}")
     part, _, _ = _run_bf16_attention(q[100:171], [(100, 71)], k, v, table, heads, kv_heads, hd, 0)
     assert_same_bits(part, full[100:171], "portion 100..170")
+
+
+def test_bf16_attention_decode_rows_split_over_chunks_give_the_same_bits():
+    """Decode rows of long contexts run one chunk of 256 keys per thread block plus a merge
+    kernel; prefill portions walk the chunks inside one block.  Same order, same bits; also
+    with a window, and for several sequences of different lengths in one step."""
+    rng = np.random.default_rng(15)
+    for heads, kv_heads, hd, page, window in ((4, 2, 64, 16, 0), (3, 3, 32, 16, 300), (8, 2, 128, 32, 0)):
+        lens = [700, 257, 1030]
+        k, v, table, _, _ = _paged(rng, lens, kv_heads, hd, page)
+        k, v = bf(k), bf(v)
+        qs = [bf(rnd(rng, n, heads, hd)) for n in lens]
+        for s, n in enumerate(lens):
+            tab = table[s:s + 1]
+            full, _, _ = _run_bf16_attention(qs[s], [(0, n)], k, v, tab, heads, kv_heads, hd, window)
+            for p in (n - 1, 256, 255, 600 if n > 600 else 100):
+                one, _, _ = _run_bf16_attention(qs[s][p:p + 1], [(p, 1)], k, v, tab, heads, kv_heads, hd, window)
+                assert_same_bits(one[0], full[p], f"heads {heads}/{kv_heads} hd {hd} window {window} seq {s} pos {p}")
+        # all three sequences decode together
+        q3 = np.stack([qs[s][lens[s] - 1] for s in range(3)])
+        got, _, _ = _run_bf16_attention(q3, [(lens[s] - 1, 1) for s in range(3)], k, v, table, heads, kv_heads, hd, window)
+        for s in range(3):
+            alone, _, _ = _run_bf16_attention(q3[s:s + 1], [(lens[s] - 1, 1)], k, v, table[s:s + 1], heads, kv_heads, hd, window)
+            assert_same_bits(got[s], alone[0], f"sequence {s} in a batch of three")
 
 
 def test_bf16_rope_and_cache_write():
