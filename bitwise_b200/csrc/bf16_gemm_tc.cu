@@ -482,3 +482,106 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
   }
   return bw::launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared in bw_noalloc.h, which says whom it is
+// for).  Same kernels as above; the scratch of split mode and the word that bounded waits
+// raise live in file-scope device arrays instead of memory from cudaMalloc.
+#include "bw_noalloc.h"
+
+namespace {
+
+// In host code these names are stand-ins, not device addresses: the address that a kernel
+// may use comes from cudaGetSymbolAddress, once per device (below).
+static __device__ __align__(256) float g_noalloc_scratch[BW_NOALLOC_MAX_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_noalloc_error[64];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
+int* g_noalloc_error_ptr[kMaxDevices] = {nullptr};
+
+}  // namespace
+
+BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
+                                  const float* residual, int m, int n, int k, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (k <= 0) {
+    bw::set_error("linear (no allocation): inner size %d", k);
+    return -1;
+  }
+  if (!bw_bf16_linear_tc_usable(x, w, k)) {
+    bw::set_error("linear (no allocation): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
+    return -1;
+  }
+  if (residual && !y_is_f32) {
+    bw::set_error("linear (no allocation): a residual needs a float32 output");
+    return -1;
+  }
+  const int chunks = (k + kChunk - 1) / kChunk;
+  const bool split = bw_bf16_linear_tc_splits(m, n, k) != 0;
+  const long long need = split ? static_cast<long long>(chunks) * m * n : 0;
+  if (need > BW_NOALLOC_MAX_SCRATCH_FLOATS) {
+    bw::set_error("linear (no allocation): [%d x %d] x [%d x %d] needs %lld floats of scratch, the library holds %d",
+                  m, k, n, k, need, BW_NOALLOC_MAX_SCRATCH_FLOATS);
+    return -2;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    bw::set_error("linear (no allocation): cannot use device %d: %s", dev, cudaGetErrorString(e));
+    return e != cudaSuccess ? static_cast<int>(e) : -1;
+  }
+  constexpr int smem = kStages * kStageBytes + sizeof(Barriers) + 1024;
+  if (!g_noalloc_scratch_ptr[dev]) {
+    // set-up, once per device, with that device current
+    float* sp = nullptr;
+    int* ep = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&sp), g_noalloc_scratch);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ep), g_noalloc_error);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      bw::set_error("linear (no allocation): set-up on device %d failed: %s", dev, cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    g_noalloc_error_ptr[dev] = ep;  // the array is zero when the library is loaded; kernels only ever set word 0
+    g_noalloc_scratch_ptr[dev] = sp;
+  }
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  int* error_word = g_noalloc_error_ptr[dev];
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, x, m, k) || !make_map(&map_w, w, n, k)) {
+    bw::set_error("linear (no allocation): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
+    return -1;
+  }
+  int sm_count = 0;
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (sm_count <= 0) sm_count = 148;
+  const int n_blocks = (n + BN - 1) / BN, m_blocks = (m + BM - 1) / BM;
+  const long long items = split ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
+  const unsigned grid = static_cast<unsigned>(items < sm_count ? items : sm_count);
+  if (split) {
+    // nothing in the scratch has to start at zero: every chunk sum that the second kernel
+    // reads is written by the first one in this same call
+    gemm_tc_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, error_word,
+                                                           scratch);
+    const size_t outputs = static_cast<size_t>(m) * n;
+    reduce_chunks_kernel<<<static_cast<unsigned>((outputs + 255) / 256), 256, 0, stream>>>(scratch, chunks, y, y_is_f32,
+                                                                                          residual, m, n);
+  } else {
+    gemm_tc_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, error_word,
+                                                            nullptr);
+  }
+  return bw::launch_status();
+}
+
+// Reads and clears the word that a kernel launched by bw_bf16_linear_noalloc raises when one
+// of its bounded waits ran out (a copy of four bytes; nothing is allocated).
+BW_API int bw_bf16_linear_noalloc_failed() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || !g_noalloc_error_ptr[dev]) return 0;
+  int v = 0;
+  cudaMemcpy(&v, g_noalloc_error_ptr[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(g_noalloc_error_ptr[dev], 0, sizeof(int));
+  return v;
+}
