@@ -6,18 +6,18 @@
 // (src/kernels.cpp:346: kv head = h / (heads / kv_heads)) are stacked with the rows, so the
 // tile's keys and values are read once for the whole group.
 //
-// One summation order for every shape. Keys are cut into chunks of 256 at fixed absolute
-// positions. Inside a chunk the keys are walked in tiles of 64 with a running maximum and
-// running sum per query row (scores, maximum, sum and the output accumulator in float32; the
-// softmax weights are rounded to bfloat16 for the value product). The chunk results
-// (maximum, sum, unnormalised output) are merged in ascending chunk order by one written-down
-// formula (merge_state below). A prefill portion walks its chunks inside one block; a decode
-// step, which has few query rows and long contexts, gives every chunk to a block of its own
-// (so that the cache streams from all SMs) and a second kernel merges the stored chunk
-// results in the same order. A row's arithmetic depends only on its own query, its position
-// and the cached keys: tiles and chunks that lie wholly outside a row's range leave its state
-// untouched bit for bit, so the result does not depend on which other rows share the block,
-// on how the prompt was cut, on the batch, or on which pages hold the keys.
+// One summation order for every shape. Keys are cut into tiles of 64 at fixed absolute
+// positions [64 t, 64 t + 64). Each tile gives, per query row, the maximum of its scores, the
+// sum of exp(score - maximum) and the unnormalised output sum(exp(...) v) (scores, maximum,
+// sum and output in float32; the weights are rounded to bfloat16 for the value product). The
+// tile results are merged in ascending tile order by one written-down formula (merge_weights
+// / merge_value below). A prefill portion walks its tiles inside one block; a decode step,
+// which has few query rows and long contexts, gives every tile to a warp of its own, four
+// tiles to a block (so that the cache streams from all SMs), and a second kernel merges the
+// stored tile results in the same order. A row's arithmetic depends only on its own query,
+// its position and the cached keys: tiles that lie wholly outside a row's range merge as an
+// exact no-op, so the result does not depend on which other rows share the block, on how the
+// prompt was cut, on the batch, or on which pages hold the keys.
 #include "bw_common.cuh"
 
 #ifndef BW_HEAD_DIM
@@ -30,8 +30,7 @@ constexpr int HD = BW_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int kTileM = 64;    // stacked (query row, head of the group) rows per block
 constexpr int kTileKV = 64;   // keys per tile
-constexpr int kChunkKV = 256; // keys per chunk of the summation order
-static_assert(kChunkKV % kTileKV == 0, "a chunk is a whole number of tiles");
+constexpr int kSplitWarps = 4; // key tiles per block in split mode, one per warp
 constexpr int kThreads = 128;
 constexpr int kRowElems = HD + 8;           // padded row: 16 bytes of padding keep ldmatrix conflict-free
 constexpr int kRowBytes = kRowElems * 2;
@@ -72,7 +71,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Merge of a chunk result (m, l, o) into the running state (M, L, O): the new maximum, both
+// Merge of a tile result (m, l, o) into the running state (M, L, O): the new maximum, both
 // sides rescaled to it. Maxima are in the base-2 exponent domain. A side that has seen no key
 // (maximum -inf) gets weight 0 through a zero reference instead of inf - inf.
 struct MergeWeights {
@@ -90,18 +89,124 @@ __device__ __forceinline__ float merge_value(float X, float x, const MergeWeight
   return __fmaf_rn(x, w.b, __fmul_rn(X, w.a));
 }
 
-// STAGES key/value tiles are in flight or in use at a time: two for prefill portions (more
-// blocks per SM), four for decode steps, where a block has little arithmetic per tile and
-// the time goes to waiting for memory. The arithmetic does not depend on STAGES.
-template <int STAGES, bool SPLIT>
+// What one warp holds of a tile result: rows lane / 4 ("lo") and lane / 4 + 8 ("hi") of its 16
+// stacked rows; o[i][0..1] are columns 8 i + 2 (lane % 4) + {0, 1} of row lo, o[i][2..3] of row hi.
+struct TileResult {
+  float o[HD / 8][4];
+  float max_lo, max_hi, sum_lo, sum_hi;
+};
+
+// One tile of 64 keys for the 16 stacked rows of one warp: S = Q K^T (scaled to the base-2
+// domain), mask, maximum, weights, sum, o = P V from zero. sq points at the warp's 16 rows of
+// Q, sk / sv at the tile's keys and values in shared memory (padded rows of kRowBytes).
+// Both modes call this one function, so a tile gives the same bits in both.
+__device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsigned char* sk, const unsigned char* sv,
+                                            int lane, int j0, int pos_lo, int pos_hi, int first_lo, int first_hi,
+                                            float scale_log2, TileResult& r) {
+  float s[kTileKV / 8][4];
+#pragma unroll
+  for (int i = 0; i < kTileKV / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[i][e] = 0.0f;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+    uint32_t a[4];
+    {
+      const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(a, smem_u32(sq + row * kRowBytes + (kk * 2 + (lane >> 4)) * 16));
+    }
+#pragma unroll
+    for (int np = 0; np < kTileKV / 16; ++np) {
+      uint32_t b[4];
+      const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
+      ldmatrix_x4(b, smem_u32(sk + key * kRowBytes + (kk * 2 + ((lane >> 3) & 1)) * 16));
+      mma_bf16(s[2 * np], a, b[0], b[1]);
+      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+  float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+#pragma unroll
+  for (int nb = 0; nb < kTileKV / 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+      const bool hi = e >= 2;
+      const bool ok = hi ? (j <= pos_hi && j >= first_hi) : (j <= pos_lo && j >= first_lo);
+      const float v = ok ? __fmul_rn(s[nb][e], scale_log2) : -INFINITY;
+      s[nb][e] = v;
+      if (hi) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
+    }
+  tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
+  tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
+  tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
+  tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
+  // a row with no key in this tile keeps a zero reference so that exp2(-inf - ref) = 0
+  const float ref_lo = (tmax_lo == -INFINITY) ? 0.0f : tmax_lo;
+  const float ref_hi = (tmax_hi == -INFINITY) ? 0.0f : tmax_hi;
+  float tsum_lo = 0.0f, tsum_hi = 0.0f;
+  uint32_t p[kTileKV / 16][4];
+#pragma unroll
+  for (int nb = 0; nb < kTileKV / 8; ++nb) {
+    const float e0 = exp2f(__fsub_rn(s[nb][0], ref_lo)), e1 = exp2f(__fsub_rn(s[nb][1], ref_lo));
+    const float e2 = exp2f(__fsub_rn(s[nb][2], ref_hi)), e3 = exp2f(__fsub_rn(s[nb][3], ref_hi));
+    tsum_lo = __fadd_rn(tsum_lo, __fadd_rn(e0, e1));
+    tsum_hi = __fadd_rn(tsum_hi, __fadd_rn(e2, e3));
+    p[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16(e0, e1);
+    p[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16(e2, e3);
+  }
+  tsum_lo = __fadd_rn(tsum_lo, __shfl_xor_sync(0xffffffffu, tsum_lo, 1));
+  tsum_lo = __fadd_rn(tsum_lo, __shfl_xor_sync(0xffffffffu, tsum_lo, 2));
+  tsum_hi = __fadd_rn(tsum_hi, __shfl_xor_sync(0xffffffffu, tsum_hi, 1));
+  tsum_hi = __fadd_rn(tsum_hi, __shfl_xor_sync(0xffffffffu, tsum_hi, 2));
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r.o[i][e] = 0.0f;
+#pragma unroll
+  for (int kp = 0; kp < kTileKV / 16; ++kp) {
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b[4];
+      const int key = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4_trans(b, smem_u32(sv + key * kRowBytes + (dp * 2 + (lane >> 4)) * 16));
+      mma_bf16(r.o[2 * dp], p[kp], b[0], b[1]);
+      mma_bf16(r.o[2 * dp + 1], p[kp], b[2], b[3]);
+    }
+  }
+  r.max_lo = tmax_lo;
+  r.max_hi = tmax_hi;
+  r.sum_lo = tsum_lo;
+  r.sum_hi = tsum_hi;
+}
+
+// cp.async of `count` threads: one tile of keys and values from the paged cache into shared
+// memory; keys at or beyond kv_hi are zero-filled.
+__device__ __forceinline__ void load_kv_tile(unsigned char* sk, unsigned char* sv, const __nv_bfloat16* kcache,
+                                             const __nv_bfloat16* vcache, const int* table, int page, int kv_heads, int g,
+                                             int j0, int kv_hi, int t, int count) {
+  for (int idx = t; idx < kTileKV * kPieces; idx += count) {
+    const int key = idx / kPieces, piece = idx - key * kPieces;
+    const int j = j0 + key;
+    const bool ok = j < kv_hi;
+    size_t off = 0;
+    if (ok) off = ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + (j % page)) * HD + piece * 8;
+    cp_async16(smem_u32(sk + key * kRowBytes + piece * 16), kcache + off, ok);
+    cp_async16(smem_u32(sv + key * kRowBytes + piece * 16), vcache + off, ok);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Whole mode: a block takes a tile of up to 64 stacked rows (query rows of one sequence x the
+// heads of one group) and walks the key tiles in order, two tiles of keys in flight.
+constexpr int kStages = 2;
+
 __global__ void __launch_bounds__(kThreads)
-attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const __nv_bfloat16* __restrict__ kcache,
-                      const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
-                      const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
-                      const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
-                      const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
-                      int kv_heads, int page, int window, float scale_log2, float* __restrict__ chunk_out,
-                      int max_chunks) {
+attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const __nv_bfloat16* __restrict__ kcache,
+                       const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
+                       const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
+                       const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
+                       const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
+                       int kv_heads, int page, int window, float scale_log2) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sq = smem;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -113,19 +218,7 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const
   const int p_last = p_first + nrows - 1;
   const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
 
-  // keys [kv_lo, kv_hi) are walked; kv_lo is a multiple of the tile size, in split mode the
-  // range is cut to this block's chunk
-  int kv_lo = (window > 0 && p_first - window + 1 > 0) ? ((p_first - window + 1) / kTileKV) * kTileKV : 0;
-  int kv_hi = p_last + 1;
-  if (SPLIT) {
-    const int c = blockIdx.z;
-    kv_lo = max(kv_lo, c * kChunkKV);
-    kv_hi = min(kv_hi, (c + 1) * kChunkKV);
-    if (kv_hi <= kv_lo) return;  // this chunk lies outside the tile's range: nothing is stored for it
-  }
-  const int ntiles = (kv_hi - kv_lo + kTileKV - 1) / kTileKV;
-
-  // ---- stage Q: stacked row m = (query row m / group, head g * group + m % group) ----------
+  // stacked row m = (query row m / group, head g * group + m % group)
   for (int idx = tid; idx < kTileM * kPieces; idx += kThreads) {
     const int m = idx / kPieces, piece = idx - m * kPieces;
     const bool ok = m < mrows;
@@ -135,28 +228,14 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const
   }
   cp_async_commit();
 
-  auto load_kv = [&](int stage, int t) {
-    unsigned char* sk = smem + kQBytes + stage * 2 * kKVBytes;
-    unsigned char* sv = sk + kKVBytes;
-    const int j0 = kv_lo + t * kTileKV;
-    for (int idx = tid; idx < kTileKV * kPieces; idx += kThreads) {
-      const int key = idx / kPieces, piece = idx - key * kPieces;
-      const int j = j0 + key;
-      const bool ok = j < kv_hi;
-      size_t off = 0;
-      if (ok) off = ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + (j % page)) * HD + piece * 8;
-      cp_async16(smem_u32(sk + key * kRowBytes + piece * 16), kcache + off, ok);
-      cp_async16(smem_u32(sv + key * kRowBytes + piece * 16), vcache + off, ok);
-    }
-  };
+  const int kv_lo = (window > 0 && p_first - window + 1 > 0) ? ((p_first - window + 1) / kTileKV) * kTileKV : 0;
+  const int kv_hi = p_last + 1;  // keys [kv_lo, kv_hi) are walked
+  const int ntiles = (kv_hi - kv_lo + kTileKV - 1) / kTileKV;
+  auto stage_k = [&](int st) { return smem + kQBytes + st * 2 * kKVBytes; };
 
-#pragma unroll
-  for (int st = 0; st < STAGES - 1; ++st) {
-    if (st < ntiles) load_kv(st, st);
-    cp_async_commit();
-  }
+  load_kv_tile(stage_k(0), stage_k(0) + kKVBytes, kcache, vcache, table, page, kv_heads, g, kv_lo, kv_hi, tid, kThreads);
+  cp_async_commit();
 
-  // per-thread rows of the warp's 16-row slice: r_lo = lane / 4, r_hi = r_lo + 8
   const int m_lo = warp * 16 + (lane >> 2), m_hi = m_lo + 8;
   const int pos_lo = (m_lo < mrows) ? p_first + m_lo / group : p_last;
   const int pos_hi = (m_hi < mrows) ? p_first + m_hi / group : p_last;
@@ -164,163 +243,42 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const
   const int first_hi = (window > 0 && pos_hi - window + 1 > 0) ? pos_hi - window + 1 : 0;
   const bool warp_active = warp * 16 < mrows;
 
-  float o_acc[HD / 8][4];
+  float o_tot[HD / 8][4];
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o_acc[i][e] = 0.0f;
-  float max_lo = -INFINITY, max_hi = -INFINITY, sum_lo = 0.0f, sum_hi = 0.0f;
-  // running state over the chunks (whole mode only)
-  float o_tot[SPLIT ? 1 : HD / 8][4];
-  float Mt_lo = -INFINITY, Mt_hi = -INFINITY, Lt_lo = 0.0f, Lt_hi = 0.0f;
-  if (!SPLIT) {
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o_tot[i][e] = 0.0f;
-  }
+    for (int e = 0; e < 4; ++e) o_tot[i][e] = 0.0f;
+  float M_lo = -INFINITY, M_hi = -INFINITY, L_lo = 0.0f, L_hi = 0.0f;
 
   for (int t = 0; t < ntiles; ++t) {
-    if (t + STAGES - 1 < ntiles) load_kv((t + STAGES - 1) % STAGES, t + STAGES - 1);
+    if (t + 1 < ntiles)
+      load_kv_tile(stage_k((t + 1) & 1), stage_k((t + 1) & 1) + kKVBytes, kcache, vcache, table, page, kv_heads, g,
+                   kv_lo + (t + 1) * kTileKV, kv_hi, tid, kThreads);
     cp_async_commit();
-    cp_async_wait<STAGES - 1>();
+    cp_async_wait<1>();
     __syncthreads();
     if (warp_active) {
-      const unsigned char* sk = smem + kQBytes + (t % STAGES) * 2 * kKVBytes;
-      const unsigned char* sv = sk + kKVBytes;
-      const int j0 = kv_lo + t * kTileKV;
-
-      // ---- S = Q K^T for 16 stacked rows x 64 keys ------------------------------------------
-      float s[kTileKV / 8][4];
-#pragma unroll
-      for (int i = 0; i < kTileKV / 8; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s[i][e] = 0.0f;
-#pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk) {
-        uint32_t a[4];
-        {
-          const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-          ldmatrix_x4(a, smem_u32(sq + row * kRowBytes + (kk * 2 + (lane >> 4)) * 16));
-        }
-#pragma unroll
-        for (int np = 0; np < kTileKV / 16; ++np) {
-          uint32_t b[4];
-          const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
-          ldmatrix_x4(b, smem_u32(sk + key * kRowBytes + (kk * 2 + ((lane >> 3) & 1)) * 16));
-          mma_bf16(s[2 * np], a, b[0], b[1]);
-          mma_bf16(s[2 * np + 1], a, b[2], b[3]);
-        }
-      }
-
-      // ---- mask, running maximum ---------------------------------------------------------------
-      float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
-#pragma unroll
-      for (int nb = 0; nb < kTileKV / 8; ++nb)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1);
-          const bool hi = e >= 2;
-          const bool ok = hi ? (j <= pos_hi && j >= first_hi) : (j <= pos_lo && j >= first_lo);
-          const float v = ok ? s[nb][e] * scale_log2 : -INFINITY;
-          s[nb][e] = v;
-          if (hi) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
-        }
-      tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
-      tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
-      tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
-      tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
-      const float new_lo = fmaxf(max_lo, tmax_lo), new_hi = fmaxf(max_hi, tmax_hi);
-      // a row that has seen no key yet keeps a zero reference so that exp2(-inf - ref) = 0
-      const float ref_lo = (new_lo == -INFINITY) ? 0.0f : new_lo;
-      const float ref_hi = (new_hi == -INFINITY) ? 0.0f : new_hi;
-      const float alpha_lo = exp2f(max_lo - ref_lo), alpha_hi = exp2f(max_hi - ref_hi);
-      max_lo = new_lo;
-      max_hi = new_hi;
-
-      // ---- weights, running sum, P as the A operand ---------------------------------------------
-      float tsum_lo = 0.0f, tsum_hi = 0.0f;
-      uint32_t p[kTileKV / 16][4];
-#pragma unroll
-      for (int nb = 0; nb < kTileKV / 8; ++nb) {
-        const float e0 = exp2f(s[nb][0] - ref_lo), e1 = exp2f(s[nb][1] - ref_lo);
-        const float e2 = exp2f(s[nb][2] - ref_hi), e3 = exp2f(s[nb][3] - ref_hi);
-        tsum_lo += e0 + e1;
-        tsum_hi += e2 + e3;
-        p[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16(e0, e1);
-        p[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16(e2, e3);
-      }
-      tsum_lo += __shfl_xor_sync(0xffffffffu, tsum_lo, 1);
-      tsum_lo += __shfl_xor_sync(0xffffffffu, tsum_lo, 2);
-      tsum_hi += __shfl_xor_sync(0xffffffffu, tsum_hi, 1);
-      tsum_hi += __shfl_xor_sync(0xffffffffu, tsum_hi, 2);
-      sum_lo = sum_lo * alpha_lo + tsum_lo;
-      sum_hi = sum_hi * alpha_hi + tsum_hi;
+      TileResult r;
+      attend_tile(sq + warp * 16 * kRowBytes, stage_k(t & 1), stage_k(t & 1) + kKVBytes, lane, kv_lo + t * kTileKV, pos_lo,
+                  pos_hi, first_lo, first_hi, scale_log2, r);
+      const MergeWeights wl = merge_weights(M_lo, r.max_lo), wh = merge_weights(M_hi, r.max_hi);
+      M_lo = wl.mx;
+      M_hi = wh.mx;
+      L_lo = merge_value(L_lo, r.sum_lo, wl);
+      L_hi = merge_value(L_hi, r.sum_hi, wh);
 #pragma unroll
       for (int i = 0; i < HD / 8; ++i) {
-        o_acc[i][0] *= alpha_lo;
-        o_acc[i][1] *= alpha_lo;
-        o_acc[i][2] *= alpha_hi;
-        o_acc[i][3] *= alpha_hi;
-      }
-
-      // ---- O += P V -----------------------------------------------------------------------------
-#pragma unroll
-      for (int kp = 0; kp < kTileKV / 16; ++kp) {
-#pragma unroll
-        for (int dp = 0; dp < HD / 16; ++dp) {
-          uint32_t b[4];
-          const int key = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-          ldmatrix_x4_trans(b, smem_u32(sv + key * kRowBytes + (dp * 2 + (lane >> 4)) * 16));
-          mma_bf16(o_acc[2 * dp], p[kp], b[0], b[1]);
-          mma_bf16(o_acc[2 * dp + 1], p[kp], b[2], b[3]);
-        }
-      }
-
-      // ---- end of a chunk: merge it into the running state and start afresh --------------------
-      if (!SPLIT && (((j0 + kTileKV) % kChunkKV) == 0 || t + 1 == ntiles)) {
-        const MergeWeights wl = merge_weights(Mt_lo, max_lo), wh = merge_weights(Mt_hi, max_hi);
-        Mt_lo = wl.mx;
-        Mt_hi = wh.mx;
-        Lt_lo = merge_value(Lt_lo, sum_lo, wl);
-        Lt_hi = merge_value(Lt_hi, sum_hi, wh);
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-          o_tot[i][0] = merge_value(o_tot[i][0], o_acc[i][0], wl);
-          o_tot[i][1] = merge_value(o_tot[i][1], o_acc[i][1], wl);
-          o_tot[i][2] = merge_value(o_tot[i][2], o_acc[i][2], wh);
-          o_tot[i][3] = merge_value(o_tot[i][3], o_acc[i][3], wh);
-          o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.0f;
-        }
-        max_lo = max_hi = -INFINITY;
-        sum_lo = sum_hi = 0.0f;
+        o_tot[i][0] = merge_value(o_tot[i][0], r.o[i][0], wl);
+        o_tot[i][1] = merge_value(o_tot[i][1], r.o[i][1], wl);
+        o_tot[i][2] = merge_value(o_tot[i][2], r.o[i][2], wh);
+        o_tot[i][3] = merge_value(o_tot[i][3], r.o[i][3], wh);
       }
     }
     __syncthreads();
   }
 
   if (!warp_active) return;
-  if (SPLIT) {
-    // ---- store this chunk's result: o[HD], then maximum and sum, per (row, head, chunk) ---------
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int m = half ? m_hi : m_lo;
-      if (m >= mrows) continue;
-      const int qr = m / group, hq = m - qr * group;
-      float* dst = chunk_out + ((static_cast<size_t>(row0 + qr) * heads + (g * group + hq)) * max_chunks + blockIdx.z) *
-                                   (HD + 2);
-#pragma unroll
-      for (int i = 0; i < HD / 8; ++i)
-        *reinterpret_cast<float2*>(dst + i * 8 + 2 * (lane & 3)) = make_float2(o_acc[i][half * 2], o_acc[i][half * 2 + 1]);
-      if ((lane & 3) == 0) {
-        dst[HD] = half ? max_hi : max_lo;
-        dst[HD + 1] = half ? sum_hi : sum_lo;
-      }
-    }
-    return;
-  }
-  // ---- normalise and store ---------------------------------------------------------------------
-  const float inv_lo = __fdiv_rn(1.0f, Lt_lo), inv_hi = __fdiv_rn(1.0f, Lt_hi);
+  const float inv_lo = __fdiv_rn(1.0f, L_lo), inv_hi = __fdiv_rn(1.0f, L_hi);
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int m = half ? m_hi : m_lo;
@@ -336,18 +294,74 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const
   }
 }
 
-// Second half of split mode: per (row, head) the chunk results are merged in ascending chunk
-// order with the same formula as above; thread d carries output element d.
-__global__ void merge_chunks_kernel(const float* __restrict__ chunk_out, int max_chunks, const int* __restrict__ pos,
-                                    __nv_bfloat16* __restrict__ out, int out_stride, int heads, int window) {
+// ---------------------------------------------------------------------------------------
+// Split mode (decode steps: one query row per sequence, at most 16 stacked rows): a block
+// takes (row, key/value head, four consecutive key tiles), each warp one tile of its own: it
+// loads the tile, computes the tile result and stores it. Record layout per (row, head,
+// tile): o[HD], maximum, sum.
+constexpr int kSplitQBytes = 16 * kRowBytes;
+
+__global__ void __launch_bounds__(kSplitWarps * 32)
+attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const __nv_bfloat16* __restrict__ kcache,
+                       const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
+                       const int* __restrict__ row_seq, const int* __restrict__ pos, int heads, int kv_heads, int page,
+                       int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* sq = smem;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x, g = blockIdx.y;
+  const int group = heads / kv_heads;  // stacked rows in use (<= 16)
+  const int p = pos[row];
+  const int first = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int t = blockIdx.z * kSplitWarps + warp;  // this warp's key tile
+  const int block_first_tile = blockIdx.z * kSplitWarps;
+  if (block_first_tile * kTileKV > p || (block_first_tile + kSplitWarps) * kTileKV <= first) return;  // nothing in range
+  const int* table = block_table + static_cast<size_t>(row_seq[row]) * max_blocks;
+
+  for (int idx = tid; idx < 16 * kPieces; idx += kSplitWarps * 32) {
+    const int m = idx / kPieces, piece = idx - m * kPieces;
+    const bool ok = m < group;
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(row) * q_stride + (g * group + (ok ? m : 0)) * HD + piece * 8;
+    cp_async16(smem_u32(sq + m * kRowBytes + piece * 16), src, ok);
+  }
+  const bool mine = t * kTileKV <= p && (t + 1) * kTileKV > first;  // the tile holds a key of the row's range
+  unsigned char* sk = smem + kSplitQBytes + warp * 2 * kKVBytes;
+  unsigned char* sv = sk + kKVBytes;
+  if (mine) load_kv_tile(sk, sv, kcache, vcache, table, page, kv_heads, g, t * kTileKV, p + 1, lane, 32);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();  // Q was loaded by all warps
+  if (!mine) return;
+
+  TileResult r;
+  attend_tile(sq, sk, sv, lane, t * kTileKV, p, p, first, first, scale_log2, r);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = (lane >> 2) + half * 8;
+    if (m >= group) continue;
+    float* dst = tile_out + ((static_cast<size_t>(row) * heads + (g * group + m)) * max_tiles + t) * (HD + 2);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+      *reinterpret_cast<float2*>(dst + i * 8 + 2 * (lane & 3)) = make_float2(r.o[i][half * 2], r.o[i][half * 2 + 1]);
+    if ((lane & 3) == 0) {
+      dst[HD] = half ? r.max_hi : r.max_lo;
+      dst[HD + 1] = half ? r.sum_hi : r.sum_lo;
+    }
+  }
+}
+
+// Second half of split mode: per (row, head) the tile results are merged in ascending tile
+// order with the same formula as in whole mode; thread d carries output element d.
+__global__ void merge_tiles_kernel(const float* __restrict__ tile_out, int max_tiles, const int* __restrict__ pos,
+                                   __nv_bfloat16* __restrict__ out, int out_stride, int heads, int window) {
   const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const int p = pos[r];
-  const int c_first = (window > 0 && p - window + 1 > 0) ? (p - window + 1) / kChunkKV : 0;
-  const int c_last = p / kChunkKV;
-  const float* src = chunk_out + (static_cast<size_t>(r) * heads + h) * max_chunks * (HD + 2);
+  const int t_first = (window > 0 && p - window + 1 > 0) ? (p - window + 1) / kTileKV : 0;
+  const int t_last = p / kTileKV;
+  const float* src = tile_out + (static_cast<size_t>(r) * heads + h) * max_tiles * (HD + 2);
   float M = -INFINITY, L = 0.0f, O = 0.0f;
-  for (int c = c_first; c <= c_last; ++c) {
-    const float* s = src + static_cast<size_t>(c) * (HD + 2);
+  for (int t = t_first; t <= t_last; ++t) {
+    const float* s = src + static_cast<size_t>(t) * (HD + 2);
     const MergeWeights w = merge_weights(M, s[HD]);
     M = w.mx;
     L = merge_value(L, s[HD + 1], w);
@@ -362,16 +376,16 @@ BW_API int bw_bf16_attention_head_dim() { return HD; }
 
 // Floats of scratch that split mode needs for `n` rows whose longest context is `max_keys`.
 BW_API long long bw_bf16_attention_scratch_floats(int n, int heads, int max_keys) {
-  const long long chunks = (max_keys + kChunkKV - 1) / kChunkKV;
-  return static_cast<long long>(n) * heads * chunks * (HD + 2);
+  const long long tiles = (max_keys + kTileKV - 1) / kTileKV;
+  return static_cast<long long>(n) * heads * tiles * (HD + 2);
 }
 
 BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_bfloat16* kcache,
                              const __nv_bfloat16* vcache, const int* block_table, int max_blocks,
                              const int* tile_seq, const int* tile_row0, const int* tile_rows, int num_tiles,
-                             const int* seq_pos0, const int* seq_row0, const int* pos, __nv_bfloat16* out,
-                             int out_stride, int n, int heads, int kv_heads, int hd, int page, int window,
-                             float scale, int max_keys, float* scratch, cudaStream_t stream) {
+                             const int* seq_pos0, const int* seq_row0, const int* row_seq, const int* pos,
+                             __nv_bfloat16* out, int out_stride, int n, int heads, int kv_heads, int hd, int page,
+                             int window, float scale, int max_keys, float* scratch, cudaStream_t stream) {
   if (n <= 0 || num_tiles <= 0) return 0;
   if (hd != HD) {
     bw::set_error("attention: this library was compiled for head size %d, got %d", HD, hd);
@@ -391,33 +405,39 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
     return -1;
   }
   const float scale_log2 = scale * 1.44269504088896341f;
-  const int chunks = (max_keys + kChunkKV - 1) / kChunkKV;
-  // decode steps (every tile a single row) with more than one chunk run split, if the caller
-  // gave scratch; both ways give the same bits
-  const bool split = scratch != nullptr && n == num_tiles && chunks > 1 && chunks <= 65535;
+  const int key_tiles = (max_keys + kTileKV - 1) / kTileKV;
+  constexpr int split_smem = kSplitQBytes + kSplitWarps * 2 * kKVBytes;
+  // decode steps (every query tile a single row) over more than a few key tiles run split, if
+  // the caller gave scratch and a group fits one warp; both ways give the same bits
+  const bool split = scratch != nullptr && n == num_tiles && key_tiles > 2 && heads / kv_heads <= 16 &&
+                     split_smem <= 200 * 1024 && (key_tiles + kSplitWarps - 1) / kSplitWarps <= 65535;
   static bool configured[2] = {false, false};
-  auto run = [&](auto kernel, int stages, int which, dim3 grid, float* chunk_out) -> int {
-    const int smem = kQBytes + stages * 2 * kKVBytes;
-    if (!configured[which]) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (split) {
+    if (!configured[1]) {
+      cudaError_t e = cudaFuncSetAttribute(attention_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, split_smem);
+      if (e != cudaSuccess) {
+        bw::set_error("attention: cannot raise shared memory to %d: %s", split_smem, cudaGetErrorString(e));
+        return static_cast<int>(e);
+      }
+      configured[1] = true;
+    }
+    attention_split_kernel<<<dim3(n, kv_heads, (key_tiles + kSplitWarps - 1) / kSplitWarps), kSplitWarps * 32, split_smem,
+                             stream>>>(qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, heads,
+                                       kv_heads, page, window, scale_log2, scratch, key_tiles);
+    merge_tiles_kernel<<<dim3(n, heads), HD, 0, stream>>>(scratch, key_tiles, pos, out, out_stride, heads, window);
+  } else {
+    constexpr int smem = kQBytes + kStages * 2 * kKVBytes;
+    if (!configured[0]) {
+      cudaError_t e = cudaFuncSetAttribute(attention_whole_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) {
         bw::set_error("attention: cannot raise shared memory to %d: %s", smem, cudaGetErrorString(e));
         return static_cast<int>(e);
       }
-      configured[which] = true;
+      configured[0] = true;
     }
-    kernel<<<grid, kThreads, smem, stream>>>(qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq,
-                                             tile_row0, tile_rows, seq_pos0, seq_row0, out, out_stride, heads, kv_heads,
-                                             page, window, scale_log2, chunk_out, chunks);
-    return 0;
-  };
-  if (split) {
-    const int rc = run(attention_bf16_kernel<3, true>, 3, 1, dim3(num_tiles, kv_heads, chunks), scratch);
-    if (rc) return rc;
-    merge_chunks_kernel<<<dim3(n, heads), HD, 0, stream>>>(scratch, chunks, pos, out, out_stride, heads, window);
-  } else {
-    const int rc = run(attention_bf16_kernel<2, false>, 2, 0, dim3(num_tiles, kv_heads), nullptr);
-    if (rc) return rc;
+    attention_whole_kernel<<<dim3(num_tiles, kv_heads), kThreads, smem, stream>>>(
+        qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out,
+        out_stride, heads, kv_heads, page, window, scale_log2);
   }
   return bw::launch_status();
 }

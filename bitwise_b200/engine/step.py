@@ -228,7 +228,7 @@ class Stepper:
         key = None
         if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:
             # the longest context enters in steps of 256 keys: the attention kernel of a decode
-            # step launches one thread block per chunk of 256 keys
+            # step launches one thread block per 256 keys
             key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows, (ctx.max_keys + 255) // 256) + tuple(
                 t[3] for t in ctx.tile_sets.values())
         if key is not None and key in self._graphs:

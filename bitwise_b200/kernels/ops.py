@@ -189,7 +189,7 @@ class KernelOps:
 
     def _attention_scratch(self, lib, device, n: int, heads: int, max_keys: int) -> torch.Tensor:
         """Scratch of the split attention: one (output, maximum, sum) record per row, head and
-        chunk of 256 keys.  Sized for contexts rounded up to 2048 keys so that it seldom grows."""
+        tile of 64 keys.  Sized for contexts rounded up to 2048 keys so that it seldom grows."""
         lib.bw_bf16_attention_scratch_floats.restype = ctypes.c_longlong
         keys = (max_keys + 2047) // 2048 * 2048
         floats = int(lib.bw_bf16_attention_scratch_floats(_c_int(n), _c_int(heads), _c_int(keys)))
@@ -269,14 +269,14 @@ class KernelOps:
             lib = self._attention_lib(head_dim)
             t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.attention_tile_rows(heads, kv_heads))
             scratch = None
-            split = t_count == n and max_keys > 256  # a decode step: one chunk of keys per thread block
+            split = t_count == n and max_keys > 128  # a decode step: one tile of keys per warp
             if split:
                 scratch = self._attention_scratch(lib, qkv.device, n, heads, max_keys)
             fn = lib.bw_bf16_attention
             fn.restype = _c_int
             rc = fn(_p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
                     _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
-                    _p(batch.seq_pos0), _p(batch.seq_row0), _p(pos), _p(out), _c_int(out.shape[1]), _c_int(n),
+                    _p(batch.seq_pos0), _p(batch.seq_row0), _p(row_seq), _p(pos), _p(out), _c_int(out.shape[1]), _c_int(n),
                     _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window), _c_float(scale),
                     _c_int(max_keys), _p(scratch), self._stream())
             if rc != 0:
