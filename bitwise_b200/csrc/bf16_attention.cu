@@ -32,8 +32,15 @@ constexpr int kTileM = 64;    // stacked (query row, head of the group) rows per
 constexpr int kTileKV = 64;   // keys per tile
 constexpr int kSplitWarps = 4; // key tiles per block in split mode, one per warp
 constexpr int kThreads = 128;
-constexpr int kRowElems = HD + 8;           // padded row: 16 bytes of padding keep ldmatrix conflict-free
-constexpr int kRowBytes = kRowElems * 2;
+// Rows of Q, K and V tiles in shared memory. When a row is a whole number of 128-byte lines
+// the 16-byte pieces of a line are xor-swizzled with the row number; other head sizes get 16
+// bytes of padding per row. Either way eight consecutive rows of one piece fall into
+// distinct banks for ldmatrix.
+constexpr bool kSwizzle = (HD % 64 == 0);
+constexpr int kRowBytes = kSwizzle ? HD * 2 : HD * 2 + 16;
+__device__ __forceinline__ int piece_offset(int row, int piece) {
+  return row * kRowBytes + (kSwizzle ? (((piece & ~7) | ((piece ^ row) & 7)) << 4) : (piece << 4));
+}
 constexpr int kQBytes = kTileM * kRowBytes;
 constexpr int kKVBytes = kTileKV * kRowBytes;
 constexpr int kPieces = HD / 8;             // 16-byte pieces per row
@@ -113,13 +120,13 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
     uint32_t a[4];
     {
       const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
-      ldmatrix_x4(a, smem_u32(sq + row * kRowBytes + (kk * 2 + (lane >> 4)) * 16));
+      ldmatrix_x4(a, smem_u32(sq + piece_offset(row, kk * 2 + (lane >> 4))));
     }
 #pragma unroll
     for (int np = 0; np < kTileKV / 16; ++np) {
       uint32_t b[4];
       const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
-      ldmatrix_x4(b, smem_u32(sk + key * kRowBytes + (kk * 2 + ((lane >> 3) & 1)) * 16));
+      ldmatrix_x4(b, smem_u32(sk + piece_offset(key, kk * 2 + ((lane >> 3) & 1))));
       mma_bf16(s[2 * np], a, b[0], b[1]);
       mma_bf16(s[2 * np + 1], a, b[2], b[3]);
     }
@@ -168,7 +175,7 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
     for (int dp = 0; dp < HD / 16; ++dp) {
       uint32_t b[4];
       const int key = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      ldmatrix_x4_trans(b, smem_u32(sv + key * kRowBytes + (dp * 2 + (lane >> 4)) * 16));
+      ldmatrix_x4_trans(b, smem_u32(sv + piece_offset(key, dp * 2 + (lane >> 4))));
       mma_bf16(r.o[2 * dp], p[kp], b[0], b[1]);
       mma_bf16(r.o[2 * dp + 1], p[kp], b[2], b[3]);
     }
@@ -190,8 +197,8 @@ __device__ __forceinline__ void load_kv_tile(unsigned char* sk, unsigned char* s
     const bool ok = j < kv_hi;
     size_t off = 0;
     if (ok) off = ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + (j % page)) * HD + piece * 8;
-    cp_async16(smem_u32(sk + key * kRowBytes + piece * 16), kcache + off, ok);
-    cp_async16(smem_u32(sv + key * kRowBytes + piece * 16), vcache + off, ok);
+    cp_async16(smem_u32(sk + piece_offset(key, piece)), kcache + off, ok);
+    cp_async16(smem_u32(sv + piece_offset(key, piece)), vcache + off, ok);
   }
 }
 
@@ -207,6 +214,8 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
                        const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
                        const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
                        int kv_heads, int page, int window, float scale_log2) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sq = smem;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -224,7 +233,7 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
     const bool ok = m < mrows;
     const int qr = ok ? m / group : 0, hq = ok ? m - qr * group : 0;
     const __nv_bfloat16* src = qkv + static_cast<size_t>(row0 + qr) * q_stride + (g * group + hq) * HD + piece * 8;
-    cp_async16(smem_u32(sq + m * kRowBytes + piece * 16), src, ok);
+    cp_async16(smem_u32(sq + piece_offset(m, piece)), src, ok);
   }
   cp_async_commit();
 
@@ -306,6 +315,8 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
                        const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                        const int* __restrict__ row_seq, const int* __restrict__ pos, int heads, int kv_heads, int page,
                        int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sq = smem;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -322,7 +333,7 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
     const int m = idx / kPieces, piece = idx - m * kPieces;
     const bool ok = m < group;
     const __nv_bfloat16* src = qkv + static_cast<size_t>(row) * q_stride + (g * group + (ok ? m : 0)) * HD + piece * 8;
-    cp_async16(smem_u32(sq + m * kRowBytes + piece * 16), src, ok);
+    cp_async16(smem_u32(sq + piece_offset(m, piece)), src, ok);
   }
   const bool mine = t * kTileKV <= p && (t + 1) * kTileKV > first;  // the tile holds a key of the row's range
   unsigned char* sk = smem + kSplitQBytes + warp * 2 * kKVBytes;
@@ -354,18 +365,35 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
 // order with the same formula as in whole mode; thread d carries output element d.
 __global__ void merge_tiles_kernel(const float* __restrict__ tile_out, int max_tiles, const int* __restrict__ pos,
                                    __nv_bfloat16* __restrict__ out, int out_stride, int heads, int window) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const int p = pos[r];
   const int t_first = (window > 0 && p - window + 1 > 0) ? (p - window + 1) / kTileKV : 0;
   const int t_last = p / kTileKV;
   const float* src = tile_out + (static_cast<size_t>(r) * heads + h) * max_tiles * (HD + 2);
   float M = -INFINITY, L = 0.0f, O = 0.0f;
-  for (int t = t_first; t <= t_last; ++t) {
-    const float* s = src + static_cast<size_t>(t) * (HD + 2);
-    const MergeWeights w = merge_weights(M, s[HD]);
-    M = w.mx;
-    L = merge_value(L, s[HD + 1], w);
-    O = merge_value(O, s[d], w);
+  // the loads of four tiles are issued together; the merges stay in ascending order
+  int t = t_first;
+  for (; t + 4 <= t_last + 1; t += 4) {
+    const float* s0 = src + static_cast<size_t>(t) * (HD + 2);
+    const float m0 = s0[HD], l0 = s0[HD + 1], o0 = s0[d];
+    const float m1 = s0[(HD + 2) + HD], l1 = s0[(HD + 2) + HD + 1], o1 = s0[(HD + 2) + d];
+    const float m2 = s0[2 * (HD + 2) + HD], l2 = s0[2 * (HD + 2) + HD + 1], o2 = s0[2 * (HD + 2) + d];
+    const float m3 = s0[3 * (HD + 2) + HD], l3 = s0[3 * (HD + 2) + HD + 1], o3 = s0[3 * (HD + 2) + d];
+    MergeWeights w = merge_weights(M, m0);
+    M = w.mx, L = merge_value(L, l0, w), O = merge_value(O, o0, w);
+    w = merge_weights(M, m1);
+    M = w.mx, L = merge_value(L, l1, w), O = merge_value(O, o1, w);
+    w = merge_weights(M, m2);
+    M = w.mx, L = merge_value(L, l2, w), O = merge_value(O, o2, w);
+    w = merge_weights(M, m3);
+    M = w.mx, L = merge_value(L, l3, w), O = merge_value(O, o3, w);
+  }
+  for (; t <= t_last; ++t) {
+    const float* s0 = src + static_cast<size_t>(t) * (HD + 2);
+    const MergeWeights w = merge_weights(M, s0[HD]);
+    M = w.mx, L = merge_value(L, s0[HD + 1], w), O = merge_value(O, s0[d], w);
   }
   out[static_cast<size_t>(r) * out_stride + h * HD + d] = __float2bfloat16_rn(__fmul_rn(O, __fdiv_rn(1.0f, L)));
 }
@@ -421,10 +449,9 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
       }
       configured[1] = true;
     }
-    attention_split_kernel<<<dim3(n, kv_heads, (key_tiles + kSplitWarps - 1) / kSplitWarps), kSplitWarps * 32, split_smem,
-                             stream>>>(qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, heads,
+    bw::launch_pdl(attention_split_kernel, dim3(dim3(n, kv_heads, (key_tiles + kSplitWarps - 1) / kSplitWarps)), dim3(kSplitWarps * 32), split_smem, stream, qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, heads,
                                        kv_heads, page, window, scale_log2, scratch, key_tiles);
-    merge_tiles_kernel<<<dim3(n, heads), HD, 0, stream>>>(scratch, key_tiles, pos, out, out_stride, heads, window);
+    bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(HD), 0, stream, scratch, key_tiles, pos, out, out_stride, heads, window);
   } else {
     constexpr int smem = kQBytes + kStages * 2 * kKVBytes;
     if (!configured[0]) {
@@ -435,7 +462,7 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
       }
       configured[0] = true;
     }
-    attention_whole_kernel<<<dim3(num_tiles, kv_heads), kThreads, smem, stream>>>(
+    bw::launch_pdl(attention_whole_kernel, dim3(dim3(num_tiles, kv_heads)), dim3(kThreads), smem, stream, 
         qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out,
         out_stride, heads, kv_heads, page, window, scale_log2);
   }

@@ -56,6 +56,8 @@ template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool SPLIT>
 __global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
 gemm_bf16_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Y, int y_is_f32,
                  const float* residual, int M, int N, int K, int aligned, float* partials, int* counters) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   constexpr int THREADS = WARPS_M * WARPS_N * 32;
   constexpr int WTM = BM / WARPS_M, WTN = BN / WARPS_N;
   constexpr int MI = WTM / 16, NI = WTN / 8;
@@ -270,7 +272,7 @@ int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32
     bw::set_error("linear: %d rows exceed the grid limit", m);
     return -1;
   }
-  kernel<<<grid, THREADS, smem, stream>>>(x, w, y, y_is_f32, residual, m, n, k, aligned, partials, counters);
+  bw::launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, x, w, y, y_is_f32, residual, m, n, k, aligned, partials, counters);
   return bw::launch_status();
 }
 

@@ -33,15 +33,33 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 64;
 constexpr int kChunk = 512;
 constexpr int kTilesPerChunk = kChunk / BK;
-constexpr int kStages = 6;
-constexpr int kStageBytes = (BM + BN) * BK * 2;  // 32 KB
 constexpr int kThreads = 192;
+constexpr int kTileBytesW = BN * BK * 2;       // 16 KB of weights per stage
+constexpr int kSmemBudget = 200 * 1024;        // ring of stages (plus barriers) per block
+
+// The x tile of a stage holds A_ROWS rows: 128 for large batches, fewer for small ones. The
+// tensor core always reads 128 rows; with a shorter tile the rows beyond it are whatever lies
+// behind in shared memory (the ring is padded so that the read stays inside the block's
+// allocation). Rows are independent in a matrix product, so this only fills accumulator
+// lanes that are never read, and it leaves room for more stages: a decode step is bound by
+// how many bytes of weights an SM keeps in flight.
+template <int A_ROWS>
+struct Ring {
+  static constexpr int kTileBytesX = A_ROWS * BK * 2;
+  static constexpr int kStageBytes = kTileBytesX + kTileBytesW;
+  static constexpr int kStages = (kSmemBudget - (BM - A_ROWS) * BK * 2) / kStageBytes > 12
+                                     ? 12
+                                     : (kSmemBudget - (BM - A_ROWS) * BK * 2) / kStageBytes;
+  static constexpr int kPadBytes = (BM - A_ROWS) * BK * 2;  // behind the last stage
+  static constexpr int kRingBytes = kStages * kStageBytes + kPadBytes;
+};
+constexpr int kMaxStages = 12;
 constexpr int kTmemCols = 256;  // two accumulators of 128 columns
 constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
 
 struct __align__(8) Barriers {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -140,6 +158,8 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 // the additions stay in order.
 __global__ void reduce_chunks_kernel(const float* __restrict__ partials, int num_chunks, void* Y, int y_is_f32,
                                      const float* residual, int M, int N) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const size_t total = static_cast<size_t>(M) * N;
   const size_t o = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (o >= total) return;
@@ -159,14 +179,112 @@ __global__ void reduce_chunks_kernel(const float* __restrict__ partials, int num
     static_cast<__nv_bfloat16*>(Y)[o] = __float2bfloat16_rn(v);
 }
 
-template <bool SPLIT>
+// The ordered sum of the chunk sums of one output (shared by the reduce kernels below).
+__device__ __forceinline__ float ordered_chunk_sum(const float* __restrict__ partials, int num_chunks, size_t plane,
+                                                   size_t o) {
+  float v = 0.0f;
+  for (int c0 = 0; c0 < num_chunks; c0 += 8) {
+    float p[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] = (c0 + e < num_chunks) ? __ldcg(partials + (c0 + e) * plane + o) : 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (c0 + e < num_chunks) v = (c0 + e == 0) ? p[e] : v + p[e];
+  }
+  return v;
+}
+
+// Split mode followed by an RMSNorm of the result: one block per row adds the chunk sums and
+// the residual, stores the float32 row, and normalises it with exactly the arithmetic of the
+// stand-alone RMSNorm kernel (thread t sums elements t, t + 256, ... in order, shuffle tree,
+// warps in order), so that fusing changes no bit.
+__global__ void __launch_bounds__(256)
+reduce_norm_kernel(const float* __restrict__ partials, int num_chunks, float* Y, const float* residual, int M, int N,
+                   const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ norm_out) {
+  bw::pdl_wait();
+  bw::pdl_launch();
+  const int r = blockIdx.x;
+  const size_t plane = static_cast<size_t>(M) * N;
+  __shared__ float red[8];
+  float acc = 0.0f;
+  // four outputs of this thread at a time, so that 32 loads are in flight; the additions of
+  // every output stay in ascending chunk order, and the squares are summed in element order
+  for (int i0 = threadIdx.x; i0 < N; i0 += 4 * 256) {
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int c0 = 0; c0 < num_chunks; c0 += 8) {
+      float p[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int i = i0 + q * 256;
+          p[q][e] = (i < N && c0 + e < num_chunks)
+                        ? __ldcg(partials + (c0 + e) * plane + static_cast<size_t>(r) * N + i)
+                        : 0.0f;
+        }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (c0 + e < num_chunks) v[q] = (c0 + e == 0) ? p[q][e] : v[q] + p[q][e];
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = i0 + q * 256;
+      if (i >= N) break;
+      const size_t o = static_cast<size_t>(r) * N + i;
+      float x = v[q];
+      if (residual) x = residual[o] + x;
+      Y[o] = x;
+      acc = __fmaf_rn(x, x, acc);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = __fadd_rn(ss, red[i]);
+  const float inv = bw::rms_scale(ss, N, eps);
+  for (int i = threadIdx.x; i < N; i += 256) {
+    const size_t o = static_cast<size_t>(r) * N + i;
+    norm_out[o] = __float2bfloat16_rn(bw::rms_apply(Y[o], inv, norm_w[i]));
+  }
+}
+
+// Split mode of the gate/up product with SwiGLU: weights are interleaved in blocks of 64 rows
+// (64 gate rows, then the 64 up rows of the same indices), so output c of a row takes the
+// gate at column 128 (c / 64) + c % 64 and the up value 64 columns further. Gate and up are
+// rounded to bfloat16 first, as if the product had been stored, then combined.
+__global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num_chunks, __nv_bfloat16* __restrict__ H,
+                                     int M, int N) {
+  bw::pdl_wait();
+  bw::pdl_launch();
+  const int inter = N / 2;
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<size_t>(M) * inter) return;
+  const int r = static_cast<int>(idx / inter), c = static_cast<int>(idx - static_cast<size_t>(r) * inter);
+  const size_t plane = static_cast<size_t>(M) * N;
+  const size_t og = static_cast<size_t>(r) * N + 128 * (c / 64) + (c % 64);
+  const float g = __bfloat162float(__float2bfloat16_rn(ordered_chunk_sum(partials, num_chunks, plane, og)));
+  const float u = __bfloat162float(__float2bfloat16_rn(ordered_chunk_sum(partials, num_chunks, plane, og + 64)));
+  H[idx] = __float2bfloat16_rn(bw::swiglu_one(g, u));
+}
+
+// EPI 0: y = (residual +) product.  EPI 1 (whole mode only): the product is the interleaved
+// gate/up projection and y[m][n / 2] = SwiGLU of it (bfloat16).
+template <bool SPLIT, int A_ROWS, int EPI>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
                int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzled tiles want 1024-byte alignment
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Barriers* bars = reinterpret_cast<Barriers*>(tiles + kStages * kStageBytes);
+  constexpr int kStages = Ring<A_ROWS>::kStages;
+  constexpr int kStageBytes = Ring<A_ROWS>::kStageBytes;
+  constexpr int kTileBytesX = Ring<A_ROWS>::kTileBytesX;
+  Barriers* bars = reinterpret_cast<Barriers*>(tiles + Ring<A_ROWS>::kRingBytes);
   volatile uint32_t* failed = &bars->failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -205,6 +323,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
+  // barriers and tensor memory are set up; only now wait for the kernel before this one
+  bw::pdl_wait();
+  bw::pdl_launch();
   const uint32_t tmem_base = bars->tmem_base;
 
   if (warp == 0) {
@@ -224,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           unsigned char* a = tiles + s * kStageBytes;
           mbar_expect_tx(&bars->full[s], kStageBytes);
           tma_load_2d(a, &map_x, kt * BK, m0, &bars->full[s]);
-          tma_load_2d(a + BM * BK * 2, &map_w, kt * BK, n0, &bars->full[s]);
+          tma_load_2d(a + kTileBytesX, &map_w, kt * BK, n0, &bars->full[s]);
         }
       }
     }
@@ -251,7 +372,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             fence_after_sync();
             const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
-            const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + BM * BK * 2);
+            const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + kTileBytesX);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               // 16 k-elements are 32 bytes: the start address field moves by 2 (units of 16 bytes)
@@ -315,6 +436,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         continue;
       }
       if (row >= M) continue;
+      if (EPI == 1) {
+        // columns 0..63 of the tile are gate rows, 64..127 the up rows of the same indices
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + static_cast<size_t>(row) * (N / 2) + n0 / 2;
+#pragma unroll
+        for (int j = 0; j < 64; j += 8) {
+          __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float g0 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e]));
+            const float g1 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e + 1]));
+            const float u0 = __bfloat162float(__float2bfloat16_rn(total[64 + j + 2 * e]));
+            const float u1 = __bfloat162float(__float2bfloat16_rn(total[64 + j + 2 * e + 1]));
+            o[e] = __floats2bfloat162_rn(bw::swiglu_one(g0, u0), bw::swiglu_one(g1, u1));
+          }
+          *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
+        }
+        continue;
+      }
       const size_t base = static_cast<size_t>(row) * N + n0;
       if (y_is_f32) {
         float* out = static_cast<float*>(Y) + base;
@@ -380,13 +519,13 @@ EncodeTiled encoder() {
   return fn;
 }
 
-// rows x k bf16, row-major; box of 128 rows x 64 k-elements, 128-byte swizzle, zero fill outside
-bool make_map(CUtensorMap* map, const void* base, int rows, int k) {
+// rows x k bf16, row-major; box of box_rows rows x 64 k-elements, 128-byte swizzle, zero fill outside
+bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows = BM) {
   EncodeTiled enc = encoder();
   if (!enc) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {BK, BM};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -425,14 +564,79 @@ BW_API int bw_bf16_linear_tc_splits(int m, int n, int k) {
   return m <= BM && k > kChunk && n_blocks < 100;
 }
 
-BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
-                             const float* residual, int m, int n, int k, float* partials, int* counters,
-                             cudaStream_t stream) {
-  if (m <= 0 || n <= 0) return 0;
-  if (!bw_bf16_linear_tc_usable(x, w, k)) {
-    bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
+namespace {
+
+int sm_count_of_device() {
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  return sm_count;
+}
+
+// What follows the product: nothing, an RMSNorm of the float32 result, or SwiGLU.
+struct Fused {
+  int mode = 0;  // 0 none, 1 rmsnorm of y into norm_out, 2 swiglu (y is [m][n / 2] bfloat16)
+  const float* norm_w = nullptr;
+  float eps = 0.0f;
+  __nv_bfloat16* norm_out = nullptr;
+};
+
+template <bool SPLIT, int A_ROWS, int EPI>
+int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m, int n,
+              int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream) {
+  constexpr int smem = Ring<A_ROWS>::kRingBytes + sizeof(Barriers) + 1024;
+  static_assert(smem <= 227 * 1024, "ring does not fit");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(gemm_tc_kernel<SPLIT, A_ROWS, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    configured = true;
+  }
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, x, m, k, A_ROWS) || !make_map(&map_w, w, n, k)) {
+    bw::set_error("linear (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
     return -1;
   }
+  const int n_blocks = (n + BN - 1) / BN, m_blocks = (m + BM - 1) / BM, chunks = (k + kChunk - 1) / kChunk;
+  const long long items = SPLIT ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
+  const int sms = sm_count_of_device();
+  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
+  bw::launch_pdl(gemm_tc_kernel<SPLIT, A_ROWS, EPI>, dim3(grid), dim3(kThreads), smem, stream, map_x, map_w, y, y_is_f32, residual, m, n, k,
+                                                                       error_word, partials);
+  if (SPLIT) {
+    const size_t outputs = static_cast<size_t>(m) * n;
+    if (fused.mode == 1)
+      bw::launch_pdl(reduce_norm_kernel, dim3(m), dim3(256), 0, stream, partials, chunks, static_cast<float*>(y), residual, m, n, fused.norm_w,
+                                                fused.eps, fused.norm_out);
+    else if (fused.mode == 2)
+      bw::launch_pdl(reduce_swiglu_kernel, dim3(static_cast<unsigned>((outputs / 2 + 255) / 256)), dim3(256), 0, stream, 
+          partials, chunks, static_cast<__nv_bfloat16*>(y), m, n);
+    else
+      bw::launch_pdl(reduce_chunks_kernel, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, stream, partials, chunks, y,
+                                                                                            y_is_f32, residual, m, n);
+  }
+  return bw::launch_status();
+}
+
+// picks the x-tile height from the batch size
+template <bool SPLIT, int EPI>
+int launch_tc_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m,
+                   int n, int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream) {
+  if (m <= 16) return launch_tc<SPLIT, 16, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  if (m <= 32) return launch_tc<SPLIT, 32, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  if (m <= 64) return launch_tc<SPLIT, 64, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  return launch_tc<SPLIT, 128, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+}
+
+int ensure_error_word() {
   if (!g_error_flag) {
     cudaError_t e = cudaMalloc(&g_error_flag, sizeof(int));
     if (e != cudaSuccess) {
@@ -441,46 +645,65 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
     }
     cudaMemset(g_error_flag, 0, sizeof(int));
   }
-  CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, x, m, k) || !make_map(&map_w, w, n, k)) {
-    bw::set_error("linear (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
+  return 0;
+}
+
+}  // namespace
+
+BW_API int bw_bf16_rmsnorm(const float* x, const float* weight, __nv_bfloat16* y, const int* rows, int n, int width,
+                           float eps, cudaStream_t stream);
+
+BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
+                             const float* residual, int m, int n, int k, float* partials, int* counters,
+                             cudaStream_t stream) {
+  (void)counters;
+  if (m <= 0 || n <= 0) return 0;
+  if (!bw_bf16_linear_tc_usable(x, w, k)) {
+    bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
     return -1;
   }
-  constexpr int smem = kStages * kStageBytes + sizeof(Barriers) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) {
-      bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
-      return static_cast<int>(e);
-    }
-    configured = true;
-  }
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
-  const int n_blocks = (n + BN - 1) / BN, m_blocks = (m + BM - 1) / BM, chunks = (k + kChunk - 1) / kChunk;
+  if (const int rc = ensure_error_word()) return rc;
   const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
-  (void)counters;
-  const long long items = split ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
-  const unsigned grid = static_cast<unsigned>(items < sm_count ? items : sm_count);
-  if (split) {
-    gemm_tc_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, g_error_flag,
-                                                           partials);
-    const size_t outputs = static_cast<size_t>(m) * n;
-    reduce_chunks_kernel<<<static_cast<unsigned>((outputs + 255) / 256), 256, 0, stream>>>(partials, chunks, y, y_is_f32,
-                                                                                          residual, m, n);
-  } else {
-    gemm_tc_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, g_error_flag,
-                                                            nullptr);
+  const Fused none;
+  if (split) return launch_tc_rows<true, 0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, partials, none, stream);
+  return launch_tc_rows<false, 0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, nullptr, none, stream);
+}
+
+// y = residual + x W^T (float32), then norm_out = RMSNorm(y) * norm_w (bfloat16): the same
+// bits as the product followed by the stand-alone norm kernel, one launch less in split mode.
+BW_API int bw_bf16_linear_tc_norm(const __nv_bfloat16* x, const __nv_bfloat16* w, float* y, const float* residual, int m,
+                                  int n, int k, float* partials, const float* norm_w, float eps,
+                                  __nv_bfloat16* norm_out, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (!bw_bf16_linear_tc_usable(x, w, k)) {
+    bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
+    return -1;
   }
-  return bw::launch_status();
+  if (const int rc = ensure_error_word()) return rc;
+  const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
+  Fused f;
+  f.mode = 1, f.norm_w = norm_w, f.eps = eps, f.norm_out = norm_out;
+  if (split) return launch_tc_rows<true, 0>(x, w, y, 1, residual, m, n, k, g_error_flag, partials, f, stream);
+  const int rc = launch_tc_rows<false, 0>(x, w, y, 1, residual, m, n, k, g_error_flag, nullptr, Fused(), stream);
+  if (rc) return rc;
+  return bw_bf16_rmsnorm(y, norm_w, norm_out, nullptr, m, n, eps, stream);
+}
+
+// h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows
+// (n a multiple of 128).
+BW_API int bw_bf16_linear_tc_swiglu(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* h, int m, int n, int k,
+                                    float* partials, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (n % 128 || !bw_bf16_linear_tc_usable(x, w, k)) {
+    bw::set_error("linear + SwiGLU: needs n %% 128 == 0 (got %d) and rows that start on 16 bytes", n);
+    return -1;
+  }
+  if (const int rc = ensure_error_word()) return rc;
+  const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
+  Fused f;
+  f.mode = 2;
+  if (split) return launch_tc_rows<true, 0>(x, w, h, 0, nullptr, m, n, k, g_error_flag, partials, f, stream);
+  return launch_tc_rows<false, 1>(x, w, h, 0, nullptr, m, n, k, g_error_flag, nullptr, f, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -531,15 +754,12 @@ BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w
     bw::set_error("linear (no allocation): cannot use device %d: %s", dev, cudaGetErrorString(e));
     return e != cudaSuccess ? static_cast<int>(e) : -1;
   }
-  constexpr int smem = kStages * kStageBytes + sizeof(Barriers) + 1024;
   if (!g_noalloc_scratch_ptr[dev]) {
     // set-up, once per device, with that device current
     float* sp = nullptr;
     int* ep = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&sp), g_noalloc_scratch);
     if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ep), g_noalloc_error);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
       bw::set_error("linear (no allocation): set-up on device %d failed: %s", dev, cudaGetErrorString(e));
       return static_cast<int>(e);
@@ -547,32 +767,13 @@ BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w
     g_noalloc_error_ptr[dev] = ep;  // the array is zero when the library is loaded; kernels only ever set word 0
     g_noalloc_scratch_ptr[dev] = sp;
   }
-  float* scratch = g_noalloc_scratch_ptr[dev];
-  int* error_word = g_noalloc_error_ptr[dev];
-  CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, x, m, k) || !make_map(&map_w, w, n, k)) {
-    bw::set_error("linear (no allocation): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
-    return -1;
-  }
-  int sm_count = 0;
-  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  if (sm_count <= 0) sm_count = 148;
-  const int n_blocks = (n + BN - 1) / BN, m_blocks = (m + BM - 1) / BM;
-  const long long items = split ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
-  const unsigned grid = static_cast<unsigned>(items < sm_count ? items : sm_count);
-  if (split) {
-    // nothing in the scratch has to start at zero: every chunk sum that the second kernel
-    // reads is written by the first one in this same call
-    gemm_tc_kernel<true><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, error_word,
-                                                           scratch);
-    const size_t outputs = static_cast<size_t>(m) * n;
-    reduce_chunks_kernel<<<static_cast<unsigned>((outputs + 255) / 256), 256, 0, stream>>>(scratch, chunks, y, y_is_f32,
-                                                                                          residual, m, n);
-  } else {
-    gemm_tc_kernel<false><<<grid, kThreads, smem, stream>>>(map_x, map_w, y, y_is_f32, residual, m, n, k, error_word,
-                                                            nullptr);
-  }
-  return bw::launch_status();
+  // Nothing in the scratch has to start at zero: every chunk sum that the second kernel reads
+  // is written by the first one in this same call. The launcher raises the kernel's
+  // shared-memory limit at its first use (no allocation either).
+  if (split)
+    return launch_tc_rows<true, 0>(x, w, y, y_is_f32, residual, m, n, k, g_noalloc_error_ptr[dev],
+                                   g_noalloc_scratch_ptr[dev], Fused(), stream);
+  return launch_tc_rows<false, 0>(x, w, y, y_is_f32, residual, m, n, k, g_noalloc_error_ptr[dev], nullptr, Fused(), stream);
 }
 
 // Reads and clears the word that a kernel launched by bw_bf16_linear_noalloc raises when one

@@ -15,6 +15,8 @@ constexpr int kNormThreads = 256;
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
                     const int* __restrict__ rows, int width, float eps) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const float* xr = x + static_cast<size_t>(src) * width;
@@ -23,17 +25,17 @@ rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __
   float acc = 0.0f;
   for (int i = threadIdx.x; i < width; i += kNormThreads) {
     const float v = xr[i];
-    acc = fmaf(v, v, acc);
+    acc = __fmaf_rn(v, v, acc);
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
   __syncthreads();
   float ss = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kNormThreads / 32; ++i) ss += red[i];
-  const float inv = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
-  for (int i = threadIdx.x; i < width; i += kNormThreads) yr[i] = __float2bfloat16_rn((xr[i] * inv) * w[i]);
+  for (int i = 0; i < kNormThreads / 32; ++i) ss = __fadd_rn(ss, red[i]);
+  const float inv = bw::rms_scale(ss, width, eps);
+  for (int i = threadIdx.x; i < width; i += kNormThreads) yr[i] = __float2bfloat16_rn(bw::rms_apply(xr[i], inv, w[i]));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -47,6 +49,8 @@ __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const
                                        const float* __restrict__ sin_t, const int* __restrict__ block_table,
                                        int max_blocks, __nv_bfloat16* kcache, __nv_bfloat16* vcache, int heads,
                                        int kv_heads, int hd, int page, int write_kv) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.x;
   const int half = hd >> 1;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
@@ -91,13 +95,12 @@ __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const
 // SwiGLU on rows laid out [gate | up]: h = (g * sigmoid(g)) * u in float32 (src/kernels.cpp:291-298).
 // blockIdx.y is the row; a thread handles 8 consecutive columns when the row width allows
 // 16-byte accesses, else one column.
-__device__ __forceinline__ float swiglu_one(float g, float u) {
-  const float sig = 1.0f / (1.0f + bw::det_expf(-g));
-  return (g * sig) * u;
-}
+using bw::swiglu_one;
 
 __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                        int inter) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= inter) return;
@@ -117,6 +120,8 @@ __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up
 
 __global__ void swiglu_bf16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                    int inter) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= inter) return;
@@ -134,7 +139,7 @@ BW_API int bw_bf16_rmsnorm(const float* x, const float* weight, __nv_bfloat16* y
     bw::set_error("rmsnorm: width %d", width);
     return -1;
   }
-  rmsnorm_bf16_kernel<<<n, kNormThreads, 0, stream>>>(x, weight, y, rows, width, eps);
+  bw::launch_pdl(rmsnorm_bf16_kernel, dim3(n), dim3(kNormThreads), 0, stream, x, weight, y, rows, width, eps);
   return bw::launch_status();
 }
 
@@ -154,7 +159,7 @@ BW_API int bw_bf16_rope_cache(__nv_bfloat16* qkv, int row_stride, const int* pos
     bw::set_error("rope: %d heads exceed the grid limit", heads);
     return -1;
   }
-  rope_cache_bf16_kernel<<<grid, threads, 0, stream>>>(qkv, row_stride, pos, row_seq, cos_t, sin_t, block_table,
+  bw::launch_pdl(rope_cache_bf16_kernel, dim3(grid), dim3(threads), 0, stream, qkv, row_stride, pos, row_seq, cos_t, sin_t, block_table,
                                                        max_blocks, kcache, vcache, heads, kv_heads, hd, page, write_kv);
   return bw::launch_status();
 }
@@ -175,11 +180,11 @@ BW_API int bw_bf16_swiglu(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int 
   if (vec) {
     const int threads = 128;
     dim3 grid((inter / 8 + threads - 1) / threads, n);
-    swiglu_bf16_vec_kernel<<<grid, threads, 0, stream>>>(gate_up, out, inter);
+    bw::launch_pdl(swiglu_bf16_vec_kernel, dim3(grid), dim3(threads), 0, stream, gate_up, out, inter);
   } else {
     const int threads = 256;
     dim3 grid((inter + threads - 1) / threads, n);
-    swiglu_bf16_kernel<<<grid, threads, 0, stream>>>(gate_up, out, inter);
+    bw::launch_pdl(swiglu_bf16_kernel, dim3(grid), dim3(threads), 0, stream, gate_up, out, inter);
   }
   return bw::launch_status();
 }

@@ -20,6 +20,30 @@ inline int launch_status() {
   return static_cast<int>(e);
 }
 
+// Programmatic dependent launch: every kernel of the serving path is launched with the
+// attribute below and begins with pdl_wait(), which returns once the kernel before it in the
+// stream has completed and its writes are visible; pdl_launch() right after lets the NEXT
+// kernel be set up on the SMs meanwhile, so that launch latency and block scheduling overlap
+// the running kernel instead of following it. Nothing is read or written before pdl_wait().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // exp(x) written only with IEEE multiply, add and fused multiply-add, each rounded to
 // nearest, so that the same sequence on a CPU gives the same bits. The reference calls
 // libm's expf (src/kernels.cpp:296,326; src/engine.cpp:56); libm is not reproducible
@@ -59,5 +83,22 @@ __device__ __forceinline__ float tree16(const float* l) {
   for (int i = 0; i < 4; ++i) s4[i] = __fadd_rn(s8[i], s8[i + 4]);
   return __fadd_rn(__fadd_rn(s4[0], s4[2]), __fadd_rn(s4[1], s4[3]));
 }
+
+// SwiGLU of one element for the bfloat16 kernels: (g * sigmoid(g)) * u in float32
+// (src/kernels.cpp:291-298) with the hardware's approximate exp2 and reciprocal; the result is
+// rounded to bfloat16 by the caller, which hides their last-place error. One definition for
+// the stand-alone kernel and the fused epilogues, so all of them give the same bits.
+__device__ __forceinline__ float swiglu_one(float g, float u) {
+  const float e = __expf(-g);
+  const float sig = __fdividef(1.0f, __fadd_rn(1.0f, e));
+  return __fmul_rn(__fmul_rn(g, sig), u);
+}
+
+// The tail of RMSNorm for one element, and the scale from the sum of squares: one definition
+// for the stand-alone kernel and the fused one.
+__device__ __forceinline__ float rms_scale(float sumsq, int width, float eps) {
+  return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, static_cast<float>(width)), eps)));
+}
+__device__ __forceinline__ float rms_apply(float x, float inv, float w) { return __fmul_rn(__fmul_rn(x, inv), w); }
 
 }  // namespace bw

@@ -23,6 +23,8 @@ BW_API const char* bw_last_error() { return bw::g_error; }
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                   float* __restrict__ out, int n, int width) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.x;
   const T* src = table + static_cast<size_t>(tokens[r]) * width;
   float* dst = out + static_cast<size_t>(r) * width;
@@ -34,9 +36,9 @@ BW_API int bw_embed_rows(const void* table, int table_is_bf16, const int* tokens
   if (n <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_is_bf16)
-    embed_rows_kernel<<<n, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(table), tokens, out, n, width);
+    bw::launch_pdl(embed_rows_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(table), tokens, out, n, width);
   else
-    embed_rows_kernel<<<n, threads, 0, stream>>>(static_cast<const float*>(table), tokens, out, n, width);
+    bw::launch_pdl(embed_rows_kernel<float>, dim3(n), dim3(threads), 0, stream, static_cast<const float*>(table), tokens, out, n, width);
   return bw::launch_status();
 }
 
@@ -53,6 +55,8 @@ constexpr int kSampleThreads = 512;
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const double* __restrict__ uniform, int* __restrict__ out_token) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int row = blockIdx.x;
   const float* l = logits + static_cast<size_t>(row) * vocab;
   const int tid = threadIdx.x;
@@ -147,7 +151,7 @@ BW_API int bw_sample_rows(const float* logits, int rows, int vocab, const float*
     bw::set_error("sample_rows: vocabulary size %d", vocab);
     return -1;
   }
-  sample_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, temperature, uniform, out_token);
+  bw::launch_pdl(sample_rows_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, logits, vocab, temperature, uniform, out_token);
   return bw::launch_status();
 }
 
@@ -164,6 +168,8 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 
 __global__ void fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab,
                                         const int* __restrict__ slot, unsigned long long* __restrict__ state) {
+  bw::pdl_wait();
+  bw::pdl_launch();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const uint32_t* w = reinterpret_cast<const uint32_t*>(logits + static_cast<size_t>(r) * vocab);
@@ -184,6 +190,6 @@ __global__ void fingerprint_rows_kernel(const float* __restrict__ logits, int ro
 BW_API int bw_fingerprint_rows(const float* logits, int rows, int vocab, const int* slot,
                                unsigned long long* state, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  fingerprint_rows_kernel<<<(rows + 31) / 32, 32, 0, stream>>>(logits, rows, vocab, slot, state);
+  bw::launch_pdl(fingerprint_rows_kernel, dim3((rows + 31) / 32), dim3(32), 0, stream, logits, rows, vocab, slot, state);
   return bw::launch_status();
 }

@@ -157,6 +157,64 @@ class KernelOps:
                        _p(residual), _c_int(m), _c_int(n), _c_int(k), _p(partials), _p(counters),
                        _c_int(int(legacy)), self._stream())
 
+    def linear_norm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor],
+                    norm_weight: torch.Tensor, eps: float, norm_out: torch.Tensor) -> None:
+        """out = residual + x @ w.T in float32, then norm_out = rmsnorm(out) * norm_weight in
+        act_dtype: the same bits as ``linear`` followed by ``rmsnorm``; the serving kernels do
+        it with one launch less when the product runs in split mode."""
+        m, k = x.shape
+        n = w.shape[0]
+        if self.kind == "bf16" and k % 8 == 0:
+            _need(x, self.act_dtype, "linear_norm x", 2)
+            _need(w, self.act_dtype, "linear_norm w", 2)
+            _need(out, torch.float32, "linear_norm out", 2)
+            _need(norm_weight, torch.float32, "linear_norm weight", 1)
+            _need(norm_out, self.act_dtype, "linear_norm norm_out", 2)
+            if w.shape[1] != k or tuple(out.shape) != (m, n) or tuple(norm_out.shape) != (m, n) or \
+                    norm_weight.shape[0] != n:
+                raise KernelError("linear_norm: shapes do not fit")
+            if residual is not None:
+                _need(residual, torch.float32, "linear_norm residual", 2)
+            partials = None
+            if m <= self._split_rows:
+                partials, _ = self._linear_scratch(x.device, n, k)
+            split = partials is not None and bool(self.lib.bw_bf16_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k)))
+            self._call("bw_bf16_linear_tc_norm", _p(x), _p(w), _p(out), _p(residual), _c_int(m), _c_int(n), _c_int(k),
+                       _p(partials), _p(norm_weight), _c_float(eps), _p(norm_out), self._stream(), launches=2)
+            return
+        self.linear(x, w, out, residual=residual)
+        self.rmsnorm(out, norm_weight, eps, norm_out)
+
+    def fuses_swiglu(self, width: int, intermediate: int) -> bool:
+        """Whether ``linear_swiglu`` can take a feed-forward of these sizes (then its gate/up
+        weights are to be interleaved with ``interleave_gate_up``)."""
+        return self.kind == "bf16" and intermediate % 64 == 0 and width % 8 == 0
+
+    @staticmethod
+    def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """Rows in blocks of 64: gate rows 64 b .. 64 b + 63, then the up rows of the same
+        indices, so that a 128-row tile of the product holds both halves of 64 outputs."""
+        inter, k = gate.shape
+        g = gate.reshape(inter // 64, 64, k)
+        u = up.reshape(inter // 64, 64, k)
+        return torch.stack([g, u], dim=1).reshape(2 * inter, k).contiguous()
+
+    def linear_swiglu(self, x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor) -> None:
+        """out[m][i] = silu(x @ gate_i) * (x @ up_i) for interleaved gate/up weights; gate and
+        up are rounded to act_dtype before they are combined, as if they had been stored."""
+        m, k = x.shape
+        n = w_interleaved.shape[0]
+        _need(x, self.act_dtype, "linear_swiglu x", 2)
+        _need(w_interleaved, self.act_dtype, "linear_swiglu w", 2)
+        _need(out, self.act_dtype, "linear_swiglu out", 2)
+        if self.kind != "bf16" or n % 128 or k % 8 or tuple(out.shape) != (m, n // 2) or w_interleaved.shape[1] != k:
+            raise KernelError("linear_swiglu: unsupported shapes or precision")
+        partials = None
+        if m <= self._split_rows:
+            partials, _ = self._linear_scratch(x.device, n, k)
+        self._call("bw_bf16_linear_tc_swiglu", _p(x), _p(w_interleaved), _p(out), _c_int(m), _c_int(n), _c_int(k),
+                   _p(partials), self._stream(), launches=2 if partials is not None else 1)
+
     def _linear_scratch(self, device, n: int, k: int):
         """Scratch of a product that is split along k: chunk sums for up to ``_split_rows``
         rows, and one counter per output tile (zero between launches).  It grows when a

@@ -56,6 +56,7 @@ class Model:
         ops = ops or _default_ops(dtype)
         state = load_state(folder, decoder.param_specs(), _TORCH_DTYPE[dtype], device)
         decoder.load_params(state, dtype, device)
+        decoder.prepare(ops)
         return Model(decoder, dtype, device, ops)
 
     @staticmethod
@@ -87,6 +88,7 @@ class Model:
                                      std, norm_jitter)
             state = state_from_tensors(tensors, specs, tdt, device)
         decoder.load_params(state, dtype, device)
+        decoder.prepare(ops)
         return Model(decoder, dtype, device, ops)
 
     @staticmethod

@@ -91,6 +91,11 @@ class DecoderModel:
         self.head.load_params(state)
         self.dtype, self.device = dtype, device
 
+    def prepare(self, ops) -> None:
+        """Let every part lay out its weights for the kernel library it will run on."""
+        for b in self.blocks:
+            b.prepare(ops)
+
     def param_bytes(self) -> int:
         return self.embedding.param_bytes() + sum(b.param_bytes() for b in self.blocks) + self.head.param_bytes()
 
@@ -115,9 +120,12 @@ class DecoderModel:
         self.embedding.forward(ctx, x)
         for pe in self.position_encodings:
             pe.on_embed(ctx, x)
-        for run in self.schedule:
+        normed = False
+        for i, run in enumerate(self.schedule):
             view = cache_views[run.cache]
             if not run.owns_cache and hasattr(view, "writable"):
                 view = type(view)(**{**view.__dict__, "writable": False})
-            self.blocks[run.block].forward(ctx, x, view)
+            # the norm the next run starts with may ride on this run's last kernel
+            nxt = self.blocks[self.schedule[i + 1].block].mixer_norm if i + 1 < len(self.schedule) else None
+            normed = self.blocks[run.block].forward(ctx, x, view, normed=normed, next_norm=nxt)
         return self.head.forward(ctx, x)

@@ -63,7 +63,9 @@ class GQAAttention(Mixer):
     def param_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
 
-    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView) -> None:
+    fuses_following_norm = True
+
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView, then_norm=None):
         ops, n = ctx.ops, ctx.n
         qkv = ctx.workspace.rows("qkv", n, self.q_dim + 2 * self.kv_dim, ctx.act_dtype)
         ops.linear(xn, self.w_qkv, qkv)
@@ -74,7 +76,12 @@ class GQAAttention(Mixer):
         attn = ctx.workspace.rows("attn", n, self.q_dim, ctx.act_dtype)
         ops.attention(qkv, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.pos, attn, self.heads,
                       self.kv_heads, self.head_dim, self.window or 0, ctx.max_keys, self.scale, batch=ctx)
+        if then_norm is not None and hasattr(then_norm[0], "fused_arguments"):
+            weight, eps = then_norm[0].fused_arguments()
+            ops.linear_norm(attn, self.w_o, x, x, weight, eps, then_norm[1])
+            return True
         ops.linear(attn, self.w_o, x, residual=x)
+        return False
 
 
 register_mixer("gqa_attention", GQAAttention)

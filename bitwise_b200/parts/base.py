@@ -145,6 +145,11 @@ class Part:
     def param_bytes(self) -> int:
         return 0
 
+    def prepare(self, ops) -> None:
+        """Called once after the parameters are loaded, with the kernel library the model
+        will run on: a part may lay its weights out the way those kernels want them."""
+        pass
+
 
 class Norm(Part):
     def forward(self, ctx: StepContext, x: torch.Tensor, out: torch.Tensor,
@@ -174,6 +179,11 @@ class Mixer(Part):
     def cache_need(self):
         return None
 
+    # A mixer or feed-forward whose last operation can also apply the norm that follows it
+    # sets this to True and accepts ``then_norm=(norm, out)`` in forward: after adding into x
+    # it writes ``norm(x)`` into ``out`` and returns True (same bits as the separate norm).
+    fuses_following_norm = False
+
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache) -> None:
         """Read the normed rows ``xn`` (act dtype), add the mixer's output into the float32
         stream ``x`` in place.  ``cache`` is the view that fits ``cache_need``."""
@@ -181,6 +191,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    fuses_following_norm = False  # see Mixer
+
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
         """Read ``xn``, add the feed-forward's output into ``x`` in place."""
         raise NotImplementedError

@@ -18,8 +18,9 @@ class SwiGLU(FeedForward):
     def __init__(self, width: int, intermediate: int, names=("gate_proj", "up_proj", "down_proj")):
         self.width, self.intermediate = width, intermediate
         self.names = names
-        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_gate_up: Optional[torch.Tensor] = None  # rows [gate | up], or interleaved when fused
         self.w_down: Optional[torch.Tensor] = None
+        self.fused = False  # gate/up product and SwiGLU in one kernel
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
         g, u, d = self.names
@@ -35,13 +36,31 @@ class SwiGLU(FeedForward):
     def param_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
-    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
+    def prepare(self, ops) -> None:
+        """Kernels that apply SwiGLU in the epilogue of the gate/up product want the two
+        matrices interleaved in blocks of 64 rows."""
+        if not self.fused and getattr(ops, "fuses_swiglu", None) and ops.fuses_swiglu(self.width, self.intermediate):
+            gate, up = self.w_gate_up[:self.intermediate], self.w_gate_up[self.intermediate:]
+            self.w_gate_up = ops.interleave_gate_up(gate, up)
+            self.fused = True
+
+    fuses_following_norm = True
+
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, then_norm=None):
         ops, n = ctx.ops, ctx.n
-        gate_up = ctx.workspace.rows("gate_up", n, 2 * self.intermediate, ctx.act_dtype)
-        ops.linear(xn, self.w_gate_up, gate_up)
         h = ctx.workspace.rows("ffn_h", n, self.intermediate, ctx.act_dtype)
-        ops.swiglu(gate_up, h)
+        if self.fused:
+            ops.linear_swiglu(xn, self.w_gate_up, h)
+        else:
+            gate_up = ctx.workspace.rows("gate_up", n, 2 * self.intermediate, ctx.act_dtype)
+            ops.linear(xn, self.w_gate_up, gate_up)
+            ops.swiglu(gate_up, h)
+        if then_norm is not None and hasattr(then_norm[0], "fused_arguments"):
+            weight, eps = then_norm[0].fused_arguments()
+            ops.linear_norm(h, self.w_down, x, x, weight, eps, then_norm[1])
+            return True
         ops.linear(h, self.w_down, x, residual=x)
+        return False
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -34,6 +34,13 @@ class CpuOps:
             y = residual + y
         out.copy_(y.to(out.dtype))
 
+    def linear_norm(self, x, w, out, residual, norm_weight, eps, norm_out):
+        self.linear(x, w, out, residual=residual)
+        self.rmsnorm(out, norm_weight, eps, norm_out)
+
+    def fuses_swiglu(self, width, intermediate):
+        return False
+
     def rope_cache(self, qkv, pos, row_seq, cos, sin, block_table, kcache, vcache, heads, kv_heads, head_dim,
                    write_kv=True):
         n = qkv.shape[0]
