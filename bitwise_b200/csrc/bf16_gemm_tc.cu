@@ -194,65 +194,6 @@ __device__ __forceinline__ float ordered_chunk_sum(const float* __restrict__ par
   return v;
 }
 
-// Split mode followed by an RMSNorm of the result: one block per row adds the chunk sums and
-// the residual, stores the float32 row, and normalises it with exactly the arithmetic of the
-// stand-alone RMSNorm kernel (thread t sums elements t, t + 256, ... in order, shuffle tree,
-// warps in order), so that fusing changes no bit.
-__global__ void __launch_bounds__(256)
-reduce_norm_kernel(const float* __restrict__ partials, int num_chunks, float* Y, const float* residual, int M, int N,
-                   const float* __restrict__ norm_w, float eps, __nv_bfloat16* __restrict__ norm_out) {
-  bw::pdl_wait();
-  bw::pdl_launch();
-  const int r = blockIdx.x;
-  const size_t plane = static_cast<size_t>(M) * N;
-  __shared__ float red[8];
-  float acc = 0.0f;
-  // four outputs of this thread at a time, so that 32 loads are in flight; the additions of
-  // every output stay in ascending chunk order, and the squares are summed in element order
-  for (int i0 = threadIdx.x; i0 < N; i0 += 4 * 256) {
-    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int c0 = 0; c0 < num_chunks; c0 += 8) {
-      float p[4][8];
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int i = i0 + q * 256;
-          p[q][e] = (i < N && c0 + e < num_chunks)
-                        ? __ldcg(partials + (c0 + e) * plane + static_cast<size_t>(r) * N + i)
-                        : 0.0f;
-        }
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          if (c0 + e < num_chunks) v[q] = (c0 + e == 0) ? p[q][e] : v[q] + p[q][e];
-    }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int i = i0 + q * 256;
-      if (i >= N) break;
-      const size_t o = static_cast<size_t>(r) * N + i;
-      float x = v[q];
-      if (residual) x = residual[o] + x;
-      Y[o] = x;
-      acc = __fmaf_rn(x, x, acc);
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  float ss = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) ss = __fadd_rn(ss, red[i]);
-  const float inv = bw::rms_scale(ss, N, eps);
-  for (int i = threadIdx.x; i < N; i += 256) {
-    const size_t o = static_cast<size_t>(r) * N + i;
-    norm_out[o] = __float2bfloat16_rn(bw::rms_apply(Y[o], inv, norm_w[i]));
-  }
-}
-
 // Split mode of the gate/up product with SwiGLU: weights are interleaved in blocks of 64 rows
 // (64 gate rows, then the 64 up rows of the same indices), so output c of a row takes the
 // gate at column 128 (c / 64) + c % 64 and the up value 64 columns further. Gate and up are
@@ -323,19 +264,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
-  // barriers and tensor memory are set up; only now wait for the kernel before this one
-  bw::pdl_wait();
+  // Barriers and tensor memory are set up. The next kernel may be set up from now on; this
+  // one waits for the kernel before it where it first touches data that kernel may have
+  // written: the loader before its first x tile, the epilogue before it reads or writes.
   bw::pdl_launch();
   const uint32_t tmem_base = bars->tmem_base;
 
   if (warp == 0) {
     if (lane == 0) {
+      // The weights do not depend on the kernel before this one: the W tiles of the first
+      // round of the ring are requested at once, the wait for the previous kernel comes
+      // after, then the x tiles of those stages follow. Later stages load both together.
       uint32_t it = 0;  // k-tiles issued so far, over all output tiles of this block
-      bool ok = true;
+      bool ok = true, waited = false;
       for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
         const int m0 = item_m0(tile), n0 = item_n0(tile);
         const int kt0 = item_c0(tile) * kTilesPerChunk, kt1 = min(num_tiles, item_c1(tile) * kTilesPerChunk);
-        for (int kt = kt0; kt < kt1; ++kt, ++it) {
+        int kt = kt0;
+        if (!waited) {  // first item of this block
+          const int early = min(kt1 - kt0, kStages);
+          for (int e = 0; e < early; ++e) {
+            unsigned char* a = tiles + e * kStageBytes;
+            mbar_expect_tx(&bars->full[e], kStageBytes);
+            tma_load_2d(a + kTileBytesX, &map_w, (kt0 + e) * BK, n0, &bars->full[e]);
+          }
+          bw::pdl_wait();
+          waited = true;
+          for (int e = 0; e < early; ++e) tma_load_2d(tiles + e * kStageBytes, &map_x, (kt0 + e) * BK, m0, &bars->full[e]);
+          kt += early;
+          it += early;
+        }
+        for (; kt < kt1; ++kt, ++it) {
           const int s = it % kStages;
           const uint32_t round = it / kStages;
           if (round > 0 && !mbar_wait(&bars->empty[s], (round - 1) & 1, failed)) {
@@ -386,6 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else {
     // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    bw::pdl_wait();
     const int quarter = warp & 3;
     const int et = quarter * 32 + lane;  // 0..127: this thread's row of the tile
     float total[BN];
@@ -577,12 +537,9 @@ int sm_count_of_device() {
   return sm_count;
 }
 
-// What follows the product: nothing, an RMSNorm of the float32 result, or SwiGLU.
+// What follows the product: nothing, or SwiGLU.
 struct Fused {
-  int mode = 0;  // 0 none, 1 rmsnorm of y into norm_out, 2 swiglu (y is [m][n / 2] bfloat16)
-  const float* norm_w = nullptr;
-  float eps = 0.0f;
-  __nv_bfloat16* norm_out = nullptr;
+  int mode = 0;  // 0 none, 2 swiglu (y is [m][n / 2] bfloat16)
 };
 
 template <bool SPLIT, int A_ROWS, int EPI>
@@ -613,10 +570,7 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
                                                                        error_word, partials);
   if (SPLIT) {
     const size_t outputs = static_cast<size_t>(m) * n;
-    if (fused.mode == 1)
-      bw::launch_pdl(reduce_norm_kernel, dim3(m), dim3(256), 0, stream, partials, chunks, static_cast<float*>(y), residual, m, n, fused.norm_w,
-                                                fused.eps, fused.norm_out);
-    else if (fused.mode == 2)
+    if (fused.mode == 2)
       bw::launch_pdl(reduce_swiglu_kernel, dim3(static_cast<unsigned>((outputs / 2 + 255) / 256)), dim3(256), 0, stream, 
           partials, chunks, static_cast<__nv_bfloat16*>(y), m, n);
     else
@@ -650,9 +604,6 @@ int ensure_error_word() {
 
 }  // namespace
 
-BW_API int bw_bf16_rmsnorm(const float* x, const float* weight, __nv_bfloat16* y, const int* rows, int n, int width,
-                           float eps, cudaStream_t stream);
-
 BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
                              const float* residual, int m, int n, int k, float* partials, int* counters,
                              cudaStream_t stream) {
@@ -667,26 +618,6 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
   const Fused none;
   if (split) return launch_tc_rows<true, 0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, partials, none, stream);
   return launch_tc_rows<false, 0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, nullptr, none, stream);
-}
-
-// y = residual + x W^T (float32), then norm_out = RMSNorm(y) * norm_w (bfloat16): the same
-// bits as the product followed by the stand-alone norm kernel, one launch less in split mode.
-BW_API int bw_bf16_linear_tc_norm(const __nv_bfloat16* x, const __nv_bfloat16* w, float* y, const float* residual, int m,
-                                  int n, int k, float* partials, const float* norm_w, float eps,
-                                  __nv_bfloat16* norm_out, cudaStream_t stream) {
-  if (m <= 0 || n <= 0) return 0;
-  if (!bw_bf16_linear_tc_usable(x, w, k)) {
-    bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
-    return -1;
-  }
-  if (const int rc = ensure_error_word()) return rc;
-  const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
-  Fused f;
-  f.mode = 1, f.norm_w = norm_w, f.eps = eps, f.norm_out = norm_out;
-  if (split) return launch_tc_rows<true, 0>(x, w, y, 1, residual, m, n, k, g_error_flag, partials, f, stream);
-  const int rc = launch_tc_rows<false, 0>(x, w, y, 1, residual, m, n, k, g_error_flag, nullptr, Fused(), stream);
-  if (rc) return rc;
-  return bw_bf16_rmsnorm(y, norm_w, norm_out, nullptr, m, n, eps, stream);
 }
 
 // h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows

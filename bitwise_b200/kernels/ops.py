@@ -160,28 +160,9 @@ class KernelOps:
     def linear_norm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor],
                     norm_weight: torch.Tensor, eps: float, norm_out: torch.Tensor) -> None:
         """out = residual + x @ w.T in float32, then norm_out = rmsnorm(out) * norm_weight in
-        act_dtype: the same bits as ``linear`` followed by ``rmsnorm``; the serving kernels do
-        it with one launch less when the product runs in split mode."""
-        m, k = x.shape
-        n = w.shape[0]
-        if self.kind == "bf16" and k % 8 == 0:
-            _need(x, self.act_dtype, "linear_norm x", 2)
-            _need(w, self.act_dtype, "linear_norm w", 2)
-            _need(out, torch.float32, "linear_norm out", 2)
-            _need(norm_weight, torch.float32, "linear_norm weight", 1)
-            _need(norm_out, self.act_dtype, "linear_norm norm_out", 2)
-            if w.shape[1] != k or tuple(out.shape) != (m, n) or tuple(norm_out.shape) != (m, n) or \
-                    norm_weight.shape[0] != n:
-                raise KernelError("linear_norm: shapes do not fit")
-            if residual is not None:
-                _need(residual, torch.float32, "linear_norm residual", 2)
-            partials = None
-            if m <= self._split_rows:
-                partials, _ = self._linear_scratch(x.device, n, k)
-            split = partials is not None and bool(self.lib.bw_bf16_linear_tc_splits(_c_int(m), _c_int(n), _c_int(k)))
-            self._call("bw_bf16_linear_tc_norm", _p(x), _p(w), _p(out), _p(residual), _c_int(m), _c_int(n), _c_int(k),
-                       _p(partials), _p(norm_weight), _c_float(eps), _p(norm_out), self._stream(), launches=2)
-            return
+        act_dtype.  Two kernels today (a fused variant for small batches was slower than
+        the pair: one block per row cannot hide the latency of adding the chunk sums); parts
+        call this one name so that a fused kernel can take its place."""
         self.linear(x, w, out, residual=residual)
         self.rmsnorm(out, norm_weight, eps, norm_out)
 
