@@ -209,20 +209,20 @@ def run_e2e(model, batch, ctx, steps, warmup, page):
     import torch
     from bitwise_b200 import Engine, EngineConfig, SamplingParams
     c = model.config
-    total = ctx + warmup + steps + 2
+    total = ctx + warmup + steps + batch + 16
     pages_per = (total + page - 1) // page
     eng = Engine(model, EngineConfig(num_blocks=pages_per * batch, block_size=page, max_batched_tokens=2048,
                                      max_num_seqs=batch, fingerprint_logits=False, max_model_len=pages_per * page))
     rng = np.random.default_rng(2)
-    sp = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + 1, ignore_eos=True)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + batch + 8, ignore_eos=True)
     for b in range(batch):
         eng.add_request(rng.integers(0, c.vocab_size, ctx - 1).tolist(), sp)
     guard = 0
-    while eng.stats.generated_tokens < batch:  # until every request has left its prompt behind
+    while eng.stats.prefill_tokens < batch * (ctx - 1):  # until every request has left its prompt behind
         eng.step()
         guard += 1
         assert guard < 10000
-    for _ in range(warmup - 1):
+    for _ in range(max(warmup, 3)):  # decode steps only from here on; the first ones build the step's graph
         eng.step()
     torch.cuda.synchronize()
     g0 = eng.stats.generated_tokens

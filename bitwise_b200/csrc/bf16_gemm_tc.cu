@@ -30,11 +30,9 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int BM = 128, BN = 128, BK = 64;  // BN: columns one epilogue thread carries; a wide tile has 2 BN
 constexpr int kChunk = 512;
 constexpr int kTilesPerChunk = kChunk / BK;
-constexpr int kThreads = 192;
-constexpr int kTileBytesW = BN * BK * 2;       // 16 KB of weights per stage
 constexpr int kSmemBudget = 200 * 1024;        // ring of stages (plus barriers) per block
 
 // The x tile of a stage holds A_ROWS rows: 128 for large batches, fewer for small ones. The
@@ -43,8 +41,9 @@ constexpr int kSmemBudget = 200 * 1024;        // ring of stages (plus barriers)
 // allocation). Rows are independent in a matrix product, so this only fills accumulator
 // lanes that are never read, and it leaves room for more stages: a decode step is bound by
 // how many bytes of weights an SM keeps in flight.
-template <int A_ROWS>
+template <int A_ROWS, int BNT>
 struct Ring {
+  static constexpr int kTileBytesW = BNT * BK * 2;  // 16 or 32 KB of weights per stage
   static constexpr int kTileBytesX = A_ROWS * BK * 2;
   static constexpr int kStageBytes = kTileBytesX + kTileBytesW;
   static constexpr int kStages = (kSmemBudget - (BM - A_ROWS) * BK * 2) / kStageBytes > 12
@@ -54,7 +53,6 @@ struct Ring {
   static constexpr int kRingBytes = kStages * kStageBytes + kPadBytes;
 };
 constexpr int kMaxStages = 12;
-constexpr int kTmemCols = 256;  // two accumulators of 128 columns
 constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
 
 struct __align__(8) Barriers {
@@ -122,15 +120,16 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
 
 // Instruction descriptor of kind::f16: D float32 (bits 4-5 = 1), A and B bfloat16 (bits 7-9
 // and 10-12 = 1), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                (static_cast<uint32_t>(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -215,23 +214,31 @@ __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num
 
 // EPI 0: y = (residual +) product.  EPI 1 (whole mode only): the product is the interleaved
 // gate/up projection and y[m][n / 2] = SwiGLU of it (bfloat16).
-template <bool SPLIT, int A_ROWS, int EPI>
-__global__ void __launch_bounds__(kThreads)
+//
+// WIDE: the output tile is 128 x 256 instead of 128 x 128 and eight epilogue warps share it
+// (each still one row x 128 columns per thread). A wide tile needs a third less operand
+// traffic per flop; large batches are bound by how fast the SM can take in operands.
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE>
+__global__ void __launch_bounds__(WIDE ? 320 : 192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
                int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzled tiles want 1024-byte alignment
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int kStages = Ring<A_ROWS>::kStages;
-  constexpr int kStageBytes = Ring<A_ROWS>::kStageBytes;
-  constexpr int kTileBytesX = Ring<A_ROWS>::kTileBytesX;
-  Barriers* bars = reinterpret_cast<Barriers*>(tiles + Ring<A_ROWS>::kRingBytes);
+  constexpr int BNT = WIDE ? 2 * BN : BN;
+  constexpr int kEpiWarps = WIDE ? 8 : 4;
+  constexpr int kTmemColsT = 2 * BNT;  // two accumulators
+  using RingT = Ring<A_ROWS, BNT>;
+  constexpr int kStages = RingT::kStages;
+  constexpr int kStageBytes = RingT::kStageBytes;
+  constexpr int kTileBytesX = RingT::kTileBytesX;
+  Barriers* bars = reinterpret_cast<Barriers*>(tiles + RingT::kRingBytes);
   volatile uint32_t* failed = &bars->failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = (K + BK - 1) / BK;          // k-tiles of one output tile
   const int num_chunks = (K + kChunk - 1) / kChunk;
-  const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
+  const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BNT - 1) / BNT;
   // Work items are dealt round-robin to the resident blocks and the three roles below walk
   // the same sequence of items. Whole mode: item t is the output tile with rows of block
   // t % m_blocks and columns of block t / m_blocks, all its chunks (blocks that run at the same
@@ -239,7 +246,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // t % num_chunks of the output tile with columns of block t / num_chunks.
   const int out_tiles = SPLIT ? n_blocks * num_chunks : m_blocks * n_blocks;
   auto item_m0 = [&](int t) { return SPLIT ? 0 : (t % m_blocks) * BM; };
-  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * BN : (t / m_blocks) * BN; };
+  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * BNT : (t / m_blocks) * BNT; };
   auto item_c0 = [&](int t) { return SPLIT ? t % num_chunks : 0; };
   auto item_c1 = [&](int t) { return SPLIT ? t % num_chunks + 1 : num_chunks; };
 
@@ -250,14 +257,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->acc_full[b], 1);
-      mbar_init(&bars->acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&bars->acc_empty[b], kEpiWarps);  // one arrival per epilogue warp
     }
     bars->failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // this warp owns the tensor-memory allocation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
-                 "n"(kTmemCols)
+                 "n"(kTmemColsT)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -321,7 +328,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             break;
           }
           fence_after_sync();
-          const uint32_t d = tmem_base + buf * BN;
+          const uint32_t d = tmem_base + buf * BNT;
           const int t_begin = c * kTilesPerChunk, t_end = min(num_tiles, t_begin + kTilesPerChunk);
           for (int kt = t_begin; kt < t_end; ++kt, ++it) {
             const int s = it % kStages;
@@ -335,7 +342,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               // 16 k-elements are 32 bytes: the start address field moves by 2 (units of 16 bytes)
-              umma(d, adesc + 2 * k, bdesc + 2 * k, (kt > t_begin || k > 0) ? 1u : 0u);
+              umma(d, adesc + 2 * k, bdesc + 2 * k, instr_desc(BNT), (kt > t_begin || k > 0) ? 1u : 0u);
             }
             umma_commit(&bars->empty[s]);  // the stage may be refilled once these MMAs are done
           }
@@ -348,13 +355,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     bw::pdl_wait();
     const int quarter = warp & 3;
     const int et = quarter * 32 + lane;  // 0..127: this thread's row of the tile
+    const int coff = WIDE ? ((warp - 2) >> 2) * BN : 0;  // this warp's half of a wide tile
     float total[BN];
     uint32_t gc = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
-      const int m0 = item_m0(tile), n0 = item_n0(tile);
+      const int m0 = item_m0(tile), n0 = item_n0(tile) + coff;
       const int row = m0 + et;
-      const int cols = min(BN, N - n0);
+      const int cols = min(BN, N - n0);  // may be <= 0 for the second half of a last, partial wide tile
       for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
         const int buf = gc & 1;
         if (!mbar_wait(&bars->acc_full[buf], (gc >> 1) & 1, failed)) {
@@ -363,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         fence_after_sync();
         if (!SPLIT || quarter * 32 < M) {  // in split mode warps whose rows are all padding read nothing
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BNT + coff;
 #pragma unroll
           for (int g = 0; g < BN / 16; ++g) {
             float v[16];
@@ -395,7 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         continue;
       }
-      if (row >= M) continue;
+      if (row >= M || cols <= 0) continue;
       if (EPI == 1) {
         // columns 0..63 of the tile are gate rows, 64..127 the up rows of the same indices
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + static_cast<size_t>(row) * (N / 2) + n0 / 2;
@@ -457,7 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   if (warp == 1) {
     __syncwarp();
     fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemColsT) : "memory");
   }
   if (threadIdx.x == 0 && bars->failed) atomicExch(error_flag, 1);
 }
@@ -542,15 +550,16 @@ struct Fused {
   int mode = 0;  // 0 none, 2 swiglu (y is [m][n / 2] bfloat16)
 };
 
-template <bool SPLIT, int A_ROWS, int EPI>
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE>
 int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m, int n,
               int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream) {
-  constexpr int smem = Ring<A_ROWS>::kRingBytes + sizeof(Barriers) + 1024;
+  constexpr int BNT = WIDE ? 2 * BN : BN;
+  constexpr int smem = Ring<A_ROWS, BNT>::kRingBytes + sizeof(Barriers) + 1024;
   static_assert(smem <= 227 * 1024, "ring does not fit");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e =
-        cudaFuncSetAttribute(gemm_tc_kernel<SPLIT, A_ROWS, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
       bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
       return static_cast<int>(e);
@@ -558,15 +567,15 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
     configured = true;
   }
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, x, m, k, A_ROWS) || !make_map(&map_w, w, n, k)) {
+  if (!make_map(&map_x, x, m, k, A_ROWS) || !make_map(&map_w, w, n, k, BNT)) {
     bw::set_error("linear (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
     return -1;
   }
-  const int n_blocks = (n + BN - 1) / BN, m_blocks = (m + BM - 1) / BM, chunks = (k + kChunk - 1) / kChunk;
+  const int n_blocks = (n + BNT - 1) / BNT, m_blocks = (m + BM - 1) / BM, chunks = (k + kChunk - 1) / kChunk;
   const long long items = SPLIT ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
   const int sms = sm_count_of_device();
   const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
-  bw::launch_pdl(gemm_tc_kernel<SPLIT, A_ROWS, EPI>, dim3(grid), dim3(kThreads), smem, stream, map_x, map_w, y, y_is_f32, residual, m, n, k,
+  bw::launch_pdl(gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE>, dim3(grid), dim3(WIDE ? 320 : 192), smem, stream, map_x, map_w, y, y_is_f32, residual, m, n, k,
                                                                        error_word, partials);
   if (SPLIT) {
     const size_t outputs = static_cast<size_t>(m) * n;
@@ -584,10 +593,15 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
 template <bool SPLIT, int EPI>
 int launch_tc_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m,
                    int n, int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream) {
-  if (m <= 16) return launch_tc<SPLIT, 16, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  if (m <= 32) return launch_tc<SPLIT, 32, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  if (m <= 64) return launch_tc<SPLIT, 64, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  return launch_tc<SPLIT, 128, EPI>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  if (m <= 16)
+    return launch_tc<SPLIT, 16, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  if (m <= 32)
+    return launch_tc<SPLIT, 32, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  if (m <= 64)
+    return launch_tc<SPLIT, 64, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  if (SPLIT || m <= 128)
+    return launch_tc<SPLIT, 128, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+  return launch_tc<false, 128, EPI, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
 }
 
 int ensure_error_word() {
