@@ -132,17 +132,30 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
     }
   }
   float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+  // a tile that lies wholly inside both rows' ranges needs no per-key test (same values either way)
+  const bool inside = j0 + kTileKV - 1 <= min(pos_lo, pos_hi) && j0 >= max(first_lo, first_hi);
+  if (inside) {
 #pragma unroll
-  for (int nb = 0; nb < kTileKV / 8; ++nb)
+    for (int nb = 0; nb < kTileKV / 8; ++nb)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1);
-      const bool hi = e >= 2;
-      const bool ok = hi ? (j <= pos_hi && j >= first_hi) : (j <= pos_lo && j >= first_lo);
-      const float v = ok ? __fmul_rn(s[nb][e], scale_log2) : -INFINITY;
-      s[nb][e] = v;
-      if (hi) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
-    }
+      for (int e = 0; e < 4; ++e) {
+        const float v = __fmul_rn(s[nb][e], scale_log2);
+        s[nb][e] = v;
+        if (e >= 2) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
+      }
+  } else {
+#pragma unroll
+    for (int nb = 0; nb < kTileKV / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+        const bool hi = e >= 2;
+        const bool ok = hi ? (j <= pos_hi && j >= first_hi) : (j <= pos_lo && j >= first_lo);
+        const float v = ok ? __fmul_rn(s[nb][e], scale_log2) : -INFINITY;
+        s[nb][e] = v;
+        if (hi) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
+      }
+  }
   tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
   tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
   tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
@@ -186,17 +199,25 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
   r.sum_hi = tsum_hi;
 }
 
-// cp.async of `count` threads: one tile of keys and values from the paged cache into shared
-// memory; keys at or beyond kv_hi are zero-filled.
+// cp.async of `count` threads: one tile of keys and values from the
+// paged cache into shared memory; keys at or beyond kv_hi are zero-filled. A thread keeps its
+// 16-byte piece and walks the keys, so that the page lookup happens once per key and thread;
+// page_shift is log2(page) when the page size is a power of two, else -1.
 __device__ __forceinline__ void load_kv_tile(unsigned char* sk, unsigned char* sv, const __nv_bfloat16* kcache,
-                                             const __nv_bfloat16* vcache, const int* table, int page, int kv_heads, int g,
-                                             int j0, int kv_hi, int t, int count) {
-  for (int idx = t; idx < kTileKV * kPieces; idx += count) {
-    const int key = idx / kPieces, piece = idx - key * kPieces;
+                                             const __nv_bfloat16* vcache, const int* table, int page, int page_shift,
+                                             int kv_heads, int g, int j0, int kv_hi, int t, int count) {
+  const int piece = t % kPieces;
+  const int keys_per_pass = count / kPieces;  // threads beyond a whole number of keys sit out
+  if (t >= keys_per_pass * kPieces) return;
+  for (int key = t / kPieces; key < kTileKV; key += keys_per_pass) {
     const int j = j0 + key;
     const bool ok = j < kv_hi;
     size_t off = 0;
-    if (ok) off = ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + (j % page)) * HD + piece * 8;
+    if (ok) {
+      const int blk = page_shift >= 0 ? j >> page_shift : j / page;
+      const int slot = page_shift >= 0 ? j & (page - 1) : j - blk * page;
+      off = ((static_cast<size_t>(table[blk]) * kv_heads + g) * page + slot) * HD + piece * 8;
+    }
     cp_async16(smem_u32(sk + piece_offset(key, piece)), kcache + off, ok);
     cp_async16(smem_u32(sv + piece_offset(key, piece)), vcache + off, ok);
   }
@@ -213,7 +234,7 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
                        const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
                        const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
                        const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
-                       int kv_heads, int page, int window, float scale_log2) {
+                       int kv_heads, int page, int page_shift, int window, float scale_log2) {
   bw::pdl_wait();
   bw::pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
@@ -242,7 +263,8 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   const int ntiles = (kv_hi - kv_lo + kTileKV - 1) / kTileKV;
   auto stage_k = [&](int st) { return smem + kQBytes + st * 2 * kKVBytes; };
 
-  load_kv_tile(stage_k(0), stage_k(0) + kKVBytes, kcache, vcache, table, page, kv_heads, g, kv_lo, kv_hi, tid, kThreads);
+  load_kv_tile(stage_k(0), stage_k(0) + kKVBytes, kcache, vcache, table, page, page_shift, kv_heads, g, kv_lo, kv_hi, tid,
+               kThreads);
   cp_async_commit();
 
   const int m_lo = warp * 16 + (lane >> 2), m_hi = m_lo + 8;
@@ -261,7 +283,7 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
 
   for (int t = 0; t < ntiles; ++t) {
     if (t + 1 < ntiles)
-      load_kv_tile(stage_k((t + 1) & 1), stage_k((t + 1) & 1) + kKVBytes, kcache, vcache, table, page, kv_heads, g,
+      load_kv_tile(stage_k((t + 1) & 1), stage_k((t + 1) & 1) + kKVBytes, kcache, vcache, table, page, page_shift, kv_heads, g,
                    kv_lo + (t + 1) * kTileKV, kv_hi, tid, kThreads);
     cp_async_commit();
     cp_async_wait<1>();
@@ -314,7 +336,7 @@ __global__ void __launch_bounds__(kSplitWarps * 32)
 attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, const __nv_bfloat16* __restrict__ kcache,
                        const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                        const int* __restrict__ row_seq, const int* __restrict__ pos, int heads, int kv_heads, int page,
-                       int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
+                       int page_shift, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
   bw::pdl_wait();
   bw::pdl_launch();
   extern __shared__ __align__(128) unsigned char smem[];
@@ -338,7 +360,7 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   const bool mine = t * kTileKV <= p && (t + 1) * kTileKV > first;  // the tile holds a key of the row's range
   unsigned char* sk = smem + kSplitQBytes + warp * 2 * kKVBytes;
   unsigned char* sv = sk + kKVBytes;
-  if (mine) load_kv_tile(sk, sv, kcache, vcache, table, page, kv_heads, g, t * kTileKV, p + 1, lane, 32);
+  if (mine) load_kv_tile(sk, sv, kcache, vcache, table, page, page_shift, kv_heads, g, t * kTileKV, p + 1, lane, 32);
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();  // Q was loaded by all warps
@@ -433,6 +455,9 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
     return -1;
   }
   const float scale_log2 = scale * 1.44269504088896341f;
+  int page_shift = -1;
+  for (int b = 0; b < 30; ++b)
+    if ((1 << b) == page) page_shift = b;
   const int key_tiles = (max_keys + kTileKV - 1) / kTileKV;
   constexpr int split_smem = kSplitQBytes + kSplitWarps * 2 * kKVBytes;
   // decode steps (every query tile a single row) over more than a few key tiles run split, if
@@ -450,7 +475,7 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
       configured[1] = true;
     }
     bw::launch_pdl(attention_split_kernel, dim3(dim3(n, kv_heads, (key_tiles + kSplitWarps - 1) / kSplitWarps)), dim3(kSplitWarps * 32), split_smem, stream, qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, heads,
-                                       kv_heads, page, window, scale_log2, scratch, key_tiles);
+                                       kv_heads, page, page_shift, window, scale_log2, scratch, key_tiles);
     bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(HD), 0, stream, scratch, key_tiles, pos, out, out_stride, heads, window);
   } else {
     constexpr int smem = kQBytes + kStages * 2 * kKVBytes;
@@ -464,7 +489,7 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
     }
     bw::launch_pdl(attention_whole_kernel, dim3(dim3(num_tiles, kv_heads)), dim3(kThreads), smem, stream, 
         qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out,
-        out_stride, heads, kv_heads, page, window, scale_log2);
+        out_stride, heads, kv_heads, page, page_shift, window, scale_log2);
   }
   return bw::launch_status();
 }

@@ -41,9 +41,27 @@ rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __
 // ---------------------------------------------------------------------------------------
 // Rotary encoding (rotate-half pairs, src/kernels.cpp:273-289) in float32 on bfloat16
 // values, rounded once; then K and V of the row go into the paged cache
-// (src/model.cpp:285-297). With a null table nothing is rotated. One thread per pair of
-// elements: blockIdx.x is the row, blockIdx.y * blockDim.x + threadIdx.x the pair, first the
-// pairs of the query heads, then those of the key heads (which also carry the values).
+// (src/model.cpp:285-297). With a null table nothing is rotated. One thread per 8 pairs
+// (16-byte accesses): blockIdx.x is the row, blockIdx.y * blockDim.x + threadIdx.x the item,
+// first the items of the query heads, then those of the key heads (which also carry the
+// values). The head size is a multiple of 16, so half a head is a whole number of items.
+__device__ __forceinline__ void rotate8(const uint4& a, const uint4& b, const float* c, const float* s, uint4& ra,
+                                        uint4& rb) {
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+  __nv_bfloat162* oa = reinterpret_cast<__nv_bfloat162*>(&ra);
+  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 x1 = __bfloat1622float2(a2[e]), x2 = __bfloat1622float2(b2[e]);
+    const float c0 = c[2 * e], c1 = c[2 * e + 1], s0 = s[2 * e], s1 = s[2 * e + 1];
+    oa[e] = __floats2bfloat162_rn(__fsub_rn(__fmul_rn(x1.x, c0), __fmul_rn(x2.x, s0)),
+                                  __fsub_rn(__fmul_rn(x1.y, c1), __fmul_rn(x2.y, s1)));
+    ob[e] = __floats2bfloat162_rn(__fadd_rn(__fmul_rn(x2.x, c0), __fmul_rn(x1.x, s0)),
+                                  __fadd_rn(__fmul_rn(x2.y, c1), __fmul_rn(x1.y, s1)));
+  }
+}
+
 __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const int* __restrict__ pos,
                                        const int* __restrict__ row_seq, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, const int* __restrict__ block_table,
@@ -52,43 +70,47 @@ __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const
   bw::pdl_wait();
   bw::pdl_launch();
   const int r = blockIdx.x;
-  const int half = hd >> 1;
+  const int half = hd >> 1, per_head = half >> 3;  // items of 8 pairs per head
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
-  const int q_items = heads * half, k_items = write_kv ? kv_heads * half : 0;
+  const int q_items = heads * per_head, k_items = write_kv ? kv_heads * per_head : 0;
   if (item >= q_items + k_items) return;
   const int p = pos[r];
   __nv_bfloat16* row = qkv + static_cast<size_t>(r) * row_stride;
   const bool is_q = item < q_items;
   const int local = is_q ? item : item - q_items;
-  const int h = local / half, i = local - h * half;
-  float c = 1.0f, s = 0.0f;
+  const int h = local / per_head, i = (local - h * per_head) * 8;
+  float c[8], s[8];
   if (cos_t) {
-    c = cos_t[static_cast<size_t>(p) * half + i];
-    s = sin_t[static_cast<size_t>(p) * half + i];
+    const float4* c4 = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * half + i);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * half + i);
+    *reinterpret_cast<float4*>(c) = c4[0], *reinterpret_cast<float4*>(c + 4) = c4[1];
+    *reinterpret_cast<float4*>(s) = s4[0], *reinterpret_cast<float4*>(s + 4) = s4[1];
   }
   if (is_q) {
     if (!cos_t) return;
-    __nv_bfloat16* v = row + h * hd;
-    const float x1 = __bfloat162float(v[i]), x2 = __bfloat162float(v[i + half]);
-    v[i] = __float2bfloat16_rn(x1 * c - x2 * s);
-    v[i + half] = __float2bfloat16_rn(x2 * c + x1 * s);
+    __nv_bfloat16* v = row + h * hd + i;
+    const uint4 a = *reinterpret_cast<const uint4*>(v), b = *reinterpret_cast<const uint4*>(v + half);
+    uint4 ra, rb;
+    rotate8(a, b, c, s, ra, rb);
+    *reinterpret_cast<uint4*>(v) = ra;
+    *reinterpret_cast<uint4*>(v + half) = rb;
     return;
   }
   const int blk = block_table[static_cast<size_t>(row_seq[r]) * max_blocks + p / page];
   const int slot = p % page;
-  const __nv_bfloat16* k = row + heads * hd + h * hd;
+  const __nv_bfloat16* k = row + heads * hd + h * hd + i;
   const __nv_bfloat16* vv = k + kv_heads * hd;
-  const size_t dst = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd;
+  const size_t dst = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd + i;
+  uint4 a = *reinterpret_cast<const uint4*>(k), b = *reinterpret_cast<const uint4*>(k + half);
   if (cos_t) {
-    const float x1 = __bfloat162float(k[i]), x2 = __bfloat162float(k[i + half]);
-    kcache[dst + i] = __float2bfloat16_rn(x1 * c - x2 * s);
-    kcache[dst + i + half] = __float2bfloat16_rn(x2 * c + x1 * s);
-  } else {
-    kcache[dst + i] = k[i];
-    kcache[dst + i + half] = k[i + half];
+    uint4 ra, rb;
+    rotate8(a, b, c, s, ra, rb);
+    a = ra, b = rb;
   }
-  vcache[dst + i] = vv[i];
-  vcache[dst + i + half] = vv[i + half];
+  *reinterpret_cast<uint4*>(kcache + dst) = a;
+  *reinterpret_cast<uint4*>(kcache + dst + half) = b;
+  *reinterpret_cast<uint4*>(vcache + dst) = *reinterpret_cast<const uint4*>(vv);
+  *reinterpret_cast<uint4*>(vcache + dst + half) = *reinterpret_cast<const uint4*>(vv + half);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -148,12 +170,12 @@ BW_API int bw_bf16_rope_cache(__nv_bfloat16* qkv, int row_stride, const int* pos
                               __nv_bfloat16* kcache, __nv_bfloat16* vcache, int n, int heads, int kv_heads, int hd,
                               int page, int write_kv, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (hd % 2) {
-    bw::set_error("rope: head size %d is odd", hd);
+  if (hd % 16 || row_stride % 8) {
+    bw::set_error("rope: head size %d must be a multiple of 16 and the row stride %d of 8", hd, row_stride);
     return -1;
   }
-  const int items = (heads + (write_kv ? kv_heads : 0)) * (hd / 2);
-  const int threads = 256;
+  const int items = (heads + (write_kv ? kv_heads : 0)) * (hd / 16);
+  const int threads = items >= 128 ? 128 : 64;
   dim3 grid(n, (items + threads - 1) / threads);
   if (grid.y > 65535u) {
     bw::set_error("rope: %d heads exceed the grid limit", heads);
