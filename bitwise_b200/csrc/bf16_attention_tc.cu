@@ -1,0 +1,476 @@
+// Prefill attention on the fifth-generation tensor cores, for head size 64.
+//
+// Same arithmetic, in the same order, as attention_whole_kernel / attention_split_kernel in
+// bf16_attention.cu (key tiles of 64 at fixed positions; per tile and row the maximum, the sum
+// of the weights and the unnormalised output with bfloat16 weights; ordered merge), so the
+// three kernels give the same bits. What changes is where the work runs:
+//   warp 0     one thread brings Q (once) and the key/value tiles of the paged cache into shared
+//              memory with TMA (128-byte swizzle), one box per page
+//   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 stacked rows x 64 keys, K-major
+//              operands) into one of two S buffers in tensor memory, and O_t = P V (P from
+//              shared memory, V as an MN-major operand) into one of two O buffers
+//   warps 2-5  one thread per stacked row: read the S row from tensor memory, scale, mask,
+//              maximum, weights, sum; write the bfloat16 weights as the next A operand into
+//              shared memory; later read the O_t row and merge it into the running state in
+//              registers; finally normalise and store
+// Two blocks share an SM (256 tensor-memory columns and about 100 KB each), so one block's
+// softmax overlaps the other's MMAs. Every mbarrier wait is bounded (see bf16_gemm_tc.cu).
+#include <cuda.h>
+
+#include "bw_common.cuh"
+
+#ifndef BW_HEAD_DIM
+#error "compile with -DBW_HEAD_DIM=<head size>"
+#endif
+
+#if BW_HEAD_DIM == 64
+
+namespace {
+
+constexpr int HD = 64;
+constexpr int kTileM = 128;   // stacked rows per block
+constexpr int kTileKV = 64;   // keys per tile
+constexpr int kStages = 3;    // key/value tiles in flight
+constexpr int kThreads = 192;
+constexpr int kQBytes = kTileM * 128;          // 16 KB
+constexpr int kKBytes = kTileKV * 128;         // 8 KB
+constexpr int kPBytes = kTileM * 128;          // 16 KB per weight buffer
+constexpr int kTmemCols = 256;                 // S0 S1 O0 O1, 64 columns each
+constexpr uint32_t kSpinLimit = 20000000u;
+
+struct __align__(8) Barriers {
+  uint64_t q_full;
+  uint64_t kv_full[kStages], kv_empty[kStages];
+  uint64_t s_full[2], s_empty[2], p_ready[2], o_full[2], o_empty[2];
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+constexpr int kSmemBytes = kQBytes + kStages * 2 * kKBytes + 2 * kPBytes + sizeof(Barriers) + 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* failed) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && *failed) return false;
+  }
+  *failed = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+// descriptor of a 128-byte-swizzled tile with 8-row groups 1024 bytes apart (K-major tiles of
+// Q, K and P; the MN-major V tile has the same numbers: 64 contiguous d, groups of 8 keys)
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// kind::f16, D float32, A and B bfloat16, M 128, N 64; bit 16 set: B is MN-major
+constexpr uint32_t kDescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kDescPV = kDescQK | (1u << 16);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// the merge of bf16_attention.cu, word for word
+struct MergeWeights {
+  float a, b, mx;
+};
+__device__ __forceinline__ MergeWeights merge_weights(float M, float m) {
+  MergeWeights w;
+  w.mx = fmaxf(M, m);
+  const float ref = (w.mx == -INFINITY) ? 0.0f : w.mx;
+  w.a = exp2f(__fsub_rn(M, ref));
+  w.b = exp2f(__fsub_rn(m, ref));
+  return w;
+}
+__device__ __forceinline__ float merge_value(float X, float x, const MergeWeights& w) {
+  return __fmaf_rn(x, w.b, __fmul_rn(X, w.a));
+}
+
+__global__ void __launch_bounds__(kThreads)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
+                    const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
+                    const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
+                    const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
+                    int kv_heads, int page, int window, float scale_log2, int* error_flag) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sq = base;
+  unsigned char* skv = sq + kQBytes;                    // stage s: K at skv + s * 16 KB, V 8 KB behind
+  unsigned char* sp = skv + kStages * 2 * kKBytes;      // two weight buffers
+  Barriers* bars = reinterpret_cast<Barriers*>(sp + 2 * kPBytes);
+  volatile uint32_t* failed = &bars->failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->s_full[b], 1);
+      mbar_init(&bars->s_empty[b], 4);
+      mbar_init(&bars->p_ready[b], 4);
+      mbar_init(&bars->o_full[b], 1);
+      mbar_init(&bars->o_empty[b], 4);
+    }
+    bars->failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "n"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  bw::pdl_wait();
+  bw::pdl_launch();
+
+  const int tile = blockIdx.x, g = blockIdx.y;
+  const int group = heads / kv_heads;
+  const int seq = tile_seq[tile], row0 = tile_row0[tile], nrows = tile_rows[tile];
+  const int mrows = nrows * group;
+  const int p_first = seq_pos0[seq] + (row0 - seq_row0[seq]);
+  const int p_last = p_first + nrows - 1;
+  const int kv_lo = (window > 0 && p_first - window + 1 > 0) ? ((p_first - window + 1) / kTileKV) * kTileKV : 0;
+  const int kv_hi = p_last + 1;
+  const int ntiles = (kv_hi - kv_lo + kTileKV - 1) / kTileKV;
+  const int pages_per_tile = kTileKV / page;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
+      mbar_expect_tx(&bars->q_full, kQBytes);
+      tma_load_4d(sq, &map_q, 0, 0, g, row0, &bars->q_full);
+      for (int t = 0; t < ntiles; ++t) {
+        const int s = t % kStages;
+        if (t >= kStages && !mbar_wait(&bars->kv_empty[s], ((t / kStages) - 1) & 1, failed)) break;
+        unsigned char* k = skv + s * 2 * kKBytes;
+        const int j0 = kv_lo + t * kTileKV;
+        mbar_expect_tx(&bars->kv_full[s], 2 * kKBytes);
+        for (int pg = 0; pg < pages_per_tile; ++pg) {
+          const int j = j0 + pg * page;
+          // pages wholly beyond the last key are not in the table: any valid page will do, its keys are masked
+          const int blk = (j < kv_hi) ? table[j / page] : table[(kv_hi - 1) / page];
+          tma_load_4d(k + pg * page * 128, &map_k, 0, 0, g, blk, &bars->kv_full[s]);
+          tma_load_4d(k + kKBytes + pg * page * 128, &map_v, 0, 0, g, blk, &bars->kv_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(&bars->q_full, 0, failed);
+      fence_after_sync();
+      const uint64_t qdesc = make_desc(smem_u32(sq));
+      auto issue_qk = [&](int t) -> bool {
+        const int s = t % kStages, b = t & 1;
+        if (!mbar_wait(&bars->kv_full[s], (t / kStages) & 1, failed)) return false;
+        if (t >= 2 && !mbar_wait(&bars->s_empty[b], ((t >> 1) - 1) & 1, failed)) return false;
+        fence_after_sync();
+        const uint64_t kdesc = make_desc(smem_u32(skv + s * 2 * kKBytes));
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma(tmem_base + b * 64, qdesc + 2 * k, kdesc + 2 * k, kDescQK, k > 0 ? 1u : 0u);
+        umma_commit(&bars->s_full[b]);
+        return true;
+      };
+      if (ok && ntiles > 0) ok = issue_qk(0);
+      for (int t = 0; t < ntiles && ok; ++t) {
+        const int s = t % kStages, b = t & 1;
+        if (t + 1 < ntiles) ok = issue_qk(t + 1);  // the next tile's scores are computed while this one's weights are formed
+        if (!ok) break;
+        if (!mbar_wait(&bars->p_ready[b], (t >> 1) & 1, failed)) break;
+        if (t >= 2 && !mbar_wait(&bars->o_empty[b], ((t >> 1) - 1) & 1, failed)) break;
+        fence_after_sync();
+        const uint64_t pdesc = make_desc(smem_u32(sp + b * kPBytes));
+        const uint64_t vdesc = make_desc(smem_u32(skv + s * 2 * kKBytes + kKBytes));
+#pragma unroll
+        for (int k = 0; k < kTileKV / 16; ++k)  // 16 keys: 32 bytes along a row of P, two 8-key groups (2048 bytes) of V
+          umma(tmem_base + 128 + b * 64, pdesc + 2 * k, vdesc + 128 * k, kDescPV, k > 0 ? 1u : 0u);
+        umma_commit(&bars->o_full[b]);
+        umma_commit(&bars->kv_empty[s]);
+      }
+    }
+  } else {
+    // one thread per stacked row; warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int quarter = warp & 3;
+    const int m = quarter * 32 + lane;
+    const int pos = (m < mrows) ? p_first + m / group : p_last;
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float o_tot[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o_tot[i] = 0.0f;
+    float M = -INFINITY, L = 0.0f;
+    bool ok = true;
+    for (int t = 0; t < ntiles && ok; ++t) {
+      const int b = t & 1;
+      const int j0 = kv_lo + t * kTileKV;
+      if (!mbar_wait(&bars->s_full[b], (t >> 1) & 1, failed)) {
+        ok = false;
+        break;
+      }
+      fence_after_sync();
+      float s[kTileKV];
+#pragma unroll
+      for (int c = 0; c < kTileKV / 16; ++c) {
+        float v[16];
+        tmem_ld16(lane_addr + b * 64 + c * 16, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s[c * 16 + i] = v[i];
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[b]);
+      // scale, mask, maximum (the mask test is skipped for tiles inside the row's range)
+      float tmax = -INFINITY;
+      const bool inside = j0 + kTileKV - 1 <= pos && j0 >= first;
+#pragma unroll
+      for (int i = 0; i < kTileKV; ++i) {
+        const int j = j0 + i;
+        const bool valid = inside || (j <= pos && j >= first);
+        const float v = valid ? __fmul_rn(s[i], scale_log2) : -INFINITY;
+        s[i] = v;
+        tmax = fmaxf(tmax, v);
+      }
+      const float ref = (tmax == -INFINITY) ? 0.0f : tmax;
+      // weights; their sum in the order of the other kernels: key j belongs to quad lane
+      // (j % 8) / 2; a quad lane adds its pairs for j / 8 ascending; then (a0 + a1) + (a2 + a3)
+      float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t packed[kTileKV / 2];
+#pragma unroll
+      for (int nb = 0; nb < kTileKV / 8; ++nb)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float e0 = exp2f(__fsub_rn(s[nb * 8 + 2 * q], ref)), e1 = exp2f(__fsub_rn(s[nb * 8 + 2 * q + 1], ref));
+          part[q] = __fadd_rn(part[q], __fadd_rn(e0, e1));
+          __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+          packed[nb * 4 + q] = *reinterpret_cast<uint32_t*>(&pr);
+        }
+      const float tsum = __fadd_rn(__fadd_rn(part[0], part[1]), __fadd_rn(part[2], part[3]));
+      // the row of P: 64 bfloat16 = eight 16-byte pieces, swizzled like a TMA-written tile
+      unsigned char* prow = sp + b * kPBytes + m * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(prow + ((c ^ (m & 7)) << 4)) =
+            make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the writes visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready[b]);
+
+      if (!mbar_wait(&bars->o_full[b], (t >> 1) & 1, failed)) {
+        ok = false;
+        break;
+      }
+      fence_after_sync();
+      const MergeWeights w = merge_weights(M, tmax);
+      M = w.mx;
+      L = merge_value(L, tsum, w);
+#pragma unroll
+      for (int c = 0; c < HD / 16; ++c) {
+        float v[16];
+        tmem_ld16(lane_addr + 128 + b * 64 + c * 16, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o_tot[c * 16 + i] = merge_value(o_tot[c * 16 + i], v[i], w);
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->o_empty[b]);
+    }
+    if (ok && m < mrows) {
+      const int qr = m / group, hq = m - qr * group;
+      __nv_bfloat16* dst = out + static_cast<size_t>(row0 + qr) * out_stride + (g * group + hq) * HD;
+      const float inv = __fdiv_rn(1.0f, L);
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
+        __align__(16) __nv_bfloat162 o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          o[e] = __floats2bfloat162_rn(__fmul_rn(o_tot[c * 8 + 2 * e], inv), __fmul_rn(o_tot[c * 8 + 2 * e + 1], inv));
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(o);
+      }
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && bars->failed) atomicExch(error_flag, 1);
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+
+bool make_map4(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
+               const cuuint32_t (&box)[4]) {
+  EncodeTiled enc = encoder();
+  if (!enc) return false;
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int* g_error_flag = nullptr;
+
+}  // namespace
+
+// Query rows per block, or 0 when this kernel cannot take the shape: head size 64, a page size
+// that divides 64, a group of heads that divides 128, rows that start on 16 bytes.
+BW_API int bw_bf16_attention_tc_tile_rows(int heads, int kv_heads, int hd, int page, int q_stride) {
+  if (hd != HD || kv_heads <= 0 || heads % kv_heads) return 0;
+  const int group = heads / kv_heads;
+  if (group > kTileM || kTileM % group || page <= 0 || kTileKV % page || q_stride % 8 || !encoder()) return 0;
+  return kTileM / group;
+}
+
+BW_API int bw_bf16_attention_tc_failed() {
+  if (!g_error_flag) return 0;
+  int v = 0;
+  cudaMemcpy(&v, g_error_flag, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v) cudaMemset(g_error_flag, 0, sizeof(int));
+  return v;
+}
+
+BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __nv_bfloat16* kcache,
+                                const __nv_bfloat16* vcache, int num_pages, const int* block_table, int max_blocks,
+                                const int* tile_seq, const int* tile_row0, const int* tile_rows, int num_tiles,
+                                const int* seq_pos0, const int* seq_row0, __nv_bfloat16* out, int out_stride, int n,
+                                int heads, int kv_heads, int hd, int page, int window, float scale,
+                                cudaStream_t stream) {
+  if (n <= 0 || num_tiles <= 0) return 0;
+  const int tile_rows_q = bw_bf16_attention_tc_tile_rows(heads, kv_heads, hd, page, q_stride);
+  if (!tile_rows_q || out_stride % 8) {
+    bw::set_error("attention (tcgen05): unsupported shape (heads %d/%d, head size %d, page %d)", heads, kv_heads, hd, page);
+    return -1;
+  }
+  const int group = heads / kv_heads;
+  if (!g_error_flag) {
+    cudaError_t e = cudaMalloc(&g_error_flag, sizeof(int));
+    if (e != cudaSuccess) {
+      bw::set_error("attention (tcgen05): cannot allocate the error word: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    cudaMemset(g_error_flag, 0, sizeof(int));
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) {
+      bw::set_error("attention (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    configured = true;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  {  // queries: [token][kv head][head of the group][d], box = 128 stacked rows of one kv head
+    const cuuint64_t dims[4] = {HD, static_cast<cuuint64_t>(group), static_cast<cuuint64_t>(kv_heads),
+                                static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[3] = {HD * 2, static_cast<cuuint64_t>(group) * HD * 2, static_cast<cuuint64_t>(q_stride) * 2};
+    const cuuint32_t box[4] = {HD, static_cast<cuuint32_t>(group), 1, static_cast<cuuint32_t>(kTileM / group)};
+    if (!make_map4(&map_q, qkv, dims, strides, box)) {
+      bw::set_error("attention (tcgen05): cuTensorMapEncodeTiled refused the query map");
+      return -1;
+    }
+  }
+  {  // cache: [page][kv head][slot][d], box = one page of one kv head
+    const cuuint64_t dims[4] = {HD, static_cast<cuuint64_t>(page), static_cast<cuuint64_t>(kv_heads),
+                                static_cast<cuuint64_t>(num_pages)};
+    const cuuint64_t strides[3] = {HD * 2, static_cast<cuuint64_t>(page) * HD * 2,
+                                   static_cast<cuuint64_t>(kv_heads) * page * HD * 2};
+    const cuuint32_t box[4] = {HD, static_cast<cuuint32_t>(page), 1, 1};
+    if (!make_map4(&map_k, kcache, dims, strides, box) || !make_map4(&map_v, vcache, dims, strides, box)) {
+      bw::set_error("attention (tcgen05): cuTensorMapEncodeTiled refused the cache map");
+      return -1;
+    }
+  }
+  const float scale_log2 = scale * 1.44269504088896341f;
+  bw::launch_pdl(attention_tc_kernel, dim3(num_tiles, kv_heads), dim3(kThreads), kSmemBytes, stream, map_q, map_k, map_v,
+                 block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out, out_stride, heads,
+                 kv_heads, page, window, scale_log2, g_error_flag);
+  return bw::launch_status();
+}
+
+#else  // other head sizes use the kernels of bf16_attention.cu
+
+BW_API int bw_bf16_attention_tc_tile_rows(int, int, int, int, int) { return 0; }
+BW_API int bw_bf16_attention_tc_failed() { return 0; }
+
+#endif

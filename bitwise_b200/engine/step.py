@@ -47,7 +47,8 @@ def query_tile_rows(model) -> List[int]:
     for b in model.blocks:
         fn = getattr(b.mixer, "query_tile_rows", None)
         if fn is not None:
-            sizes.add(int(fn()))
+            got = fn()
+            sizes.update(int(v) for v in (got if isinstance(got, (list, tuple, set)) else [got]))
     return sorted(sizes) or [16]
 
 

@@ -30,7 +30,7 @@ KERNEL_SETS: Dict[str, List[tuple]] = {
     "f32": [("common.cu", []), ("exact_f32.cu", ["-fmad=false"])],
     "bf16": [("common.cu", []), ("bf16_ops.cu", []), ("bf16_gemm.cu", []), ("bf16_gemm_tc.cu", [])],
     # compiled once per head size, with -DBW_HEAD_DIM=<n>
-    "bf16_attn": [("common.cu", []), ("bf16_attention.cu", [])],
+    "bf16_attn": [("common.cu", []), ("bf16_attention.cu", []), ("bf16_attention_tc.cu", [])],
 }
 
 # head sizes whose attention library a full build prepares (others are compiled when a model asks)

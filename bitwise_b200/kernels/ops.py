@@ -62,6 +62,7 @@ class KernelOps:
         self._counters: Optional[torch.Tensor] = None
         self._retired = []
         self._attn_scratch: Optional[torch.Tensor] = None
+        self.legacy_attention = False  # tests set this to compare the attention kernels bit for bit
         if self.kind == "bf16":
             self.lib.bw_bf16_linear_scratch_floats.restype = ctypes.c_longlong
             self._split_rows = int(self.lib.bw_bf16_linear_split_rows())
@@ -217,7 +218,10 @@ class KernelOps:
         word from the device, so callers ask now and then, not every step."""
         if self.kind != "bf16":
             return False
-        return bool(self.lib.bw_bf16_linear_tc_failed())
+        bad = bool(self.lib.bw_bf16_linear_tc_failed())
+        for lib in self._attn_libs.values():
+            bad = bool(lib.bw_bf16_attention_tc_failed()) or bad
+        return bad
 
     def attention_tile_rows(self, heads: int, kv_heads: int) -> int:
         """Query rows per attention tile: the bfloat16 kernel stacks the heads of a group
@@ -309,6 +313,25 @@ class KernelOps:
             t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.attention_tile_rows(heads, kv_heads))
             scratch = None
             split = t_count == n and max_keys > 128  # a decode step: one tile of keys per warp
+            if not split and not self.legacy_attention:
+                # prefill portions: the tcgen05 kernel, where it takes the shape (same bits)
+                rows_tc = int(lib.bw_bf16_attention_tc_tile_rows(_c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+                                                                 _c_int(page), _c_int(qkv.shape[1])))
+                sets = getattr(batch, "tile_sets", None)
+                if rows_tc > 0 and (sets is None or rows_tc in sets) and n > t_count:
+                    q_seq, q_row0, q_rows, q_count = batch.query_tiles(rows_tc)
+                    fn = lib.bw_bf16_attention_tc
+                    fn.restype = _c_int
+                    rc = fn(_p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _c_int(kcache.shape[0]),
+                            _p(block_table), _c_int(block_table.shape[1]), _p(q_seq), _p(q_row0), _p(q_rows),
+                            _c_int(q_count), _p(batch.seq_pos0), _p(batch.seq_row0), _p(out), _c_int(out.shape[1]),
+                            _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window),
+                            _c_float(scale), self._stream())
+                    if rc != 0:
+                        raise KernelError(f"bw_bf16_attention_tc failed ({rc}): "
+                                          + lib.bw_last_error().decode("utf-8", "replace"))
+                    self.launches += 1
+                    return
             if split:
                 scratch = self._attention_scratch(lib, qkv.device, n, heads, max_keys)
             fn = lib.bw_bf16_attention

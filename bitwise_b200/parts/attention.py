@@ -45,7 +45,10 @@ class GQAAttention(Mixer):
         """Height of the query tiles this mixer's attention kernel wants (rows of one
         sequence per thread block); the stepper prepares tiles of every height asked for."""
         group = self.heads // self.kv_heads
-        return max(1, 64 // group)
+        rows = [max(1, 64 // group)]
+        if 128 % group == 0:
+            rows.append(128 // group)  # the tcgen05 prefill kernel stacks 128 rows per block
+        return rows
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
         q, k, v, o = self.names

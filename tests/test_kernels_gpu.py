@@ -301,22 +301,25 @@ def _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window
     class Batch:
         pass
     b = Batch()
-    tr = ops.attention_tile_rows(heads, kv_heads)
-    seq_row0, seq_pos0, tiles, r = [], [], [], 0
+    seq_row0, seq_pos0, r = [], [], 0
     pos, row_seq = [], []
     for s, (p0, cnt) in enumerate(rows_by_seq):
         seq_row0.append(r)
         seq_pos0.append(p0)
-        for a in range(0, cnt, tr):
-            tiles.append((s, r + a, min(tr, cnt - a)))
         pos += list(range(p0, p0 + cnt))
         row_seq += [s] * cnt
         r += cnt
     seq_row0.append(r)
     I = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
     b.seq_row0, b.seq_pos0 = I(seq_row0), I(seq_pos0)
-    sets = (I([x[0] for x in tiles]), I([x[1] for x in tiles]), I([x[2] for x in tiles]), len(tiles))
-    b.query_tiles = lambda rows: sets
+
+    def query_tiles(rows):  # tiles of at most `rows` query rows of one sequence, as the stepper builds them
+        tiles = []
+        for s, (p0, cnt) in enumerate(rows_by_seq):
+            for a in range(0, cnt, rows):
+                tiles.append((s, seq_row0[s] + a, min(rows, cnt - a)))
+        return I([x[0] for x in tiles]), I([x[1] for x in tiles]), I([x[2] for x in tiles]), len(tiles)
+    b.query_tiles = query_tiles
     out = torch.empty(n, heads * hd, device=DEV, dtype=torch.bfloat16)
     ops.attention(t(qkv, torch.bfloat16), t(k, torch.bfloat16), t(v, torch.bfloat16), I(table), I(row_seq), I(pos),
                   out, heads, kv_heads, hd, window, max(pos) + 1, 1.0 / float(np.sqrt(hd)), batch=b)
@@ -410,6 +413,29 @@ def test_bf16_attention_decode_rows_split_over_chunks_give_the_same_bits():
         for s in range(3):
             alone, _, _ = _run_bf16_attention(q3[s:s + 1], [(lens[s] - 1, 1)], k, v, table[s:s + 1], heads, kv_heads, hd, window)
             assert_same_bits(got[s], alone[0], f"sequence {s} in a batch of three")
+
+
+def test_bf16_attention_tensor_core_generations_agree_bit_for_bit():
+    """The tcgen05 prefill kernel (head size 64) and the mma.sync kernels give the same bits:
+    whole prompts, late portions, with a window, grouped heads, several sequences in a step."""
+    rng = np.random.default_rng(16)
+    ops = _ops("bfloat16")
+    for heads, kv_heads, page, window in ((4, 4, 16, 0), (8, 2, 16, 0), (2, 1, 32, 0), (4, 2, 64, 90), (16, 2, 16, 0)):
+        hd = 64
+        lens = [333, 70, 129]
+        k, v, table, _, _ = _paged(rng, lens, kv_heads, hd, page)
+        k, v = bf(k), bf(v)
+        rows_by_seq = [(0, 333), (10, 60), (100, 29)]
+        n = sum(c for _, c in rows_by_seq)
+        q = bf(rnd(rng, n, heads, hd))
+        new, _, _ = _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window)
+        ops.legacy_attention = True
+        try:
+            old, _, _ = _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window)
+        finally:
+            ops.legacy_attention = False
+        assert_same_bits(new, old, f"heads {heads}/{kv_heads} page {page} window {window}")
+    assert not ops.device_failure()
 
 
 def test_bf16_rope_and_cache_write():
