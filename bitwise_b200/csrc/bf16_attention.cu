@@ -88,8 +88,8 @@ __device__ __forceinline__ MergeWeights merge_weights(float M, float m) {
   MergeWeights w;
   w.mx = fmaxf(M, m);
   const float ref = (w.mx == -INFINITY) ? 0.0f : w.mx;
-  w.a = exp2f(__fsub_rn(M, ref));
-  w.b = exp2f(__fsub_rn(m, ref));
+  w.a = bw::exp2_approx(__fsub_rn(M, ref));
+  w.b = bw::exp2_approx(__fsub_rn(m, ref));
   return w;
 }
 __device__ __forceinline__ float merge_value(float X, float x, const MergeWeights& w) {
@@ -131,6 +131,8 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
       mma_bf16(s[2 * np + 1], a, b[2], b[3]);
     }
   }
+  // maximum of the raw scores (scaling by a positive factor commutes with the maximum), then
+  // weights e = 2^(s * scale - ref) with one fused multiply-add per key
   float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
   // a tile that lies wholly inside both rows' ranges needs no per-key test (same values either way)
   const bool inside = j0 + kTileKV - 1 <= min(pos_lo, pos_hi) && j0 >= max(first_lo, first_hi);
@@ -139,9 +141,7 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
     for (int nb = 0; nb < kTileKV / 8; ++nb)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float v = __fmul_rn(s[nb][e], scale_log2);
-        s[nb][e] = v;
-        if (e >= 2) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
+        if (e >= 2) tmax_hi = fmaxf(tmax_hi, s[nb][e]); else tmax_lo = fmaxf(tmax_lo, s[nb][e]);
       }
   } else {
 #pragma unroll
@@ -151,7 +151,7 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
         const int j = j0 + nb * 8 + 2 * (lane & 3) + (e & 1);
         const bool hi = e >= 2;
         const bool ok = hi ? (j <= pos_hi && j >= first_hi) : (j <= pos_lo && j >= first_lo);
-        const float v = ok ? __fmul_rn(s[nb][e], scale_log2) : -INFINITY;
+        const float v = ok ? s[nb][e] : -INFINITY;
         s[nb][e] = v;
         if (hi) tmax_hi = fmaxf(tmax_hi, v); else tmax_lo = fmaxf(tmax_lo, v);
       }
@@ -160,15 +160,19 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
   tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
   tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
   tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
-  // a row with no key in this tile keeps a zero reference so that exp2(-inf - ref) = 0
-  const float ref_lo = (tmax_lo == -INFINITY) ? 0.0f : tmax_lo;
-  const float ref_hi = (tmax_hi == -INFINITY) ? 0.0f : tmax_hi;
+  tmax_lo = __fmul_rn(tmax_lo, scale_log2);
+  tmax_hi = __fmul_rn(tmax_hi, scale_log2);
+  // a row with no key in this tile keeps a zero reference so that 2^(-inf - ref) = 0
+  const float nref_lo = (tmax_lo == -INFINITY) ? 0.0f : -tmax_lo;
+  const float nref_hi = (tmax_hi == -INFINITY) ? 0.0f : -tmax_hi;
   float tsum_lo = 0.0f, tsum_hi = 0.0f;
   uint32_t p[kTileKV / 16][4];
 #pragma unroll
   for (int nb = 0; nb < kTileKV / 8; ++nb) {
-    const float e0 = exp2f(__fsub_rn(s[nb][0], ref_lo)), e1 = exp2f(__fsub_rn(s[nb][1], ref_lo));
-    const float e2 = exp2f(__fsub_rn(s[nb][2], ref_hi)), e3 = exp2f(__fsub_rn(s[nb][3], ref_hi));
+    const float e0 = bw::exp2_approx(__fmaf_rn(s[nb][0], scale_log2, nref_lo));
+    const float e1 = bw::exp2_approx(__fmaf_rn(s[nb][1], scale_log2, nref_lo));
+    const float e2 = bw::exp2_approx(__fmaf_rn(s[nb][2], scale_log2, nref_hi));
+    const float e3 = bw::exp2_approx(__fmaf_rn(s[nb][3], scale_log2, nref_hi));
     tsum_lo = __fadd_rn(tsum_lo, __fadd_rn(e0, e1));
     tsum_hi = __fadd_rn(tsum_hi, __fadd_rn(e2, e3));
     p[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16(e0, e1);

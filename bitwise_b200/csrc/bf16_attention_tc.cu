@@ -45,8 +45,9 @@ struct __align__(8) Barriers {
   uint32_t tmem_base;
   uint32_t failed;
 };
+constexpr int kMaxTablePages = 2048;  // page ids of the block's key range, staged in shared memory
 
-constexpr int kSmemBytes = kQBytes + kStages * 2 * kKBytes + 2 * kPBytes + sizeof(Barriers) + 1024;
+constexpr int kSmemBytes = kQBytes + kStages * 2 * kKBytes + 2 * kPBytes + sizeof(Barriers) + kMaxTablePages * 4 + 1024;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -111,18 +112,18 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
+// 64 consecutive columns of this thread's lane: one load instruction and one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -135,8 +136,8 @@ __device__ __forceinline__ MergeWeights merge_weights(float M, float m) {
   MergeWeights w;
   w.mx = fmaxf(M, m);
   const float ref = (w.mx == -INFINITY) ? 0.0f : w.mx;
-  w.a = exp2f(__fsub_rn(M, ref));
-  w.b = exp2f(__fsub_rn(m, ref));
+  w.a = bw::exp2_approx(__fsub_rn(M, ref));
+  w.b = bw::exp2_approx(__fsub_rn(m, ref));
   return w;
 }
 __device__ __forceinline__ float merge_value(float X, float x, const MergeWeights& w) {
@@ -156,6 +157,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   unsigned char* skv = sq + kQBytes;                    // stage s: K at skv + s * 16 KB, V 8 KB behind
   unsigned char* sp = skv + kStages * 2 * kKBytes;      // two weight buffers
   Barriers* bars = reinterpret_cast<Barriers*>(sp + 2 * kPBytes);
+  int* spages = reinterpret_cast<int*>(bars + 1);
   volatile uint32_t* failed = &bars->failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -188,7 +190,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   bw::pdl_wait();
   bw::pdl_launch();
 
-  const int tile = blockIdx.x, g = blockIdx.y;
+  // tiles are listed in row order and later rows of a prompt have more keys: taking them in
+  // reverse order starts the long blocks first, which shortens the tail of the launch
+  const int tile = gridDim.x - 1 - blockIdx.x, g = blockIdx.y;
   const int group = heads / kv_heads;
   const int seq = tile_seq[tile], row0 = tile_row0[tile], nrows = tile_rows[tile];
   const int mrows = nrows * group;
@@ -200,8 +204,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int pages_per_tile = kTileKV / page;
 
   if (warp == 0) {
+    // the page ids of this block's key range go to shared memory first (one coalesced read),
+    // so that the loop below does not wait for a table entry per page
+    const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
+    const int first_page = kv_lo / page, last_page = (kv_hi - 1) / page;
+    const int staged = min(last_page - first_page + 1, kMaxTablePages);
+    for (int i = lane; i < staged; i += 32) spages[i] = table[first_page + i];
+    __syncwarp();
     if (lane == 0) {
-      const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
       mbar_expect_tx(&bars->q_full, kQBytes);
       tma_load_4d(sq, &map_q, 0, 0, g, row0, &bars->q_full);
       for (int t = 0; t < ntiles; ++t) {
@@ -213,7 +223,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int pg = 0; pg < pages_per_tile; ++pg) {
           const int j = j0 + pg * page;
           // pages wholly beyond the last key are not in the table: any valid page will do, its keys are masked
-          const int blk = (j < kv_hi) ? table[j / page] : table[(kv_hi - 1) / page];
+          const int pi = min(j / page, last_page) - first_page;
+          const int blk = pi < staged ? spages[pi] : table[first_page + pi];
           tma_load_4d(k + pg * page * 128, &map_k, 0, 0, g, blk, &bars->kv_full[s]);
           tma_load_4d(k + kKBytes + pg * page * 128, &map_v, 0, 0, g, blk, &bars->kv_full[s]);
         }
@@ -262,7 +273,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float o_tot[HD];
 #pragma unroll
     for (int i = 0; i < HD; ++i) o_tot[i] = 0.0f;
-    float M = -INFINITY, L = 0.0f;
+    float M = -INFINITY, L = 0.0f, prev_max = -INFINITY, prev_sum = 0.0f;
     bool ok = true;
     for (int t = 0; t < ntiles && ok; ++t) {
       const int b = t & 1;
@@ -273,37 +284,44 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       fence_after_sync();
       float s[kTileKV];
-#pragma unroll
-      for (int c = 0; c < kTileKV / 16; ++c) {
-        float v[16];
-        tmem_ld16(lane_addr + b * 64 + c * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) s[c * 16 + i] = v[i];
-      }
+      tmem_ld64(lane_addr + b * 64, s);
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[b]);
-      // scale, mask, maximum (the mask test is skipped for tiles inside the row's range)
+      // mask, maximum of the raw scores (the mask test is skipped for tiles inside the row's
+      // range), then weights e = 2^(s * scale - ref) with one fused multiply-add per key
       float tmax = -INFINITY;
       const bool inside = j0 + kTileKV - 1 <= pos && j0 >= first;
+      if (!inside) {
 #pragma unroll
-      for (int i = 0; i < kTileKV; ++i) {
-        const int j = j0 + i;
-        const bool valid = inside || (j <= pos && j >= first);
-        const float v = valid ? __fmul_rn(s[i], scale_log2) : -INFINITY;
-        s[i] = v;
-        tmax = fmaxf(tmax, v);
+        for (int i = 0; i < kTileKV; ++i) {
+          const int j = j0 + i;
+          s[i] = (j <= pos && j >= first) ? s[i] : -INFINITY;
+        }
       }
-      const float ref = (tmax == -INFINITY) ? 0.0f : tmax;
-      // weights; their sum in the order of the other kernels: key j belongs to quad lane
-      // (j % 8) / 2; a quad lane adds its pairs for j / 8 ascending; then (a0 + a1) + (a2 + a3)
+      {  // the maximum is exact in any order: four independent chains instead of one of 64
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < kTileKV; i += 4) {
+          m4[0] = fmaxf(m4[0], s[i]);
+          m4[1] = fmaxf(m4[1], s[i + 1]);
+          m4[2] = fmaxf(m4[2], s[i + 2]);
+          m4[3] = fmaxf(m4[3], s[i + 3]);
+        }
+        tmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      }
+      tmax = __fmul_rn(tmax, scale_log2);
+      const float nref = (tmax == -INFINITY) ? 0.0f : -tmax;
+      // their sum in the order of the other kernels: key j belongs to quad lane (j % 8) / 2; a
+      // quad lane adds its pairs for j / 8 ascending; then (a0 + a1) + (a2 + a3)
       float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint32_t packed[kTileKV / 2];
 #pragma unroll
       for (int nb = 0; nb < kTileKV / 8; ++nb)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float e0 = exp2f(__fsub_rn(s[nb * 8 + 2 * q], ref)), e1 = exp2f(__fsub_rn(s[nb * 8 + 2 * q + 1], ref));
+          const float e0 = bw::exp2_approx(__fmaf_rn(s[nb * 8 + 2 * q], scale_log2, nref));
+          const float e1 = bw::exp2_approx(__fmaf_rn(s[nb * 8 + 2 * q + 1], scale_log2, nref));
           part[q] = __fadd_rn(part[q], __fadd_rn(e0, e1));
           __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
           packed[nb * 4 + q] = *reinterpret_cast<uint32_t*>(&pr);
@@ -319,24 +337,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_ready[b]);
 
-      if (!mbar_wait(&bars->o_full[b], (t >> 1) & 1, failed)) {
+      // the output of the tile before this one is merged now, while the tensor core forms this
+      // tile's output from the weights just written
+      if (t > 0) {
+        const int pb = (t - 1) & 1;
+        if (!mbar_wait(&bars->o_full[pb], ((t - 1) >> 1) & 1, failed)) {
+          ok = false;
+          break;
+        }
+        fence_after_sync();
+        const MergeWeights w = merge_weights(M, prev_max);
+        M = w.mx;
+        L = merge_value(L, prev_sum, w);
+        {
+          float v[HD];
+          tmem_ld64(lane_addr + 128 + pb * 64, v);
+#pragma unroll
+          for (int i = 0; i < HD; ++i) o_tot[i] = merge_value(o_tot[i], v[i], w);
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->o_empty[pb]);
+      }
+      prev_max = tmax;
+      prev_sum = tsum;
+    }
+    if (ok && ntiles > 0) {  // the last tile's output
+      const int pb = (ntiles - 1) & 1;
+      if (mbar_wait(&bars->o_full[pb], ((ntiles - 1) >> 1) & 1, failed)) {
+        fence_after_sync();
+        const MergeWeights w = merge_weights(M, prev_max);
+        M = w.mx;
+        L = merge_value(L, prev_sum, w);
+        {
+          float v[HD];
+          tmem_ld64(lane_addr + 128 + pb * 64, v);
+#pragma unroll
+          for (int i = 0; i < HD; ++i) o_tot[i] = merge_value(o_tot[i], v[i], w);
+        }
+      } else {
         ok = false;
-        break;
       }
-      fence_after_sync();
-      const MergeWeights w = merge_weights(M, tmax);
-      M = w.mx;
-      L = merge_value(L, tsum, w);
-#pragma unroll
-      for (int c = 0; c < HD / 16; ++c) {
-        float v[16];
-        tmem_ld16(lane_addr + 128 + b * 64 + c * 16, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o_tot[c * 16 + i] = merge_value(o_tot[c * 16 + i], v[i], w);
-      }
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->o_empty[b]);
     }
     if (ok && m < mrows) {
       const int qr = m / group, hq = m - qr * group;

@@ -84,6 +84,15 @@ __device__ __forceinline__ float tree16(const float* l) {
   return __fadd_rn(__fadd_rn(s4[0], s4[2]), __fadd_rn(s4[1], s4[3]));
 }
 
+// 2^x by the hardware's approximation unit (one instruction; -inf gives 0). The bfloat16
+// attention kernels all use this one function for softmax weights and merge factors, so
+// they agree bit for bit with each other.
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // SwiGLU of one element for the bfloat16 kernels: (g * sigmoid(g)) * u in float32
 // (src/kernels.cpp:291-298) with the hardware's approximate exp2 and reciprocal; the result is
 // rounded to bfloat16 by the caller, which hides their last-place error. One definition for
