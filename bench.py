@@ -15,6 +15,11 @@ synthetic prompt ids uniform over the vocabulary; batch of 8 requests decoding a
   roofline     decode step: bytes it must read (every weight once + the cache of the live
                requests) / time, against the copy bandwidth
   points       decode tokens per second at batch 1 and 64
+  fp32         decode and prefill of the same shape on the true 32-bit path
+
+Other workloads: --shape smollm2-360m|llama3-8b runs the same measurements on those layer
+sizes; --workload serve pushes 64 mixed requests through the engine's scheduler under a
+512-token budget and reports generated tokens per second by the host clock.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present ("of measured"), else
 from the fallback figures of an earlier measurement on this kind of GPU ("of fallback").
@@ -103,11 +108,32 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-def model_config(layers):
+SHAPES = {
+    # name: (title, layers, LlamaConfig keywords, default decode context)
+    "smollm2-1.7b": ("SmolLM2-1.7B shape", 24, dict(
+        vocab_size=49152, hidden_size=2048, num_attention_heads=32, num_key_value_heads=32, head_dim=64,
+        intermediate_size=8192, rope_theta=130000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+        max_position_embeddings=8192), 2048),
+    "smollm2-360m": ("SmolLM2-360M shape", 32, dict(
+        vocab_size=49152, hidden_size=960, num_attention_heads=15, num_key_value_heads=5, head_dim=64,
+        intermediate_size=2560, rope_theta=100000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+        max_position_embeddings=8192), 2048),
+    "llama3-8b": ("Llama-3-8B shape", 32, dict(
+        vocab_size=128256, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+        intermediate_size=14336, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+        max_position_embeddings=8192,
+        rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                          original_max_position_embeddings=8192)), 4096),
+}
+
+
+def model_config(shape, layers):
     from bitwise_b200 import LlamaConfig
-    return LlamaConfig(vocab_size=49152, hidden_size=2048, num_hidden_layers=layers, num_attention_heads=32,
-                       num_key_value_heads=32, head_dim=64, intermediate_size=8192, rope_theta=130000.0,
-                       rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=8192)
+    from bitwise_b200.config.llama import RopeScaling
+    kw = dict(SHAPES[shape][2])
+    if "rope_scaling" in kw:
+        kw["rope_scaling"] = RopeScaling(**kw["rope_scaling"])
+    return LlamaConfig(num_hidden_layers=layers, **kw)
 
 
 def matrix_params(c):
@@ -245,9 +271,14 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=24, help="layers to run (the shape has 24)")
+    ap.add_argument("--shape", default="smollm2-1.7b", choices=sorted(SHAPES))
+    ap.add_argument("--layers", type=int, default=0, help="layers to run (default: all of the shape's)")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--ctx", type=int, default=0, help="tokens in each request's cache (default: the shape's)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve"],
+                    help="serve: 64 requests with prompts of 16..1024 and outputs of 16..256 tokens through the "
+                         "engine's scheduler under a 512-token budget")
+    ap.add_argument("--skip-fp32", action="store_true", help="leave out the float32 figures")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling runs)")
@@ -267,9 +298,15 @@ def main():
     import torch
     from bitwise_b200 import Model
     pk = peaks()
-    cfg = model_config(args.layers)
+    title, full_layers, _, shape_ctx = SHAPES[args.shape]
+    args.layers = args.layers or full_layers
+    args.ctx = args.ctx or shape_ctx
+    cfg = model_config(args.shape, args.layers)
     model = Model.random(cfg, seed=0, dtype=args.dtype, device="cuda:0", fast=True)
     elt = 2 if args.dtype == "bfloat16" else 4
+    if args.workload == "serve":
+        print(json.dumps(run_serve(model, title, args, pk)))
+        return 0
 
     with ClockSampler() as clocks:
         ms, launches = run_decode(model, args.batch, args.ctx, args.steps, warmup, args.page)
@@ -278,16 +315,16 @@ def main():
     achieved = bytes_step / (ms / 1e3) / 1e9
 
     line = {
-        "metric": "decode tok/s at batch 8, 2,048-token context (SmolLM2-1.7B shape)",
+        "metric": f"decode tok/s at batch {args.batch}, {args.ctx:,}-token context ({title})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(value / REFERENCE_DECODE_TOKS, 1), "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary",
         "impl": "ours",
-        "config": {"model": "SmolLM2-1.7B shape", "layers": cfg.num_hidden_layers, "layers_run": args.layers,
+        "config": {"model": title, "layers": full_layers, "layers_run": args.layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "tied_embeddings": True, "global_batch": args.batch, "seq_len": args.ctx,
+                   "tied_embeddings": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": args.ctx,
                    "page_size": args.page, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights + cache read per step exceed 126 MB)",
                    "peaks": "of " + pk["source"]},
@@ -296,8 +333,6 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": bytes_step},
     }
-    if args.layers != 24:
-        line["config"]["layers"] = 24
     if not args.skip_prefill:
         pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
         fl = prefill_flops(cfg, 2048)
@@ -312,8 +347,69 @@ def main():
         line["points"] = pts
         e, h2d, d2h = run_e2e(model, args.batch, args.ctx, args.steps, warmup, args.page)
         line["e2e"] = {"value": round(e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    if not args.skip_fp32 and args.dtype == "bfloat16" and not args.skip_points:
+        # the true 32-bit path of the same shape (no reduced-precision matrix mode anywhere)
+        del model
+        torch.cuda.empty_cache()
+        m32 = Model.random(cfg, seed=0, dtype="float32", device="cuda:0", fast=True)
+        fm, _ = run_decode(m32, args.batch, args.ctx, max(5, args.steps // 5), 3, args.page)
+        f32 = {"decode_b%d" % args.batch: round(args.batch / (fm / 1e3), 1), "ms_per_step": round(fm, 3),
+               "decode_hbm_frac": round(decode_bytes(cfg, args.batch, args.ctx, 4) / (fm / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        if not args.skip_prefill:
+            fp = run_prefill(m32, 2048, reps=3, warmup=3, page=args.page)
+            f32["prefill"] = round(2048 / (fp / 1e3), 1)
+            f32["prefill_ms"] = round(fp, 2)
+        line["fp32"] = f32
     print(json.dumps(line))
     return 0
+
+
+def run_serve(model, title, args, pk):
+    """Continuous batching through the engine: 64 requests, prompt lengths uniform in [16, 1024],
+    output lengths uniform in [16, 256], prompts cut under a 512-token budget; host clock around
+    the whole run, which is repeated after one untimed pass."""
+    import numpy as np
+    import torch
+    from bitwise_b200 import Engine, EngineConfig, SamplingParams
+    c = model.config
+    rng = np.random.default_rng(3)
+    n = 64
+    plen = rng.integers(16, 1025, n)
+    olen = rng.integers(16, 257, n)
+    prompts = [rng.integers(0, c.vocab_size, int(l)).tolist() for l in plen]
+    params = [SamplingParams(temperature=0.0, max_new_tokens=int(o), ignore_eos=True) for o in olen]
+    page = args.page
+    blocks = sum((int(p) + int(o) + page) // page for p, o in zip(plen, olen)) + 8
+    out = {}
+    with ClockSampler() as clocks:
+        for rep in range(2):
+            eng = Engine(model, EngineConfig(num_blocks=blocks, block_size=page, max_batched_tokens=512,
+                                             max_num_seqs=n, fingerprint_logits=False, max_model_len=2048))
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            res = eng.generate(prompts, params)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            made = sum(len(r) for r in res)
+            out = {"value": made / dt, "seconds": dt, "steps": eng.stats.steps, "generated": made,
+                   "prompt_tokens": int(plen.sum()), "launches": model.ops.launches}
+            del eng
+            torch.cuda.empty_cache()
+    return {
+        "metric": f"generated tok/s, 64 mixed requests under a 512-token budget ({title})",
+        "value": round(out["value"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": out["steps"], "warmup": 1,
+        "ms_per_step": round(out["seconds"] * 1e3 / max(1, out["steps"]), 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary", "impl": "ours",
+        "config": {"model": title, "layers": c.num_hidden_layers, "hidden": c.hidden_size,
+                   "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim,
+                   "intermediate": c.intermediate_size, "vocab": c.vocab_size, "requests": n,
+                   "prompt_tokens": out["prompt_tokens"], "generated_tokens": out["generated"],
+                   "token_budget": 512, "page_size": page, "parallelism": "single GPU",
+                   "timing": "host clock around Engine.generate, second of two passes"},
+        "clocks": clocks.summary(), "gpu_launches": out["launches"],
+        "total_tokens_per_s": round((out["prompt_tokens"] + out["generated"]) / out["seconds"], 1),
+    }
 
 
 if __name__ == "__main__":

@@ -2,7 +2,7 @@
 // accumulation, for every projection of the model (the reference's hand-written matmul,
 // src/kernels.cpp:196-259, is its counterpart).
 //
-// One summation order for every shape. The inner dimension is cut into chunks of 512
+// One summation order for every shape. The inner dimension is cut into chunks of 2048
 // elements at fixed positions. Inside a chunk the products are accumulated by the tensor
 // core in steps of 16 along k, ascending. The chunk sums are added in float32 in ascending
 // chunk order, p0, then + p1, then + p2 ..., and the residual last. A large batch walks the
@@ -282,6 +282,7 @@ int launch(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32
 // rows start on 16 bytes.
 BW_API int bw_bf16_linear_tc_usable(const void* x, const void* w, int k);
 BW_API int bw_bf16_linear_tc_splits(int m, int n, int k);
+BW_API int bw_bf16_linear_tc_may_split(int m, int n, int k);
 BW_API long long bw_bf16_linear_tc_scratch_floats(int m, int n, int k);
 BW_API int bw_bf16_linear_tc_counters(int n);
 BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
@@ -296,7 +297,7 @@ constexpr int kSplitBN = 64;
 // variant runs it: the caller provides at least this much.
 BW_API long long bw_bf16_linear_scratch_floats(int m, int n, int k) {
   const long long chunks = (k + kChunk - 1) / kChunk;
-  const bool tc = bw_bf16_linear_tc_splits(m, n, k) != 0;
+  const bool tc = bw_bf16_linear_tc_may_split(m, n, k) != 0;
   const bool legacy = m <= kSplitMaxRows && chunks > 1 && (n + kSplitBN - 1) / kSplitBN < 2 * 148;
   return (tc || legacy) ? chunks * m * n : 0;
 }

@@ -1,6 +1,6 @@
 // The bfloat16 matrix product on the fifth-generation tensor cores: tcgen05.mma with the
 // accumulator in tensor memory, operands brought into shared memory by TMA. One summation
-// order for every batch size: chunks of 512 along k at fixed positions, inside a chunk the
+// order for every batch size: chunks of 2048 along k at fixed positions, inside a chunk the
 // tensor core accumulates in steps of 16 along k, the chunk sums are added in float32 in
 // ascending order. A product with many output tiles walks the chunks of a tile inside one
 // block ("whole" mode). A product with few output tiles and few rows (decode steps) gives
@@ -41,18 +41,24 @@ constexpr int kSmemBudget = 200 * 1024;        // ring of stages (plus barriers)
 // allocation). Rows are independent in a matrix product, so this only fills accumulator
 // lanes that are never read, and it leaves room for more stages: a decode step is bound by
 // how many bytes of weights an SM keeps in flight.
-template <int A_ROWS, int BNT>
-struct Ring {
-  static constexpr int kTileBytesW = BNT * BK * 2;  // 16 or 32 KB of weights per stage
-  static constexpr int kTileBytesX = A_ROWS * BK * 2;
-  static constexpr int kStageBytes = kTileBytesX + kTileBytesW;
-  static constexpr int kStages = (kSmemBudget - (BM - A_ROWS) * BK * 2) / kStageBytes > 12
-                                     ? 12
-                                     : (kSmemBudget - (BM - A_ROWS) * BK * 2) / kStageBytes;
-  static constexpr int kPadBytes = (BM - A_ROWS) * BK * 2;  // behind the last stage
-  static constexpr int kRingBytes = kStages * kStageBytes + kPadBytes;
+//
+// The W tile of a stage holds w_rows rows: 128 (256 for a wide tile), or fewer, in steps of
+// 16, when a product has too few columns to give every SM a 128-column tile: a decode step
+// then runs more, narrower tiles instead of cutting k further.
+constexpr int kMaxStages = 32;
+struct RingShape {
+  int tile_bytes_x, stage_bytes, stages, pad_bytes, ring_bytes;
 };
-constexpr int kMaxStages = 12;
+__host__ __device__ inline RingShape ring_shape(int a_rows, int w_rows) {
+  RingShape r;
+  r.tile_bytes_x = a_rows * BK * 2;
+  r.stage_bytes = r.tile_bytes_x + w_rows * BK * 2;
+  r.pad_bytes = (BM - a_rows) * BK * 2;  // behind the last stage
+  const int fit = (kSmemBudget - r.pad_bytes) / r.stage_bytes;
+  r.stages = fit > kMaxStages ? kMaxStages : fit;
+  r.ring_bytes = r.stages * r.stage_bytes + r.pad_bytes;
+  return r;
+}
 constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
 
 struct __align__(8) Barriers {
@@ -136,7 +142,61 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+
+// ---- two blocks on one tile (cta_group::2) ----------------------------------------------
+// A cluster of two blocks computes a 256 x 256 tile: each block loads 128 rows of x and 128
+// rows of W per stage; one tcgen05.mma issued by the block of rank 0 reads both blocks'
+// shared memory (M 256: 128 rows per block, N 256: 128 W rows from each block) and writes
+// each block's 128 x 256 part into that block's own tensor memory. Per flop a block takes
+// in a third less from shared memory than with a 128 x 256 tile of its own.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address of the same shared-memory location in the block of the given rank
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of a block of the pair; the bytes are counted on the barrier at `bar_cluster_addr`,
+// which lies in the block of rank 0
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t instr_desc_pair(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at the same offset in both blocks of the pair once the MMAs issued
+// so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[16]) {
   uint32_t r[16];
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -148,6 +208,44 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+        "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+        "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+        "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -215,38 +313,52 @@ __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num
 // EPI 0: y = (residual +) product.  EPI 1 (whole mode only): the product is the interleaved
 // gate/up projection and y[m][n / 2] = SwiGLU of it (bfloat16).
 //
-// WIDE: the output tile is 128 x 256 instead of 128 x 128 and eight epilogue warps share it
-// (each still one row x 128 columns per thread). A wide tile needs a third less operand
-// traffic per flop; large batches are bound by how fast the SM can take in operands.
-template <bool SPLIT, int A_ROWS, int EPI, bool WIDE>
-__global__ void __launch_bounds__(WIDE ? 320 : 192)
+// WIDE: the output tile is 128 x 256 instead of 128 x 128 and sixteen epilogue warps share it
+// (one row x 64 columns per thread). A wide tile needs a third less operand traffic per flop.
+// Large batches are bound by how fast a chunk sum leaves tensor memory: the tensor core may
+// start chunk c + 2 only when the epilogue has read chunk c out of that accumulator, so the
+// read is spread over many warps, 32 columns per tcgen05.ld, and the totals of a thread (64)
+// stay in registers.
+//
+// PAIR (with WIDE, whole mode): two blocks of a cluster share a 256 x 256 tile, see above.
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR>
+__global__ void __launch_bounds__(WIDE ? 384 : 192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
-               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials) {
+               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials, int bn) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzled tiles want 1024-byte alignment
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int BNT = WIDE ? 2 * BN : BN;
+  static_assert(!PAIR || (WIDE && !SPLIT && A_ROWS == BM), "a pair works on wide tiles in whole mode");
+  constexpr int BNT = WIDE ? 2 * BN : BN;   // columns of this block's accumulators
+  constexpr int BNW = PAIR ? BN : BNT;      // W rows this block loads per stage
+  constexpr int BMT = PAIR ? 2 * BM : BM;   // rows of a work item's output tile
   constexpr int kEpiWarps = WIDE ? 8 : 4;
+  constexpr int kFirstEpiWarp = WIDE ? 4 : 2;  // wide: warps 0-3 are one warpgroup (loader, MMA, two idle)
+  constexpr int PW = 64;                    // columns of one of the two pieces an epilogue thread owns
+  constexpr int LDW = 32;                   // columns per tcgen05.ld
   constexpr int kTmemColsT = 2 * BNT;  // two accumulators
-  using RingT = Ring<A_ROWS, BNT>;
-  constexpr int kStages = RingT::kStages;
-  constexpr int kStageBytes = RingT::kStageBytes;
-  constexpr int kTileBytesX = RingT::kTileBytesX;
-  Barriers* bars = reinterpret_cast<Barriers*>(tiles + RingT::kRingBytes);
+  const int bt = WIDE ? BNT : bn;           // columns of a work item's tile (bn: 16 .. 128 in steps of 16)
+  const RingShape ring = ring_shape(A_ROWS, WIDE ? BNW : bn);
+  const int kStages = ring.stages, kStageBytes = ring.stage_bytes, kTileBytesX = ring.tile_bytes_x;
+  Barriers* bars = reinterpret_cast<Barriers*>(tiles + ring.ring_bytes);
   volatile uint32_t* failed = &bars->failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = (K + BK - 1) / BK;          // k-tiles of one output tile
   const int num_chunks = (K + kChunk - 1) / kChunk;
-  const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BNT - 1) / BNT;
+  const int m_blocks = (M + BMT - 1) / BMT, n_blocks = (N + bt - 1) / bt;
+  // a pair is one worker: both blocks walk the same items, each on its own 128 rows
+  const uint32_t rank = PAIR ? cluster_rank() : 0;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   // Work items are dealt round-robin to the resident blocks and the three roles below walk
   // the same sequence of items. Whole mode: item t is the output tile with rows of block
   // t % m_blocks and columns of block t / m_blocks, all its chunks (blocks that run at the same
   // time share W tiles through L2). Split mode (one block of rows): item t is chunk
   // t % num_chunks of the output tile with columns of block t / num_chunks.
   const int out_tiles = SPLIT ? n_blocks * num_chunks : m_blocks * n_blocks;
-  auto item_m0 = [&](int t) { return SPLIT ? 0 : (t % m_blocks) * BM; };
-  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * BNT : (t / m_blocks) * BNT; };
+  auto item_m0 = [&](int t) { return SPLIT ? 0 : (t % m_blocks) * BMT + static_cast<int>(rank) * BM; };
+  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * bt : (t / m_blocks) * bt; };
   auto item_c0 = [&](int t) { return SPLIT ? t % num_chunks : 0; };
   auto item_c1 = [&](int t) { return SPLIT ? t % num_chunks + 1 : num_chunks; };
 
@@ -257,26 +369,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->acc_full[b], 1);
-      mbar_init(&bars->acc_empty[b], kEpiWarps);  // one arrival per epilogue warp
+      mbar_init(&bars->acc_empty[b], PAIR ? 2 * kEpiWarps : kEpiWarps);  // one arrival per epilogue warp
     }
     bars->failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // this warp owns the tensor-memory allocation
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
-                 "n"(kTmemColsT)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {  // this warp owns the tensor-memory allocation (in a pair: the same warp of both blocks)
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                   "n"(kTmemColsT)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                   "n"(kTmemColsT)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   fence_before_sync();
-  __syncthreads();
+  if (PAIR)
+    cluster_sync_all();  // the other block's barriers exist before anything arrives on them
+  else
+    __syncthreads();
   fence_after_sync();
   // Barriers and tensor memory are set up. The next kernel may be set up from now on; this
   // one waits for the kernel before it where it first touches data that kernel may have
   // written: the loader before its first x tile, the epilogue before it reads or writes.
   bw::pdl_launch();
   const uint32_t tmem_base = bars->tmem_base;
-
+  // Wide tiles: the epilogue threads carry 128 running totals and the values in flight from
+  // tensor memory; the loader and MMA warps need little. Registers move from the first
+  // warpgroup to the two epilogue warpgroups (384 threads start with 168 each).
+  if (warp < kFirstEpiWarp) {
+  if (WIDE) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     if (lane == 0) {
       // The weights do not depend on the kernel before this one: the W tiles of the first
@@ -284,20 +410,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       // after, then the x tiles of those stages follow. Later stages load both together.
       uint32_t it = 0;  // k-tiles issued so far, over all output tiles of this block
       bool ok = true, waited = false;
-      for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
-        const int m0 = item_m0(tile), n0 = item_n0(tile);
+      // In a pair both blocks' loads are counted on the "full" barrier of rank 0, which
+      // expects the bytes of both; each block waits on its own "empty" barrier.
+      auto expect = [&](int s) {
+        if (!PAIR)
+          mbar_expect_tx(&bars->full[s], kStageBytes);
+        else if (rank == 0)
+          mbar_expect_tx(&bars->full[s], 2 * kStageBytes);
+      };
+      auto load = [&](void* dst, const CUtensorMap* map, int x, int y, int s) {
+        if (PAIR)
+          tma_load_2d_pair(dst, map, x, y, peer_addr(smem_u32(&bars->full[s]), 0));
+        else
+          tma_load_2d(dst, map, x, y, &bars->full[s]);
+      };
+      for (int tile = worker; tile < out_tiles && ok; tile += workers) {
+        const int m0 = item_m0(tile), n0 = item_n0(tile) + (PAIR ? static_cast<int>(rank) * BN : 0);
         const int kt0 = item_c0(tile) * kTilesPerChunk, kt1 = min(num_tiles, item_c1(tile) * kTilesPerChunk);
         int kt = kt0;
         if (!waited) {  // first item of this block
           const int early = min(kt1 - kt0, kStages);
           for (int e = 0; e < early; ++e) {
             unsigned char* a = tiles + e * kStageBytes;
-            mbar_expect_tx(&bars->full[e], kStageBytes);
-            tma_load_2d(a + kTileBytesX, &map_w, (kt0 + e) * BK, n0, &bars->full[e]);
+            expect(e);
+            load(a + kTileBytesX, &map_w, (kt0 + e) * BK, n0, e);
           }
           bw::pdl_wait();
           waited = true;
-          for (int e = 0; e < early; ++e) tma_load_2d(tiles + e * kStageBytes, &map_x, (kt0 + e) * BK, m0, &bars->full[e]);
+          for (int e = 0; e < early; ++e) load(tiles + e * kStageBytes, &map_x, (kt0 + e) * BK, m0, e);
           kt += early;
           it += early;
         }
@@ -309,17 +449,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             break;
           }
           unsigned char* a = tiles + s * kStageBytes;
-          mbar_expect_tx(&bars->full[s], kStageBytes);
-          tma_load_2d(a, &map_x, kt * BK, m0, &bars->full[s]);
-          tma_load_2d(a + kTileBytesX, &map_w, kt * BK, n0, &bars->full[s]);
+          expect(s);
+          load(a, &map_x, kt * BK, m0, s);
+          load(a + kTileBytesX, &map_w, kt * BK, n0, s);
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {  // in a pair the block of rank 0 issues for both
       uint32_t it = 0, gc = 0;  // k-tiles and chunks consumed so far
       bool ok = true;
-      for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < out_tiles && ok; tile += workers) {
         for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
           const int buf = gc & 1;
           const uint32_t use = gc >> 1;  // how often this accumulator was used before
@@ -342,27 +482,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               // 16 k-elements are 32 bytes: the start address field moves by 2 (units of 16 bytes)
-              umma(d, adesc + 2 * k, bdesc + 2 * k, instr_desc(BNT), (kt > t_begin || k > 0) ? 1u : 0u);
+              const uint32_t acc = (kt > t_begin || k > 0) ? 1u : 0u;
+              if (PAIR)
+                umma_pair(d, adesc + 2 * k, bdesc + 2 * k, instr_desc_pair(BNT), acc);
+              else
+                umma(d, adesc + 2 * k, bdesc + 2 * k, instr_desc(bt), acc);
             }
-            umma_commit(&bars->empty[s]);  // the stage may be refilled once these MMAs are done
+            // the stage may be refilled once these MMAs are done
+            if (PAIR)
+              umma_commit_pair(&bars->empty[s]);
+            else
+              umma_commit(&bars->empty[s]);
           }
-          if (ok) umma_commit(&bars->acc_full[buf]);
+          if (ok) {
+            if (PAIR)
+              umma_commit_pair(&bars->acc_full[buf]);
+            else
+              umma_commit(&bars->acc_full[buf]);
+          }
         }
       }
     }
+  }
   } else {
-    // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    if (WIDE) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31. A thread owns one
+    // row of the tile and the two halves (pieces of 64 columns) of a 128-column block of it;
+    // a wide tile has two such blocks, one per group of four warps. With interleaved gate/up
+    // weights the first piece holds gates and the second the up values of the same outputs.
     bw::pdl_wait();
     const int quarter = warp & 3;
     const int et = quarter * 32 + lane;  // 0..127: this thread's row of the tile
-    const int coff = WIDE ? ((warp - 2) >> 2) * BN : 0;  // this warp's half of a wide tile
-    float total[BN];
+    const int blk = (warp - kFirstEpiWarp) >> 2;  // 0, or 0..1 in a wide tile
+    constexpr int half = 0;
+    const int off0 = blk * BN, off1 = off0 + BN / 2;  // column offsets of the pieces in the tile
+    float total[2 * PW];
     uint32_t gc = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < out_tiles && ok; tile += gridDim.x) {
-      const int m0 = item_m0(tile), n0 = item_n0(tile) + coff;
+    for (int tile = worker; tile < out_tiles && ok; tile += workers) {
+      const int m0 = item_m0(tile), n0 = item_n0(tile);
       const int row = m0 + et;
-      const int cols = min(BN, N - n0);  // may be <= 0 for the second half of a last, partial wide tile
       for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
         const int buf = gc & 1;
         if (!mbar_wait(&bars->acc_full[buf], (gc >> 1) & 1, failed)) {
@@ -371,101 +530,131 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         fence_after_sync();
         if (!SPLIT || quarter * 32 < M) {  // in split mode warps whose rows are all padding read nothing
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BNT + coff;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BNT;
 #pragma unroll
-          for (int g = 0; g < BN / 16; ++g) {
-            float v[16];
-            tmem_ld16(taddr + g * 16, v);
+          for (int piece = 0; piece < 2; ++piece) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              total[g * 16 + j] = (SPLIT || c == 0) ? v[j] : total[g * 16 + j] + v[j];
+            for (int g = 0; g < PW / LDW; ++g) {
+              if (!WIDE && (piece ? off1 : off0) + g * LDW >= bt) continue;  // a narrow tile ends here
+              float v[LDW];
+              tmem_ld(taddr + (piece ? off1 : off0) + g * LDW, v);
+#pragma unroll
+              for (int j = 0; j < LDW; ++j) {
+                float& t = total[piece * PW + g * LDW + j];
+                t = (SPLIT || c == 0) ? v[j] : t + v[j];
+              }
+            }
           }
         }
         fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+        if (lane == 0) {
+          if (PAIR)
+            mbar_arrive_cluster(peer_addr(smem_u32(&bars->acc_empty[buf]), 0));
+          else
+            mbar_arrive(&bars->acc_empty[buf]);
+        }
       }
       if (!ok) break;
+      if (row >= M) continue;
       if (SPLIT && num_chunks > 1) {
         // this item's chunk sum goes to scratch; a second kernel adds the chunk sums in order
         const int chunk = item_c0(tile);
-        if (row < M) {
-          float* mine = partials + (static_cast<size_t>(chunk) * M + row) * N + n0;
-          if (cols == BN && (N & 3) == 0) {
 #pragma unroll
-            for (int j = 0; j < BN; j += 4)
-              __stcg(reinterpret_cast<float4*>(mine + j), make_float4(total[j], total[j + 1], total[j + 2], total[j + 3]));
+        for (int piece = 0; piece < 2; ++piece) {
+          const int col0 = n0 + (piece ? off1 : off0);
+          const int cols = min(PW, min(N, n0 + bt) - col0);
+          float* mine = partials + (static_cast<size_t>(chunk) * M + row) * N + col0;
+          const float* t = total + piece * PW;
+          if (cols == PW && (N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < PW; j += 4)
+              __stcg(reinterpret_cast<float4*>(mine + j), make_float4(t[j], t[j + 1], t[j + 2], t[j + 3]));
           } else {
 #pragma unroll
-            for (int j = 0; j < BN; ++j)
-              if (j < cols) __stcg(mine + j, total[j]);
+            for (int j = 0; j < PW; ++j)
+              if (j < cols) __stcg(mine + j, t[j]);
           }
         }
         continue;
       }
-      if (row >= M || cols <= 0) continue;
       if (EPI == 1) {
-        // columns 0..63 of the tile are gate rows, 64..127 the up rows of the same indices
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + static_cast<size_t>(row) * (N / 2) + n0 / 2;
+        // the first piece holds gate rows, the second the up rows of the same indices; both
+        // are rounded to bfloat16 first, as if the product had been stored
+        if (n0 + off0 >= N) continue;
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + static_cast<size_t>(row) * (N / 2) + (n0 + blk * BN) / 2 + half * PW;
 #pragma unroll
-        for (int j = 0; j < 64; j += 8) {
+        for (int j = 0; j < PW; j += 8) {
           __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float g0 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e]));
             const float g1 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e + 1]));
-            const float u0 = __bfloat162float(__float2bfloat16_rn(total[64 + j + 2 * e]));
-            const float u1 = __bfloat162float(__float2bfloat16_rn(total[64 + j + 2 * e + 1]));
+            const float u0 = __bfloat162float(__float2bfloat16_rn(total[PW + j + 2 * e]));
+            const float u1 = __bfloat162float(__float2bfloat16_rn(total[PW + j + 2 * e + 1]));
             o[e] = __floats2bfloat162_rn(bw::swiglu_one(g0, u0), bw::swiglu_one(g1, u1));
           }
           *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
         }
         continue;
       }
-      const size_t base = static_cast<size_t>(row) * N + n0;
-      if (y_is_f32) {
-        float* out = static_cast<float*>(Y) + base;
-        const float* res = residual ? residual + base : nullptr;
-        if (cols == BN && (N & 3) == 0) {
 #pragma unroll
-          for (int j = 0; j < BN; j += 4) {
-            float4 o = make_float4(total[j], total[j + 1], total[j + 2], total[j + 3]);
-            if (res) {
-              const float4 r = *reinterpret_cast<const float4*>(res + j);
-              o.x = r.x + o.x, o.y = r.y + o.y, o.z = r.z + o.z, o.w = r.w + o.w;
+      for (int piece = 0; piece < 2; ++piece) {
+        const int col0 = n0 + (piece ? off1 : off0);
+        const int cols = min(PW, min(N, n0 + bt) - col0);  // may be <= 0 in a narrow or a last, partial tile
+        if (cols <= 0) continue;
+        const float* t = total + piece * PW;
+        const size_t base = static_cast<size_t>(row) * N + col0;
+        if (y_is_f32) {
+          float* out = static_cast<float*>(Y) + base;
+          const float* res = residual ? residual + base : nullptr;
+          if (cols == PW && (N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < PW; j += 4) {
+              float4 o = make_float4(t[j], t[j + 1], t[j + 2], t[j + 3]);
+              if (res) {
+                const float4 r = *reinterpret_cast<const float4*>(res + j);
+                o.x = r.x + o.x, o.y = r.y + o.y, o.z = r.z + o.z, o.w = r.w + o.w;
+              }
+              *reinterpret_cast<float4*>(out + j) = o;
             }
-            *reinterpret_cast<float4*>(out + j) = o;
+          } else {
+#pragma unroll
+            for (int j = 0; j < PW; ++j)  // static indices keep the totals in registers
+              if (j < cols) out[j] = res ? res[j] + t[j] : t[j];
           }
         } else {
+          __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + base;
+          if (cols == PW && (N & 7) == 0) {
 #pragma unroll
-          for (int j = 0; j < BN; ++j)  // static indices keep the totals in registers
-            if (j < cols) out[j] = res ? res[j] + total[j] : total[j];
-        }
-      } else {
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + base;
-        if (cols == BN && (N & 7) == 0) {
+            for (int j = 0; j < PW; j += 8) {
+              __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
-          for (int j = 0; j < BN; j += 8) {
-            __align__(16) __nv_bfloat162 o[4];
+              for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(t[j + 2 * e], t[j + 2 * e + 1]);
+              *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
+            }
+          } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(total[j + 2 * e], total[j + 2 * e + 1]);
-            *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
+            for (int j = 0; j < PW; ++j)
+              if (j < cols) out[j] = __float2bfloat16_rn(t[j]);
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < BN; ++j)
-            if (j < cols) out[j] = __float2bfloat16_rn(total[j]);
         }
       }
     }
   }
 
   fence_before_sync();
-  __syncthreads();
+  if (PAIR)
+    cluster_sync_all();  // neither block leaves while the other may still read its memory or signal it
+  else
+    __syncthreads();
   if (warp == 1) {
     __syncwarp();
     fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemColsT) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemColsT) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(kTmemColsT) : "memory");
   }
   if (threadIdx.x == 0 && bars->failed) atomicExch(error_flag, 1);
 }
@@ -501,6 +690,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows 
 }
 
 int* g_error_flag = nullptr;  // one word of device memory, allocated on first use
+int g_pair_tiles = 1;         // large batches: two blocks per 256 x 256 tile (0: one block per 128 x 256 tile)
 
 }  // namespace
 
@@ -508,6 +698,14 @@ int* g_error_flag = nullptr;  // one word of device memory, allocated on first u
 BW_API int bw_bf16_linear_tc_usable(const void* x, const void* w, int k) {
   return (k % 8 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
          encoder() != nullptr;
+}
+
+// Large batches run two blocks per tile (1, the default) or one (0); both give the same bits.
+// Returns the previous setting. For tests and measurements.
+BW_API int bw_bf16_linear_tc_pair_tiles(int on) {
+  const int before = g_pair_tiles;
+  g_pair_tiles = on ? 1 : 0;
+  return before;
 }
 
 // Reads and clears the flag that a kernel raises when one of its bounded waits ran out.
@@ -527,11 +725,6 @@ BW_API int bw_bf16_linear_tc_counters(int n) { return (n + BN - 1) / BN; }
 
 // Split mode is chosen from the shape alone: one block of rows, more than one chunk, and too
 // few output tiles to occupy the machine. Both modes give the same bits.
-BW_API int bw_bf16_linear_tc_splits(int m, int n, int k) {
-  const int n_blocks = (n + BN - 1) / BN;
-  return m <= BM && k > kChunk && n_blocks < 100;
-}
-
 namespace {
 
 int sm_count_of_device() {
@@ -545,38 +738,135 @@ int sm_count_of_device() {
   return sm_count;
 }
 
+// How a product with one block of rows (m <= 128) runs. A tcgen05.mma that adds to the
+// accumulator of the one before it starts only when that one is done, about 100 ns later
+// whatever the tile's width, so a block's time is the number of such steps it issues one
+// after the other: 32 per chunk of 512. The plan minimises (rounds of the SMs over the work
+// items) x (steps per item): items are output tiles (all chunks inside, "whole") or (tile,
+// chunk) pairs ("split", which adds a second kernel and the traffic of the chunk sums);
+// tiles are 16 .. 128 columns wide in steps of 16, or 256. Of equal plans the one with the
+// narrower tiles wins (more SMs stream weights). Every plan gives the same bits.
+struct Plan {
+  bool split;
+  int bn;
+};
+int g_tile_width = 0;  // 0: chosen from the shape; else forced (tests, measurements)
+int g_force_mode = 0;  // 0: chosen; 1: whole; 2: split where it is possible
+
+constexpr int kMaxSplitColumns = 16384;  // bounds the scratch of the chunk sums
+
+Plan plan_rows(int m, int n, int k, bool swiglu, int sms) {
+  const int chunks = (k + kChunk - 1) / kChunk;
+  const int steps_chunk = kChunk / 16;
+  const bool may_split = m <= BM && chunks > 1 && n <= kMaxSplitColumns;
+  Plan best{false, BN};
+  double best_cost = -1.0;
+  for (int mode = 0; mode < 2; ++mode) {
+    if (mode == 1 && !may_split) continue;
+    if (g_force_mode == 1 && mode == 1) continue;
+    if (g_force_mode == 2 && mode == 0 && may_split) continue;
+    for (int bn = 16; bn <= 2 * BN; bn = (bn < BN ? bn + 16 : 2 * bn)) {
+      if (swiglu && bn < BN) continue;  // gate and up of an output lie 64 columns apart
+      if (g_tile_width && bn != g_tile_width && !(swiglu && g_tile_width < BN && bn == BN)) continue;
+      const long long tiles = (n + bn - 1) / bn;
+      const long long items = mode ? tiles * chunks : tiles;
+      const long long rounds = (items + sms - 1) / sms;
+      double cost = static_cast<double>(rounds) * (mode ? steps_chunk : steps_chunk * chunks);
+      // the second kernel, and writing and reading the chunk sums (8 bytes each at about 3 TB/s)
+      if (mode) cost += 20.0 + 2.67e-5 * chunks * static_cast<double>(m) * n;
+      if (best_cost < 0 || cost < best_cost - 1e-9) best = Plan{mode == 1, bn}, best_cost = cost;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+// Forces the width of the output tiles of small batches (a multiple of 16 up to 128, or 256;
+// 0: chosen from the shape) and the mode (0 chosen, 1 whole, 2 split where possible). Every
+// combination gives the same bits. For tests and measurements.
+BW_API void bw_bf16_linear_tc_force(int bn, int mode) {
+  if (bn == 0 || bn == 2 * BN || (bn % 16 == 0 && bn >= 16 && bn <= BN)) g_tile_width = bn;
+  if (mode >= 0 && mode <= 2) g_force_mode = mode;
+}
+
+// Whether a plain product of this shape is split along k (then it needs scratch).
+BW_API int bw_bf16_linear_tc_splits(int m, int n, int k) {
+  return m <= BM && plan_rows(m, n, k, false, sm_count_of_device()).split;
+}
+// Whether some plan may split it (what callers size the scratch by).
+BW_API int bw_bf16_linear_tc_may_split(int m, int n, int k) { return m <= BM && k > kChunk && n <= kMaxSplitColumns; }
+// Kernels that one call launches (1, or 2 when the product is split): callers count launches.
+BW_API int bw_bf16_linear_tc_kernels(int m, int n, int k, int swiglu, int has_scratch) {
+  return (m <= BM && has_scratch && plan_rows(m, n, k, swiglu != 0, sm_count_of_device()).split) ? 2 : 1;
+}
+
+namespace {
+
 // What follows the product: nothing, or SwiGLU.
 struct Fused {
   int mode = 0;  // 0 none, 2 swiglu (y is [m][n / 2] bfloat16)
 };
 
-template <bool SPLIT, int A_ROWS, int EPI, bool WIDE>
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR = false>
 int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m, int n,
-              int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream) {
+              int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream, int narrow_bn = BN) {
   constexpr int BNT = WIDE ? 2 * BN : BN;
-  constexpr int smem = Ring<A_ROWS, BNT>::kRingBytes + sizeof(Barriers) + 1024;
-  static_assert(smem <= 227 * 1024, "ring does not fit");
+  constexpr int BNW = PAIR ? BN : BNT;
+  constexpr int BMT = PAIR ? 2 * BM : BM;
+  constexpr int smem_max = kSmemBudget + sizeof(Barriers) + 1024;
+  constexpr int threads = WIDE ? 384 : 192;
+  static_assert(smem_max <= 227 * 1024, "ring does not fit");
+  const int chunks = (k + kChunk - 1) / kChunk;
+  const int bn = WIDE ? BNT : narrow_bn;
+  const RingShape ring = ring_shape(A_ROWS, WIDE ? BNW : bn);
+  const int smem = ring.ring_bytes + static_cast<int>(sizeof(Barriers)) + 1024;
+  auto kernel = gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE, PAIR>;
   static bool configured = false;
+  static int max_pairs = 0;  // pairs that the device runs at the same time
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
     if (e != cudaSuccess) {
       bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
       return static_cast<int>(e);
     }
+    if (PAIR) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(2 * (sm_count_of_device() / 2));
+      probe.blockDim = dim3(threads);
+      probe.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+      probe.attrs = attr;
+      probe.numAttrs = 1;
+      e = cudaOccupancyMaxActiveClusters(&max_pairs, kernel, &probe);
+      if (e != cudaSuccess || max_pairs <= 0) {
+        bw::set_error("linear (tcgen05): the device offers no cluster of two blocks for this kernel: %s",
+                      cudaGetErrorString(e));
+        cudaGetLastError();
+        return e != cudaSuccess ? static_cast<int>(e) : -1;
+      }
+    }
     configured = true;
   }
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, x, m, k, A_ROWS) || !make_map(&map_w, w, n, k, BNT)) {
+  if (!make_map(&map_x, x, m, k, A_ROWS) || !make_map(&map_w, w, n, k, WIDE ? BNW : bn)) {
     bw::set_error("linear (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
     return -1;
   }
-  const int n_blocks = (n + BNT - 1) / BNT, m_blocks = (m + BM - 1) / BM, chunks = (k + kChunk - 1) / kChunk;
+  const int n_blocks = (n + bn - 1) / bn, m_blocks = (m + BMT - 1) / BMT;
   const long long items = SPLIT ? static_cast<long long>(n_blocks) * chunks : static_cast<long long>(n_blocks) * m_blocks;
+  if (PAIR) {
+    const unsigned pairs = static_cast<unsigned>(items < max_pairs ? items : max_pairs);
+    bw::launch_pdl_cluster2(kernel, dim3(2 * pairs), dim3(threads), smem, stream, map_x, map_w, y, y_is_f32, residual, m,
+                            n, k, error_word, partials, bn);
+    return bw::launch_status();
+  }
   const int sms = sm_count_of_device();
   const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
-  bw::launch_pdl(gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE>, dim3(grid), dim3(WIDE ? 320 : 192), smem, stream, map_x, map_w, y, y_is_f32, residual, m, n, k,
-                                                                       error_word, partials);
+  bw::launch_pdl(kernel, dim3(grid), dim3(threads), smem, stream, map_x, map_w, y, y_is_f32, residual, m, n, k,
+                 error_word, partials, bn);
   if (SPLIT) {
     const size_t outputs = static_cast<size_t>(m) * n;
     if (fused.mode == 2)
@@ -589,19 +879,29 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
   return bw::launch_status();
 }
 
-// picks the x-tile height from the batch size
-template <bool SPLIT, int EPI>
+// picks the x-tile height from the batch size, and for small batches the plan
+template <int EPI>
 int launch_tc_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m,
                    int n, int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream) {
-  if (m <= 16)
-    return launch_tc<SPLIT, 16, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  if (m <= 32)
-    return launch_tc<SPLIT, 32, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  if (m <= 64)
-    return launch_tc<SPLIT, 64, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  if (SPLIT || m <= 128)
-    return launch_tc<SPLIT, 128, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
-  return launch_tc<false, 128, EPI, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream);
+#define BW_LAUNCH(SPLIT_, ROWS_, EPI_, WIDE_) \
+  launch_tc<SPLIT_, ROWS_, EPI_, WIDE_>(x, w, y, y_is_f32, residual, m, n, k, error_word, partials, fused, stream, plan.bn)
+#define BW_LAUNCH_ROWS(SPLIT_, EPI_, WIDE_)                        \
+  (m <= 16   ? BW_LAUNCH(SPLIT_, 16, EPI_, WIDE_)                  \
+   : m <= 32 ? BW_LAUNCH(SPLIT_, 32, EPI_, WIDE_)                  \
+   : m <= 64 ? BW_LAUNCH(SPLIT_, 64, EPI_, WIDE_)                  \
+             : BW_LAUNCH(SPLIT_, 128, EPI_, WIDE_))
+  if (m <= BM) {
+    Plan plan = plan_rows(m, n, k, fused.mode == 2, sm_count_of_device());
+    if (!partials) plan = Plan{false, plan.split ? BN : plan.bn};
+    const bool wide = plan.bn > BN;
+    if (plan.split) return wide ? BW_LAUNCH_ROWS(true, 0, true) : BW_LAUNCH_ROWS(true, 0, false);
+    return wide ? BW_LAUNCH_ROWS(false, EPI, true) : BW_LAUNCH_ROWS(false, EPI, false);
+  }
+#undef BW_LAUNCH_ROWS
+#undef BW_LAUNCH
+  if (g_pair_tiles)
+    return launch_tc<false, 128, EPI, true, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, nullptr, fused, stream);
+  return launch_tc<false, 128, EPI, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, nullptr, fused, stream);
 }
 
 int ensure_error_word() {
@@ -628,10 +928,8 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
     return -1;
   }
   if (const int rc = ensure_error_word()) return rc;
-  const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
   const Fused none;
-  if (split) return launch_tc_rows<true, 0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, partials, none, stream);
-  return launch_tc_rows<false, 0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, nullptr, none, stream);
+  return launch_tc_rows<0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, partials, none, stream);
 }
 
 // h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows
@@ -644,11 +942,9 @@ BW_API int bw_bf16_linear_tc_swiglu(const __nv_bfloat16* x, const __nv_bfloat16*
     return -1;
   }
   if (const int rc = ensure_error_word()) return rc;
-  const bool split = bw_bf16_linear_tc_splits(m, n, k) && partials != nullptr;
   Fused f;
   f.mode = 2;
-  if (split) return launch_tc_rows<true, 0>(x, w, h, 0, nullptr, m, n, k, g_error_flag, partials, f, stream);
-  return launch_tc_rows<false, 1>(x, w, h, 0, nullptr, m, n, k, g_error_flag, nullptr, f, stream);
+  return launch_tc_rows<1>(x, w, h, 0, nullptr, m, n, k, g_error_flag, partials, f, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -715,10 +1011,8 @@ BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w
   // Nothing in the scratch has to start at zero: every chunk sum that the second kernel reads
   // is written by the first one in this same call. The launcher raises the kernel's
   // shared-memory limit at its first use (no allocation either).
-  if (split)
-    return launch_tc_rows<true, 0>(x, w, y, y_is_f32, residual, m, n, k, g_noalloc_error_ptr[dev],
-                                   g_noalloc_scratch_ptr[dev], Fused(), stream);
-  return launch_tc_rows<false, 0>(x, w, y, y_is_f32, residual, m, n, k, g_noalloc_error_ptr[dev], nullptr, Fused(), stream);
+  return launch_tc_rows<0>(x, w, y, y_is_f32, residual, m, n, k, g_noalloc_error_ptr[dev],
+                           split ? g_noalloc_scratch_ptr[dev] : nullptr, Fused(), stream);
 }
 
 // Reads and clears the word that a kernel launched by bw_bf16_linear_noalloc raises when one

@@ -18,8 +18,8 @@
 extern "C" {
 #endif
 
-// Largest scratch the entry point can serve, in floats: ceil(k / 512) * m * n must not exceed
-// it for a product that is split along k (few rows, few output columns, k > 512).  16 MiB of
+// Largest scratch the entry point can serve, in floats: ceil(k / 2048) * m * n must not exceed
+// it for a product that is split along k (few rows, few output columns, k > 2048).  16 MiB of
 // device memory per GPU that loads the library, held until the process exits.
 #define BW_NOALLOC_MAX_SCRATCH_FLOATS (4 * 1024 * 1024)
 

@@ -15,6 +15,7 @@ indices from there, which also keeps the step replayable as a CUDA graph.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -240,8 +241,16 @@ class Stepper:
         elif key is not None and self._seen.get(key, 0) >= 1 and len(self._graphs) < self.GRAPH_CACHE:
             before = self.ops.launches
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, views)
+            # No garbage collection while the stream captures: collecting an old stepper
+            # destroys its graphs, and destroying a graph during a capture invalidates it.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self.model.forward(ctx, views)
+            finally:
+                if collecting:
+                    gc.enable()
             launches = self.ops.launches - before
             self._graphs[key] = (graph, logits, launches)
             graph.replay()

@@ -19,6 +19,9 @@ _c_float = ctypes.c_float
 _ptr = ctypes.c_void_p
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -62,6 +65,11 @@ class KernelOps:
         self._counters: Optional[torch.Tensor] = None
         self._retired = []
         self._attn_scratch: Optional[torch.Tensor] = None
+        self._fns = {}
+        self._dev_index: Optional[int] = None
+        self._scratch_sizes = {}
+        self._kernel_counts = {}
+        self._tc_tile_rows = {}
         self.legacy_attention = False  # tests set this to compare the attention kernels bit for bit
         if self.kind == "bf16":
             self.lib.bw_bf16_linear_scratch_floats.restype = ctypes.c_longlong
@@ -69,7 +77,16 @@ class KernelOps:
 
     # -- plumbing ----------------------------------------------------------------------
     def _stream(self):
+        # the raw handle of torch's current stream; the private getter skips the Stream object
+        # that torch.cuda.current_stream() builds, which costs more than a kernel launch
+        if _raw_stream is not None:
+            return ctypes.c_void_p(_raw_stream(self._device_index()))
         return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _device_index(self) -> int:
+        if self._dev_index is None:
+            self._dev_index = torch.cuda.current_device()
+        return self._dev_index
 
     def _check(self, rc: int, name: str) -> None:
         if rc != 0:
@@ -77,8 +94,12 @@ class KernelOps:
             raise KernelError(f"{name} failed ({rc}): {msg}")
 
     def _call(self, name: str, *args, lib=None, launches: int = 1) -> None:
-        fn = getattr(lib or self.lib, name)
-        fn.restype = _c_int
+        fn = self._fns.get(name) if lib is None else None
+        if fn is None:
+            fn = getattr(lib or self.lib, name)
+            fn.restype = _c_int
+            if lib is None:
+                self._fns[name] = fn
         self._check(fn(*args), name)
         self.launches += launches
 
@@ -156,7 +177,8 @@ class KernelOps:
                 partials, counters = self._linear_scratch(x.device, n, k)
             self._call("bw_bf16_linear", _p(x), _p(w), _p(out), _c_int(int(out.dtype == torch.float32)),
                        _p(residual), _c_int(m), _c_int(n), _c_int(k), _p(partials), _p(counters),
-                       _c_int(int(legacy)), self._stream())
+                       _c_int(int(legacy)), self._stream(),
+                       launches=1 if legacy else self._linear_kernels(m, n, k, False, partials is not None))
 
     def linear_norm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor],
                     norm_weight: torch.Tensor, eps: float, norm_out: torch.Tensor) -> None:
@@ -195,16 +217,29 @@ class KernelOps:
         if m <= self._split_rows:
             partials, _ = self._linear_scratch(x.device, n, k)
         self._call("bw_bf16_linear_tc_swiglu", _p(x), _p(w_interleaved), _p(out), _c_int(m), _c_int(n), _c_int(k),
-                   _p(partials), self._stream(), launches=2 if partials is not None else 1)
+                   _p(partials), self._stream(), launches=self._linear_kernels(m, n, k, True, partials is not None))
+
+    def _linear_kernels(self, m: int, n: int, k: int, swiglu: bool, scratch: bool) -> int:
+        """Kernels that a product of this shape launches (2 when it is split along k)."""
+        key = (m, n, k, swiglu, scratch)
+        c = self._kernel_counts.get(key)
+        if c is None:
+            c = int(self.lib.bw_bf16_linear_tc_kernels(_c_int(m), _c_int(n), _c_int(k), _c_int(int(swiglu)),
+                                                       _c_int(int(scratch))))
+            self._kernel_counts[key] = c
+        return c
 
     def _linear_scratch(self, device, n: int, k: int):
         """Scratch of a product that is split along k: chunk sums for up to ``_split_rows``
         rows, and one counter per output tile (zero between launches).  It grows when a
         larger product appears and is otherwise reused by every product of the stream."""
         # sized for the largest batch that may be split, so that the address stays the same
-        floats = max(int(self.lib.bw_bf16_linear_scratch_floats(_c_int(r), _c_int(n), _c_int(k)))
-                     for r in (64, self._split_rows))
-        tiles = int(self.lib.bw_bf16_linear_counters(_c_int(n)))
+        sizes = self._scratch_sizes.get((n, k))
+        if sizes is None:
+            sizes = (max(int(self.lib.bw_bf16_linear_scratch_floats(_c_int(r), _c_int(n), _c_int(k)))
+                         for r in (64, self._split_rows)), int(self.lib.bw_bf16_linear_counters(_c_int(n))))
+            self._scratch_sizes[(n, k)] = sizes
+        floats, tiles = sizes
         if floats and (self._partials is None or self._partials.numel() < floats):
             self._retired.append(self._partials)  # a captured graph may still point at the old one
             self._partials = torch.empty(floats, dtype=torch.float32, device=device)
@@ -212,6 +247,21 @@ class KernelOps:
             self._retired.append(self._counters)
             self._counters = torch.zeros(max(tiles, 1024), dtype=torch.int32, device=device)
         return self._partials, self._counters
+
+    def force_linear_plan(self, width: int = 0, mode: int = 0) -> None:
+        """Tests and measurements: force the tile width of small batches (16 .. 128 in steps of
+        16, or 256; 0: chosen from the shape) and the mode (0 chosen, 1 one block walks k,
+        2 split along k where possible).  Every combination gives the same bits."""
+        if self.kind == "bf16":
+            self._kernel_counts.clear()
+            self.lib.bw_bf16_linear_tc_force(_c_int(width), _c_int(mode))
+
+    def pair_tiles(self, on: bool) -> bool:
+        """Large batches run two thread blocks per 256 x 256 tile of a product (the default) or
+        one per 128 x 256 tile; same bits either way.  Returns the previous setting."""
+        if self.kind != "bf16":
+            return False
+        return bool(self.lib.bw_bf16_linear_tc_pair_tiles(_c_int(int(on))))
 
     def device_failure(self) -> bool:
         """True (once) when a kernel gave up a bounded wait since the last call.  This reads a
@@ -315,8 +365,13 @@ class KernelOps:
             split = t_count == n and max_keys > 128  # a decode step: one tile of keys per warp
             if not split and not self.legacy_attention:
                 # prefill portions: the tcgen05 kernel, where it takes the shape (same bits)
-                rows_tc = int(lib.bw_bf16_attention_tc_tile_rows(_c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-                                                                 _c_int(page), _c_int(qkv.shape[1])))
+                shape_key = (heads, kv_heads, head_dim, page, qkv.shape[1])
+                rows_tc = self._tc_tile_rows.get(shape_key)
+                if rows_tc is None:
+                    rows_tc = int(lib.bw_bf16_attention_tc_tile_rows(_c_int(heads), _c_int(kv_heads),
+                                                                     _c_int(head_dim), _c_int(page),
+                                                                     _c_int(qkv.shape[1])))
+                    self._tc_tile_rows[shape_key] = rows_tc
                 sets = getattr(batch, "tile_sets", None)
                 if rows_tc > 0 and (sets is None or rows_tc in sets) and n > t_count:
                     q_seq, q_row0, q_rows, q_count = batch.query_tiles(rows_tc)

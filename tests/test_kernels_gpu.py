@@ -219,7 +219,8 @@ def bf(a):
 
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (5, 100, 96), (64, 344, 64), (65, 130, 172), (200, 256, 1100),
                                    (8, 2048, 2048), (33, 72, 520), (65, 64, 64), (130, 100, 96), (200, 256, 1104),
-                                   (300, 2112, 2048), (1000, 136, 520)])
+                                   (300, 2112, 2048), (1000, 136, 520), (8, 2048, 8192), (20, 1000, 4100),
+                                   (5, 48, 2064), (70, 2304, 6152), (260, 96, 4104)])
 def test_bf16_linear(m, n, k):
     """Tolerance: float32 accumulation of exact bfloat16 products; the result may differ from
     the float64 sum by accumulation rounding only: 1e-4 of the largest output (float32 out),
@@ -244,9 +245,10 @@ def test_bf16_linear(m, n, k):
 
 def test_bf16_linear_row_bits_do_not_depend_on_the_batch():
     """The summation order is the same for every batch size: a row gives the same bits
-    alone, in a small batch (split along k) and in a large one (one block walks k)."""
+    alone, in a small batch (narrow tiles, split along k where k is long and n small) and in
+    a large one (one block or a pair of blocks walks k)."""
     rng = np.random.default_rng(8)
-    for n, k in ((96, 2048), (2048, 1536), (64, 200)):
+    for n, k in ((96, 2048), (2048, 1536), (64, 200), (2048, 8192), (136, 4104), (6144, 2048)):
         x, w = bf(rnd(rng, 200, k)), bf(rnd(rng, n, k, scale=0.05))
         ops = _ops("bfloat16")
         full = torch.empty(200, n, device=DEV)
@@ -263,13 +265,71 @@ def test_bf16_linear_tensor_core_generations_agree_bit_for_bit():
     rng = np.random.default_rng(14)
     ops = _ops("bfloat16")
     for m, n, k in ((8, 2048, 2048), (1, 6144, 2048), (64, 2048, 8192), (100, 320, 1536), (128, 16384, 512),
-                    (300, 200, 1032), (17, 136, 520)):
+                    (300, 200, 1032), (17, 136, 520), (3, 1000, 4104), (128, 2304, 6152), (16, 6144, 4096),
+                    (40, 96, 2056), (300, 200, 4104), (8, 4096, 14336)):
         x, w = bf(rnd(rng, m, k)), bf(rnd(rng, n, k, scale=0.05))
         res = rnd(rng, m, n)
         a, b = t(res).clone(), t(res).clone()
         ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), a, residual=a)
         ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), b, residual=b, legacy=True)
         assert_same_bits(a.cpu().numpy(), b.cpu().numpy(), f"[{m}x{k}] x [{n}x{k}]")
+        want = res + x.astype(np.float64) @ w.astype(np.float64).T
+        assert np.abs(a.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
+    assert not ops.device_failure()
+
+
+def test_bf16_linear_every_plan_of_a_small_batch_gives_the_same_bits():
+    """A small batch may run whole (one block walks k) or split along k, on tiles 16 .. 128
+    or 256 columns wide: the plan is chosen for speed and must not change a bit."""
+    rng = np.random.default_rng(16)
+    ops = _ops("bfloat16")
+    for m, n, k in ((8, 2048, 2048), (1, 6144, 1536), (40, 1000, 4104), (128, 520, 1032), (17, 136, 520)):
+        x, w = bf(rnd(rng, m, k)), bf(rnd(rng, n, k, scale=0.05))
+        res = rnd(rng, m, n)
+        want = t(res).clone()
+        ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), want, residual=want, legacy=True)
+        try:
+            for mode in (1, 2):
+                for width in (16, 48, 112, 128, 256):
+                    ops.force_linear_plan(width, mode)
+                    got = t(res).clone()
+                    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), got, residual=got)
+                    assert_same_bits(got.cpu().numpy(), want.cpu().numpy(),
+                                     f"mode {mode} width {width} [{m}x{k}] x [{n}x{k}]")
+                    got16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+                    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), got16)
+                    ref16 = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+                    ops.force_linear_plan(0, 0)
+                    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), ref16, legacy=True)
+                    assert torch.equal(got16.view(torch.int16), ref16.view(torch.int16))
+        finally:
+            ops.force_linear_plan(0, 0)
+    assert not ops.device_failure()
+
+
+def test_bf16_linear_two_blocks_per_tile_give_the_same_bits():
+    """Large batches run on pairs of thread blocks that share a 256 x 256 tile (cta_group::2);
+    the same product with one block per tile, and the legacy kernel, give equal bits. Sizes:
+    a second block with no rows, with one row, partial tiles in both directions, many tiles
+    per pair, k with a partial chunk."""
+    rng = np.random.default_rng(15)
+    ops = _ops("bfloat16")
+    for m, n, k in ((129, 256, 64), (257, 264, 520), (256, 512, 2048), (600, 520, 1032), (2047, 2048, 576),
+                    (1500, 6144, 512), (385, 136, 4104)):
+        x, w = bf(rnd(rng, m, k)), bf(rnd(rng, n, k, scale=0.05))
+        res = rnd(rng, m, n)
+        a, b, c = t(res).clone(), t(res).clone(), t(res).clone()
+        before = ops.pair_tiles(True)
+        try:
+            ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), a, residual=a)
+            ops.pair_tiles(False)
+            ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), b, residual=b)
+        finally:
+            ops.pair_tiles(before)
+        assert_same_bits(a.cpu().numpy(), b.cpu().numpy(), f"pair vs single [{m}x{k}] x [{n}x{k}]")
+        if m * n * k < 2e9:
+            ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), c, residual=c, legacy=True)
+            assert_same_bits(a.cpu().numpy(), c.cpu().numpy(), f"pair vs legacy [{m}x{k}] x [{n}x{k}]")
         want = res + x.astype(np.float64) @ w.astype(np.float64).T
         assert np.abs(a.cpu().numpy() - want).max() <= 1e-4 * np.abs(want).max()
     assert not ops.device_failure()

@@ -39,8 +39,10 @@ def _call(fn, x, w, y, residual, stream):
               residual.data_ptr() if residual is not None else None, m, n, k, stream)
 
 
-@pytest.mark.parametrize("m,n,k,uses_scratch", [(8, 2048, 2048, True), (64, 1024, 4096, True), (1, 6144, 1536, True),
-                                                (8, 16384, 2048, False), (200, 384, 1024, False)])
+@pytest.mark.parametrize("m,n,k,uses_scratch", [(8, 2048, 8192, True), (64, 1024, 4096, True), (1, 2304, 6152, True),
+                                                (8, 16384, 2048, True), (200, 384, 1024, False),
+                                                (8, 49152, 2048, False), (100, 16384, 2048, False),
+                                                (16, 512, 512, False)])
 def test_no_alloc_entry_gives_the_bits_of_the_ordinary_one_twice_in_a_row(m, n, k, uses_scratch):
     lib, fn, ops = _lib_and_ops()
     assert bool(lib.bw_bf16_linear_tc_splits(m, n, k)) == uses_scratch
@@ -71,7 +73,7 @@ def test_no_alloc_entry_gives_the_bits_of_the_ordinary_one_twice_in_a_row(m, n, 
 def test_no_alloc_entry_refuses_what_does_not_fit():
     lib, fn, ops = _lib_and_ops()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    m, n, k = 128, 8192, 8192  # 16 chunks * 128 * 8192 floats = 16.8 M > 4 M
+    m, n, k = 16, 8192, 32768  # 64 chunks * 16 * 8192 floats = 8.4 M > 4 M
     x = torch.zeros(m, k, device="cuda:0", dtype=torch.bfloat16)
     w = torch.zeros(n, k, device="cuda:0", dtype=torch.bfloat16)
     y = torch.zeros(m, n, device="cuda:0")
