@@ -247,6 +247,23 @@ __device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 32-byte accesses: a thread of the epilogue owns a row, so a warp's store touches 32 rows;
+// whole 32-byte sectors keep the memory system from merging partial ones.
+__device__ __forceinline__ void st256(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+__device__ __forceinline__ void ld256(const void* p, uint32_t (&v)[8]) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "l"(p)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -310,8 +327,13 @@ __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num
   H[idx] = __float2bfloat16_rn(bw::swiglu_one(g, u));
 }
 
-// EPI 0: y = (residual +) product.  EPI 1 (whole mode only): the product is the interleaved
-// gate/up projection and y[m][n / 2] = SwiGLU of it (bfloat16).
+// EPI 0: y = product in bfloat16.  EPI 2: y = (residual +) product in float32.  EPI 1 (whole
+// mode only): the product is the interleaved gate/up projection and y[m][n / 2] = SwiGLU of it
+// (bfloat16). In split mode the kernel writes chunk sums and the second kernel finishes.
+//
+// A wide tile has no path for pieces that are cut by the matrix edge or that do not start on
+// 32 bytes (the path costs registers that the totals need): the host gives wide tiles only
+// products with n a multiple of 64 and outputs that start on 32 bytes.
 //
 // WIDE: the output tile is 128 x 256 instead of 128 x 128 and sixteen epilogue warps share it
 // (one row x 64 columns per thread). A wide tile needs a third less operand traffic per flop.
@@ -335,7 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   constexpr int kEpiWarps = WIDE ? 8 : 4;
   constexpr int kFirstEpiWarp = WIDE ? 4 : 2;  // wide: warps 0-3 are one warpgroup (loader, MMA, two idle)
   constexpr int PW = 64;                    // columns of one of the two pieces an epilogue thread owns
-  constexpr int LDW = 32;                   // columns per tcgen05.ld
+  constexpr int LDW = WIDE ? 64 : 32;       // columns per tcgen05.ld (what the register budget allows)
   constexpr int kTmemColsT = 2 * BNT;  // two accumulators
   const int bt = WIDE ? BNT : bn;           // columns of a work item's tile (bn: 16 .. 128 in steps of 16)
   const RingShape ring = ring_shape(A_ROWS, WIDE ? BNW : bn);
@@ -565,15 +587,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const int col0 = n0 + (piece ? off1 : off0);
           const int cols = min(PW, min(N, n0 + bt) - col0);
           float* mine = partials + (static_cast<size_t>(chunk) * M + row) * N + col0;
-          const float* t = total + piece * PW;
-          if (cols == PW && (N & 3) == 0) {
+          if (cols == PW && (N & 7) == 0 && (reinterpret_cast<uintptr_t>(partials) & 31) == 0) {
 #pragma unroll
-            for (int j = 0; j < PW; j += 4)
-              __stcg(reinterpret_cast<float4*>(mine + j), make_float4(t[j], t[j + 1], t[j + 2], t[j + 3]));
+            for (int j = 0; j < PW; j += 8) {
+              uint32_t o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(total[piece * PW + j + e]);
+              st256(mine + j, o);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < PW; ++j)
-              if (j < cols) __stcg(mine + j, t[j]);
+              if (!WIDE && j < cols) __stcg(mine + j, total[piece * PW + j]);
           }
         }
         continue;
@@ -583,18 +608,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // are rounded to bfloat16 first, as if the product had been stored
         if (n0 + off0 >= N) continue;
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + static_cast<size_t>(row) * (N / 2) + (n0 + blk * BN) / 2 + half * PW;
+        const bool wide_store = (reinterpret_cast<uintptr_t>(Y) & 31) == 0;  // rows are N bytes, N % 128 == 0
 #pragma unroll
-        for (int j = 0; j < PW; j += 8) {
-          __align__(16) __nv_bfloat162 o[4];
+        for (int j = 0; j < PW; j += 16) {
+          uint32_t o[8];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+          for (int e = 0; e < 8; ++e) {
             const float g0 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e]));
             const float g1 = __bfloat162float(__float2bfloat16_rn(total[j + 2 * e + 1]));
             const float u0 = __bfloat162float(__float2bfloat16_rn(total[PW + j + 2 * e]));
             const float u1 = __bfloat162float(__float2bfloat16_rn(total[PW + j + 2 * e + 1]));
-            o[e] = __floats2bfloat162_rn(bw::swiglu_one(g0, u0), bw::swiglu_one(g1, u1));
+            o[e] = pack_bf16(bw::swiglu_one(g0, u0), bw::swiglu_one(g1, u1));
           }
-          *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
+          if (wide_store) {
+            st256(out + j, o);
+          } else {
+            *reinterpret_cast<uint4*>(out + j) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(out + j + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+          }
         }
         continue;
       }
@@ -603,40 +634,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int col0 = n0 + (piece ? off1 : off0);
         const int cols = min(PW, min(N, n0 + bt) - col0);  // may be <= 0 in a narrow or a last, partial tile
         if (cols <= 0) continue;
-        const float* t = total + piece * PW;
         const size_t base = static_cast<size_t>(row) * N + col0;
-        if (y_is_f32) {
+        if (EPI == 2) {
           float* out = static_cast<float*>(Y) + base;
           const float* res = residual ? residual + base : nullptr;
-          if (cols == PW && (N & 3) == 0) {
+          if (cols == PW && (N & 7) == 0 && (reinterpret_cast<uintptr_t>(Y) & 31) == 0 &&
+              (reinterpret_cast<uintptr_t>(residual) & 31) == 0) {
 #pragma unroll
-            for (int j = 0; j < PW; j += 4) {
-              float4 o = make_float4(t[j], t[j + 1], t[j + 2], t[j + 3]);
+            for (int j = 0; j < PW; j += 8) {
+              uint32_t o[8];
               if (res) {
-                const float4 r = *reinterpret_cast<const float4*>(res + j);
-                o.x = r.x + o.x, o.y = r.y + o.y, o.z = r.z + o.z, o.w = r.w + o.w;
+                ld256(res + j, o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) + total[piece * PW + j + e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(total[piece * PW + j + e]);
               }
-              *reinterpret_cast<float4*>(out + j) = o;
+              st256(out + j, o);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < PW; ++j)  // static indices keep the totals in registers
-              if (j < cols) out[j] = res ? res[j] + t[j] : t[j];
+              if (!WIDE && j < cols) out[j] = res ? res[j] + total[piece * PW + j] : total[piece * PW + j];
           }
         } else {
           __nv_bfloat16* out = static_cast<__nv_bfloat16*>(Y) + base;
-          if (cols == PW && (N & 7) == 0) {
+          if (cols == PW && (N & 15) == 0 && (reinterpret_cast<uintptr_t>(Y) & 31) == 0) {
 #pragma unroll
-            for (int j = 0; j < PW; j += 8) {
-              __align__(16) __nv_bfloat162 o[4];
+            for (int j = 0; j < PW; j += 16) {
+              uint32_t o[8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(t[j + 2 * e], t[j + 2 * e + 1]);
-              *reinterpret_cast<uint4*>(out + j) = *reinterpret_cast<const uint4*>(o);
+              for (int e = 0; e < 8; ++e) o[e] = pack_bf16(total[piece * PW + j + 2 * e], total[piece * PW + j + 2 * e + 1]);
+              st256(out + j, o);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < PW; ++j)
-              if (j < cols) out[j] = __float2bfloat16_rn(t[j]);
+              if (!WIDE && j < cols) out[j] = __float2bfloat16_rn(total[piece * PW + j]);
           }
         }
       }
@@ -755,7 +790,7 @@ int g_force_mode = 0;  // 0: chosen; 1: whole; 2: split where it is possible
 
 constexpr int kMaxSplitColumns = 16384;  // bounds the scratch of the chunk sums
 
-Plan plan_rows(int m, int n, int k, bool swiglu, int sms) {
+Plan plan_rows(int m, int n, int k, bool swiglu, int sms, bool allow_wide = true) {
   const int chunks = (k + kChunk - 1) / kChunk;
   const int steps_chunk = kChunk / 16;
   const bool may_split = m <= BM && chunks > 1 && n <= kMaxSplitColumns;
@@ -767,6 +802,7 @@ Plan plan_rows(int m, int n, int k, bool swiglu, int sms) {
     if (g_force_mode == 2 && mode == 0 && may_split) continue;
     for (int bn = 16; bn <= 2 * BN; bn = (bn < BN ? bn + 16 : 2 * bn)) {
       if (swiglu && bn < BN) continue;  // gate and up of an output lie 64 columns apart
+      if (bn > BN && (!allow_wide || n % 64)) continue;
       if (g_tile_width && bn != g_tile_width && !(swiglu && g_tile_width < BN && bn == BN)) continue;
       const long long tiles = (n + bn - 1) / bn;
       const long long items = mode ? tiles * chunks : tiles;
@@ -890,8 +926,11 @@ int launch_tc_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int 
    : m <= 32 ? BW_LAUNCH(SPLIT_, 32, EPI_, WIDE_)                  \
    : m <= 64 ? BW_LAUNCH(SPLIT_, 64, EPI_, WIDE_)                  \
              : BW_LAUNCH(SPLIT_, 128, EPI_, WIDE_))
+  // wide tiles want whole pieces of 64 columns and 32-byte stores
+  const bool wide_ok = n % 64 == 0 && reinterpret_cast<uintptr_t>(y) % 32 == 0 &&
+                       reinterpret_cast<uintptr_t>(residual) % 32 == 0 && reinterpret_cast<uintptr_t>(partials) % 32 == 0;
   if (m <= BM) {
-    Plan plan = plan_rows(m, n, k, fused.mode == 2, sm_count_of_device());
+    Plan plan = plan_rows(m, n, k, fused.mode == 2, sm_count_of_device(), wide_ok);
     if (!partials) plan = Plan{false, plan.split ? BN : plan.bn};
     const bool wide = plan.bn > BN;
     if (plan.split) return wide ? BW_LAUNCH_ROWS(true, 0, true) : BW_LAUNCH_ROWS(true, 0, false);
@@ -899,6 +938,8 @@ int launch_tc_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int 
   }
 #undef BW_LAUNCH_ROWS
 #undef BW_LAUNCH
+  if (!wide_ok)
+    return launch_tc<false, 128, EPI, false>(x, w, y, y_is_f32, residual, m, n, k, error_word, nullptr, fused, stream);
   if (g_pair_tiles)
     return launch_tc<false, 128, EPI, true, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, nullptr, fused, stream);
   return launch_tc<false, 128, EPI, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, nullptr, fused, stream);
@@ -929,7 +970,8 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
   }
   if (const int rc = ensure_error_word()) return rc;
   const Fused none;
-  return launch_tc_rows<0>(x, w, y, y_is_f32, residual, m, n, k, g_error_flag, partials, none, stream);
+  if (y_is_f32) return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, g_error_flag, partials, none, stream);
+  return launch_tc_rows<0>(x, w, y, 0, nullptr, m, n, k, g_error_flag, partials, none, stream);
 }
 
 // h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows
@@ -1011,8 +1053,10 @@ BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w
   // Nothing in the scratch has to start at zero: every chunk sum that the second kernel reads
   // is written by the first one in this same call. The launcher raises the kernel's
   // shared-memory limit at its first use (no allocation either).
-  return launch_tc_rows<0>(x, w, y, y_is_f32, residual, m, n, k, g_noalloc_error_ptr[dev],
-                           split ? g_noalloc_scratch_ptr[dev] : nullptr, Fused(), stream);
+  float* scratch = split ? g_noalloc_scratch_ptr[dev] : nullptr;
+  if (y_is_f32)
+    return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, g_noalloc_error_ptr[dev], scratch, Fused(), stream);
+  return launch_tc_rows<0>(x, w, y, 0, nullptr, m, n, k, g_noalloc_error_ptr[dev], scratch, Fused(), stream);
 }
 
 // Reads and clears the word that a kernel launched by bw_bf16_linear_noalloc raises when one
