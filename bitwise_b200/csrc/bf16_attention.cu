@@ -341,8 +341,11 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
                        const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                        const int* __restrict__ row_seq, const int* __restrict__ pos, int heads, int kv_heads, int page,
                        int page_shift, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  // The step's index arrays (positions, row -> sequence, block tables) were copied to the
+  // device before the step's first kernel, and the keys and values of a tile that ends before
+  // the row's own position were stored by earlier steps: those loads are issued before the
+  // wait for the previous kernel (which stores this step's key and value and rotates q), so
+  // they overlap its tail.
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sq = smem;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -352,8 +355,20 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   const int first = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int t = blockIdx.z * kSplitWarps + warp;  // this warp's key tile
   const int block_first_tile = blockIdx.z * kSplitWarps;
-  if (block_first_tile * kTileKV > p || (block_first_tile + kSplitWarps) * kTileKV <= first) return;  // nothing in range
+  if (block_first_tile * kTileKV > p || (block_first_tile + kSplitWarps) * kTileKV <= first) {
+    bw::pdl_wait();
+    bw::pdl_launch();
+    return;  // nothing in range
+  }
   const int* table = block_table + static_cast<size_t>(row_seq[row]) * max_blocks;
+  const bool mine = t * kTileKV <= p && (t + 1) * kTileKV > first;  // the tile holds a key of the row's range
+  const bool settled = (t + 1) * kTileKV <= p;                      // all of it was stored by earlier steps
+  unsigned char* sk = smem + kSplitQBytes + warp * 2 * kKVBytes;
+  unsigned char* sv = sk + kKVBytes;
+  if (mine && settled)
+    load_kv_tile(sk, sv, kcache, vcache, table, page, page_shift, kv_heads, g, t * kTileKV, p + 1, lane, 32);
+  bw::pdl_wait();
+  bw::pdl_launch();
 
   for (int idx = tid; idx < 16 * kPieces; idx += kSplitWarps * 32) {
     const int m = idx / kPieces, piece = idx - m * kPieces;
@@ -361,10 +376,8 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
     const __nv_bfloat16* src = qkv + static_cast<size_t>(row) * q_stride + (g * group + (ok ? m : 0)) * HD + piece * 8;
     cp_async16(smem_u32(sq + piece_offset(m, piece)), src, ok);
   }
-  const bool mine = t * kTileKV <= p && (t + 1) * kTileKV > first;  // the tile holds a key of the row's range
-  unsigned char* sk = smem + kSplitQBytes + warp * 2 * kKVBytes;
-  unsigned char* sv = sk + kKVBytes;
-  if (mine) load_kv_tile(sk, sv, kcache, vcache, table, page, page_shift, kv_heads, g, t * kTileKV, p + 1, lane, 32);
+  if (mine && !settled)
+    load_kv_tile(sk, sv, kcache, vcache, table, page, page_shift, kv_heads, g, t * kTileKV, p + 1, lane, 32);
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();  // Q was loaded by all warps
@@ -388,40 +401,40 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
 }
 
 // Second half of split mode: per (row, head) the tile results are merged in ascending tile
-// order with the same formula as in whole mode; thread d carries output element d.
-__global__ void merge_tiles_kernel(const float* __restrict__ tile_out, int max_tiles, const int* __restrict__ pos,
-                                   __nv_bfloat16* __restrict__ out, int out_stride, int heads, int window) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+// order with the same formula as in whole mode; thread d carries output element d. The records
+// of up to kMergeBatch tiles are brought into shared memory by all threads together (one
+// round trip to memory instead of one per tile), then each thread walks them in order.
+constexpr int kMergeBatch = (10 * 1024) / (HD + 2) > 64 ? 64 : (10 * 1024) / (HD + 2);  // at most 40 KB of records
+constexpr int kMergeThreads = HD < 64 ? 64 : HD;
+
+__global__ void __launch_bounds__(kMergeThreads)
+merge_tiles_kernel(const float* __restrict__ tile_out, int max_tiles, const int* __restrict__ pos,
+                   __nv_bfloat16* __restrict__ out, int out_stride, int heads, int window) {
+  __shared__ float rec[kMergeBatch * (HD + 2)];
   const int r = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
-  const int p = pos[r];
+  const int p = pos[r];  // copied before the step began
   const int t_first = (window > 0 && p - window + 1 > 0) ? (p - window + 1) / kTileKV : 0;
   const int t_last = p / kTileKV;
   const float* src = tile_out + (static_cast<size_t>(r) * heads + h) * max_tiles * (HD + 2);
+  bw::pdl_wait();
+  bw::pdl_launch();
   float M = -INFINITY, L = 0.0f, O = 0.0f;
-  // the loads of four tiles are issued together; the merges stay in ascending order
-  int t = t_first;
-  for (; t + 4 <= t_last + 1; t += 4) {
-    const float* s0 = src + static_cast<size_t>(t) * (HD + 2);
-    const float m0 = s0[HD], l0 = s0[HD + 1], o0 = s0[d];
-    const float m1 = s0[(HD + 2) + HD], l1 = s0[(HD + 2) + HD + 1], o1 = s0[(HD + 2) + d];
-    const float m2 = s0[2 * (HD + 2) + HD], l2 = s0[2 * (HD + 2) + HD + 1], o2 = s0[2 * (HD + 2) + d];
-    const float m3 = s0[3 * (HD + 2) + HD], l3 = s0[3 * (HD + 2) + HD + 1], o3 = s0[3 * (HD + 2) + d];
-    MergeWeights w = merge_weights(M, m0);
-    M = w.mx, L = merge_value(L, l0, w), O = merge_value(O, o0, w);
-    w = merge_weights(M, m1);
-    M = w.mx, L = merge_value(L, l1, w), O = merge_value(O, o1, w);
-    w = merge_weights(M, m2);
-    M = w.mx, L = merge_value(L, l2, w), O = merge_value(O, o2, w);
-    w = merge_weights(M, m3);
-    M = w.mx, L = merge_value(L, l3, w), O = merge_value(O, o3, w);
+  for (int t0 = t_first; t0 <= t_last; t0 += kMergeBatch) {
+    const int count = min(kMergeBatch, t_last + 1 - t0);
+    const int floats = count * (HD + 2);
+    const float* from = src + static_cast<size_t>(t0) * (HD + 2);
+    if (t0 > t_first) __syncthreads();  // the previous batch has been read
+    for (int i = d; i < floats; i += kMergeThreads) rec[i] = __ldcg(from + i);
+    __syncthreads();
+    if (d < HD) {
+      for (int t = 0; t < count; ++t) {
+        const float* s0 = rec + t * (HD + 2);
+        const MergeWeights w = merge_weights(M, s0[HD]);
+        M = w.mx, L = merge_value(L, s0[HD + 1], w), O = merge_value(O, s0[d], w);
+      }
+    }
   }
-  for (; t <= t_last; ++t) {
-    const float* s0 = src + static_cast<size_t>(t) * (HD + 2);
-    const MergeWeights w = merge_weights(M, s0[HD]);
-    M = w.mx, L = merge_value(L, s0[HD + 1], w), O = merge_value(O, s0[d], w);
-  }
-  out[static_cast<size_t>(r) * out_stride + h * HD + d] = __float2bfloat16_rn(__fmul_rn(O, __fdiv_rn(1.0f, L)));
+  if (d < HD) out[static_cast<size_t>(r) * out_stride + h * HD + d] = __float2bfloat16_rn(__fmul_rn(O, __fdiv_rn(1.0f, L)));
 }
 
 }  // namespace
@@ -480,7 +493,7 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
     }
     bw::launch_pdl(attention_split_kernel, dim3(dim3(n, kv_heads, (key_tiles + kSplitWarps - 1) / kSplitWarps)), dim3(kSplitWarps * 32), split_smem, stream, qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, heads,
                                        kv_heads, page, page_shift, window, scale_log2, scratch, key_tiles);
-    bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(HD), 0, stream, scratch, key_tiles, pos, out, out_stride, heads, window);
+    bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(kMergeThreads), 0, stream, scratch, key_tiles, pos, out, out_stride, heads, window);
   } else {
     constexpr int smem = kQBytes + kStages * 2 * kKVBytes;
     if (!configured[0]) {

@@ -24,7 +24,9 @@ inline int launch_status() {
 // attribute below and begins with pdl_wait(), which returns once the kernel before it in the
 // stream has completed and its writes are visible; pdl_launch() right after lets the NEXT
 // kernel be set up on the SMs meanwhile, so that launch latency and block scheduling overlap
-// the running kernel instead of following it. Nothing is read or written before pdl_wait().
+// the running kernel instead of following it. Before pdl_wait() a kernel reads only what no
+// kernel of the same step writes: weights, the step's index arrays (copied to the device
+// before the step's first kernel) and cache entries that earlier steps stored.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
