@@ -30,7 +30,11 @@ constexpr int HD = BW_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int kTileM = 64;    // stacked (query row, head of the group) rows per block
 constexpr int kTileKV = 64;   // keys per tile
-constexpr int kSplitWarps = 4; // key tiles per block in split mode, one per warp
+// Key tiles per block in split mode, one per warp. One: a block is a single warp with its own
+// 16 KB of keys and values, a dozen of them share an SM, and each leaves as soon as its tile
+// is done, so loads stay in flight all the time (with four warps per block that wait for each
+// other the same kernel was a tenth slower).
+constexpr int kSplitWarps = 1;
 constexpr int kThreads = 128;
 // Rows of Q, K and V tiles in shared memory. When a row is a whole number of 128-byte lines
 // the 16-byte pieces of a line are xor-swizzled with the row number; other head sizes get 16
@@ -331,9 +335,9 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
 
 // ---------------------------------------------------------------------------------------
 // Split mode (decode steps: one query row per sequence, at most 16 stacked rows): a block
-// takes (row, key/value head, four consecutive key tiles), each warp one tile of its own: it
-// loads the tile, computes the tile result and stores it. Record layout per (row, head,
-// tile): o[HD], maximum, sum.
+// takes (row, key/value head, kSplitWarps consecutive key tiles), each warp one tile of its
+// own: it loads the tile, computes the tile result and stores it. Record layout per (row,
+// head, tile): o[HD], maximum, sum.
 constexpr int kSplitQBytes = 16 * kRowBytes;
 
 __global__ void __launch_bounds__(kSplitWarps * 32)
