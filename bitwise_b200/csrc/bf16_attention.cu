@@ -248,7 +248,7 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sq = smem;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tile = blockIdx.x, g = blockIdx.y;
+  const int tile = blockIdx.y, g = blockIdx.x;  // heads fastest: the host lists the longest tiles first
   const int group = heads / kv_heads;
   const int seq = tile_seq[tile], row0 = tile_row0[tile], nrows = tile_rows[tile];
   const int mrows = nrows * group;  // stacked rows in use (<= 64)
@@ -471,8 +471,8 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
     bw::set_error("attention: row strides %d / %d are not aligned for 16-byte loads", q_stride, out_stride);
     return -1;
   }
-  if (kv_heads > 65535 || heads > 65535) {
-    bw::set_error("attention: %d heads exceed the grid limit", heads);
+  if (kv_heads > 65535 || heads > 65535 || num_tiles > 65535) {
+    bw::set_error("attention: %d heads or %d query tiles exceed the grid limit", heads, num_tiles);
     return -1;
   }
   const float scale_log2 = scale * 1.44269504088896341f;
@@ -508,7 +508,7 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
       }
       configured[0] = true;
     }
-    bw::launch_pdl(attention_whole_kernel, dim3(dim3(num_tiles, kv_heads)), dim3(kThreads), smem, stream, 
+    bw::launch_pdl(attention_whole_kernel, dim3(dim3(kv_heads, num_tiles)), dim3(kThreads), smem, stream, 
         qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out,
         out_stride, heads, kv_heads, page, page_shift, window, scale_log2);
   }

@@ -190,9 +190,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   bw::pdl_wait();
   bw::pdl_launch();
 
-  // tiles are listed in row order and later rows of a prompt have more keys: taking them in
-  // reverse order starts the long blocks first, which shortens the tail of the launch
-  const int tile = gridDim.x - 1 - blockIdx.x, g = blockIdx.y;
+  // The host lists the tiles with the most keys first, and blocks are handed out with
+  // blockIdx.x running fastest: the heads of the longest tile start first, then those of the
+  // next one, so the long blocks do not start late and stretch the tail of the launch.
+  const int tile = blockIdx.y, g = blockIdx.x;
   const int group = heads / kv_heads;
   const int seq = tile_seq[tile], row0 = tile_row0[tile], nrows = tile_rows[tile];
   const int mrows = nrows * group;
@@ -457,6 +458,10 @@ BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __
                                 int heads, int kv_heads, int hd, int page, int window, float scale,
                                 cudaStream_t stream) {
   if (n <= 0 || num_tiles <= 0) return 0;
+  if (num_tiles > 65535) {
+    bw::set_error("attention (tcgen05): %d query tiles exceed the grid limit", num_tiles);
+    return -1;
+  }
   const int tile_rows_q = bw_bf16_attention_tc_tile_rows(heads, kv_heads, hd, page, q_stride);
   if (!tile_rows_q || out_stride % 8) {
     bw::set_error("attention (tcgen05): unsupported shape (heads %d/%d, head size %d, page %d)", heads, kv_heads, hd, page);
@@ -503,7 +508,7 @@ BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __
     }
   }
   const float scale_log2 = scale * 1.44269504088896341f;
-  bw::launch_pdl(attention_tc_kernel, dim3(num_tiles, kv_heads), dim3(kThreads), kSmemBytes, stream, map_q, map_k, map_v,
+  bw::launch_pdl(attention_tc_kernel, dim3(kv_heads, num_tiles), dim3(kThreads), kSmemBytes, stream, map_q, map_k, map_v,
                  block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out, out_stride, heads,
                  kv_heads, page, window, scale_log2, g_error_flag);
   return bw::launch_status();

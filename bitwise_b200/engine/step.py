@@ -190,15 +190,23 @@ class Stepper:
         h[L.seq_row0 + num_seqs] = n
         c = len(logit_rows)
         h[L.logit_rows:L.logit_rows + c] = logit_rows
+        # Query tiles, for every tile height in use, listed with the most keys first: a tile's
+        # attention takes as long as it has keys, and blocks that start in this order finish
+        # together instead of leaving the longest for last.
         tiles = {}
         for tr, (o_seq, o_row0, o_rows, cap) in L.tiles.items():
-            t = 0
+            listed = []
             for s, (r0, cnt) in enumerate(seq_rows):
                 for a in range(0, cnt, tr):
-                    h[o_seq + t] = s
-                    h[o_row0 + t] = r0 + a
-                    h[o_rows + t] = min(tr, cnt - a)
-                    t += 1
+                    rows_here = min(tr, cnt - a)
+                    listed.append((-(seq_pos0[s] + a + rows_here), s, r0 + a, rows_here))
+            if len(listed) > 1:
+                listed.sort()
+            t = len(listed)
+            if t:
+                h[o_seq:o_seq + t] = [x[1] for x in listed]
+                h[o_row0:o_row0 + t] = [x[2] for x in listed]
+                h[o_rows:o_rows + t] = [x[3] for x in listed]
             tiles[tr] = t
         self.dev.copy_(self.host, non_blocking=True)
         if self._copy_done is not None:
