@@ -78,6 +78,7 @@ class RequestCache:
     first_live: List[int]             # per group: first block index not yet given back
     length: int = 0                   # tokens whose keys/values are in the cache
     slot: int = -1
+    epoch: int = 0                    # goes up when the tables are emptied: entries seen before are void
 
 
 class CacheManager:
@@ -170,6 +171,7 @@ class CacheManager:
             table.clear()
             rc.first_live[g] = 0
         rc.length = 0
+        rc.epoch += 1
         if not keep_slot:
             self._free_slots.append(rc.slot)
             del self.requests[rid]

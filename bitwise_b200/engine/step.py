@@ -99,6 +99,9 @@ class Stepper:
         self.layout = _Layout(max_rows, max_seqs, [mb] * len(manager.groups), query_tile_rows(model))
         pin = self.device is not None and torch.device(self.device).type == "cuda"
         self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=pin)
+        self._host_np = self.host.numpy()
+        self._table_rows: Dict[tuple, tuple] = {}  # (batch row, cache group) -> what its table row holds
+        self._views: Dict[tuple, dict] = {}        # step sizes -> views of the device buffer
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
         self.workspace = Workspace(self.device, max_rows)
         self.vocab = model.head.vocab
@@ -137,13 +140,17 @@ class Stepper:
             raise StepError(f"{len(entries)} requests in one step; the stepper was built for {self.max_seqs}")
         seen = set()
         n = 0
-        h = self.host.numpy()
+        h = self._host_np
         seq_rows: List[Tuple[int, int]] = []
         seq_pos0: List[int] = []
         seq_slot: List[int] = []
         after: List[Tuple[Hashable, int]] = []
         logit_rows: List[int] = []
+        all_tokens: List[int] = []
+        all_pos: List[int] = []
+        all_row_seq: List[int] = []
         max_keys = 0
+        vocab = self.vocab
         for s, e in enumerate(entries):
             if e.rid in seen:
                 raise StepError(f"request {e.rid!r} appears twice in one step")
@@ -163,23 +170,29 @@ class Stepper:
                                     f"covers {mbg * mgr.page_size}")
             if not mgr.ensure(e.rid, start + cnt):
                 raise OutOfPages(f"no free page for request {e.rid!r} ({start} + {cnt} tokens)")
-            toks = list(e.tokens)
-            for t in toks:
-                if not (0 <= t < self.vocab):
-                    raise StepError(f"token id {t} outside the vocabulary of {self.vocab}")
-            h[L.tokens + n:L.tokens + n + cnt] = toks
-            h[L.pos + n:L.pos + n + cnt] = range(start, start + cnt)
-            h[L.row_seq + n:L.row_seq + n + cnt] = s
-            h[L.seq_row0 + s] = n
-            h[L.seq_pos0 + s] = start
-            h[L.seq_slot + s] = rc.slot
+            toks = e.tokens
+            if min(toks) < 0 or max(toks) >= vocab:
+                bad = next(t for t in toks if not (0 <= t < vocab))
+                raise StepError(f"token id {bad} outside the vocabulary of {vocab}")
+            all_tokens.extend(toks)
+            all_pos.extend(range(start, start + cnt))
+            all_row_seq.extend([s] * cnt)
             for w in e.want:
                 if not (0 <= w < cnt):
                     raise StepError(f"request {e.rid!r}: wanted place {w} outside its {cnt} tokens")
                 logit_rows.append(n + w)
+            # The row of the block table: the pinned buffer keeps what earlier steps wrote, so a
+            # request that sits in the same row as last time only adds the pages it gained.
             for g, table in enumerate(rc.tables):
                 base = L.tables[g] + s * L.max_blocks[g]
-                h[base:base + len(table)] = [p if p != FREED else 0 for p in table]
+                was = self._table_rows.get((s, g))
+                first_live = rc.first_live[g]
+                begin = was[1] if (was is not None and was[0] is rc and was[2] == first_live
+                                   and was[3] == rc.epoch and was[1] <= len(table)) else 0
+                if begin < len(table):
+                    part = table[begin:]
+                    h[base + begin:base + len(table)] = [p if p != FREED else 0 for p in part] if first_live > begin else part
+                self._table_rows[(s, g)] = (rc, len(table), first_live, rc.epoch)
             seq_rows.append((n, cnt))
             seq_pos0.append(start)
             seq_slot.append(rc.slot)
@@ -187,7 +200,12 @@ class Stepper:
             max_keys = max(max_keys, start + cnt)
             n += cnt
         num_seqs = len(entries)
-        h[L.seq_row0 + num_seqs] = n
+        h[L.tokens:L.tokens + n] = all_tokens
+        h[L.pos:L.pos + n] = all_pos
+        h[L.row_seq:L.row_seq + n] = all_row_seq
+        h[L.seq_row0:L.seq_row0 + num_seqs + 1] = [r[0] for r in seq_rows] + [n]
+        h[L.seq_pos0:L.seq_pos0 + num_seqs] = seq_pos0
+        h[L.seq_slot:L.seq_slot + num_seqs] = seq_slot
         c = len(logit_rows)
         h[L.logit_rows:L.logit_rows + c] = logit_rows
         # Query tiles, for every tile height in use, listed with the most keys first: a tile's
@@ -213,20 +231,36 @@ class Stepper:
             self._copy_done.record()
             self._copy_pending = True
         self.h2d_bytes = self.host.numel() * 4
-        d = self.dev
+        # The views of the device buffer depend on the step's sizes only: steps of a shape seen
+        # before take them from a small cache (slicing a tensor costs microseconds, a dozen each step).
+        shape = (n, num_seqs, c) + tuple(tiles.values())
+        views = self._views.get(shape)
+        if views is None:
+            d = self.dev
+            views = dict(
+                tokens=d[L.tokens:L.tokens + n], pos=d[L.pos:L.pos + n], row_seq=d[L.row_seq:L.row_seq + n],
+                seq_row0=d[L.seq_row0:L.seq_row0 + num_seqs + 1], seq_pos0=d[L.seq_pos0:L.seq_pos0 + num_seqs],
+                seq_slot=d[L.seq_slot:L.seq_slot + num_seqs], logit_rows=d[L.logit_rows:L.logit_rows + c],
+                tile_sets={tr: (d[o[0]:o[0] + tiles[tr]], d[o[1]:o[1] + tiles[tr]], d[o[2]:o[2] + tiles[tr]],
+                                tiles[tr]) for tr, o in L.tiles.items()},
+                block_tables=[d[L.tables[g]:L.tables[g] + num_seqs * L.max_blocks[g]].view(num_seqs, L.max_blocks[g])
+                              for g in range(len(L.max_blocks))])
+            if len(self._views) >= 512:
+                self._views.clear()
+            self._views[shape] = views
         first_tr = L.tile_rows[0]
         ctx = StepContext(
             ops=self.ops, workspace=self.workspace, n=n, num_seqs=num_seqs,
-            tokens=d[L.tokens:L.tokens + n], pos=d[L.pos:L.pos + n], row_seq=d[L.row_seq:L.row_seq + n],
-            seq_row0=d[L.seq_row0:L.seq_row0 + num_seqs + 1], seq_pos0=d[L.seq_pos0:L.seq_pos0 + num_seqs],
-            seq_slot=d[L.seq_slot:L.seq_slot + num_seqs], logit_rows=d[L.logit_rows:L.logit_rows + c],
+            tokens=views["tokens"], pos=views["pos"], row_seq=views["row_seq"], seq_row0=views["seq_row0"],
+            seq_pos0=views["seq_pos0"], seq_slot=views["seq_slot"], logit_rows=views["logit_rows"],
             num_logit_rows=c, max_keys=max_keys,
             host_seq_rows=seq_rows, host_seq_pos0=seq_pos0, host_seq_slot=seq_slot)
-        ctx.tile_sets = {tr: (d[o[0]:o[0] + tiles[tr]], d[o[1]:o[1] + tiles[tr]], d[o[2]:o[2] + tiles[tr]],
-                              tiles[tr]) for tr, o in L.tiles.items()}
+        ctx.tile_sets = views["tile_sets"]
         ctx.tile_seq, ctx.tile_row0, ctx.tile_rows, ctx.num_tiles = ctx.tile_sets[first_tr]
-        ctx.block_tables = [d[L.tables[g]:L.tables[g] + num_seqs * L.max_blocks[g]].view(num_seqs, L.max_blocks[g])
-                            for g in range(len(L.max_blocks))]
+        ctx.block_tables = views["block_tables"]
+        if "cache" not in views:
+            views["cache"] = self.storage.views(ctx.block_tables, ctx.seq_slot)
+        ctx.cache_views = views["cache"]
         return ctx, after
 
     # -- running -----------------------------------------------------------------------
@@ -234,7 +268,7 @@ class Stepper:
         """Run one step; returns float32 logits [wanted, vocab] on the device (a view of
         the stepper's buffer, valid until the next step) or None when nothing is wanted."""
         ctx, after = self.prepare(entries)
-        views = self.storage.views(ctx.block_tables, ctx.seq_slot)
+        views = ctx.cache_views
         key = None
         if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:
             # the longest context enters in steps of 256 keys: the attention kernel of a decode

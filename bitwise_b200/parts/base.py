@@ -120,6 +120,7 @@ class StepContext:
     # filled by the stepper: query tiles by tile height, and the device block table of each group
     tile_sets: Dict[int, tuple] = field(default_factory=dict)
     block_tables: List[torch.Tensor] = field(default_factory=list)
+    cache_views: List[object] = field(default_factory=list)  # one per cache entry, as the model's forward takes them
 
     def query_tiles(self, rows_per_tile: int):
         """(tile_seq, tile_row0, tile_rows, count) for tiles of at most ``rows_per_tile`` rows."""
