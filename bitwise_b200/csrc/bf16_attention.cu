@@ -243,8 +243,7 @@ attention_whole_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
                        const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
                        const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
                        int kv_heads, int page, int page_shift, int window, float scale_log2) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sq = smem;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -360,8 +359,7 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   const int t = blockIdx.z * kSplitWarps + warp;  // this warp's key tile
   const int block_first_tile = blockIdx.z * kSplitWarps;
   if (block_first_tile * kTileKV > p || (block_first_tile + kSplitWarps) * kTileKV <= first) {
-    bw::pdl_wait();
-    bw::pdl_launch();
+    bw::pdl_enter();
     return;  // nothing in range
   }
   const int* table = block_table + static_cast<size_t>(row_seq[row]) * max_blocks;
@@ -371,8 +369,7 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   unsigned char* sv = sk + kKVBytes;
   if (mine && settled)
     load_kv_tile(sk, sv, kcache, vcache, table, page, page_shift, kv_heads, g, t * kTileKV, p + 1, lane, 32);
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
 
   for (int idx = tid; idx < 16 * kPieces; idx += kSplitWarps * 32) {
     const int m = idx / kPieces, piece = idx - m * kPieces;
@@ -420,8 +417,7 @@ merge_tiles_kernel(const float* __restrict__ tile_out, int max_tiles, const int*
   const int t_first = (window > 0 && p - window + 1 > 0) ? (p - window + 1) / kTileKV : 0;
   const int t_last = p / kTileKV;
   const float* src = tile_out + (static_cast<size_t>(r) * heads + h) * max_tiles * (HD + 2);
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   float M = -INFINITY, L = 0.0f, O = 0.0f;
   for (int t0 = t_first; t0 <= t_last; t0 += kMergeBatch) {
     const int count = min(kMergeBatch, t_last + 1 - t0);

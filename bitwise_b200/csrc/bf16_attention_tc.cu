@@ -187,8 +187,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
 
   // The host lists the tiles with the most keys first, and blocks are handed out with
   // blockIdx.x running fastest: the heads of the longest tile start first, then those of the

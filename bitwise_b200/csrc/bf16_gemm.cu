@@ -56,8 +56,7 @@ template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool SPLIT>
 __global__ void __launch_bounds__(WARPS_M * WARPS_N * 32)
 gemm_bf16_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* Y, int y_is_f32,
                  const float* residual, int M, int N, int K, int aligned, float* partials, int* counters) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   constexpr int THREADS = WARPS_M * WARPS_N * 32;
   constexpr int WTM = BM / WARPS_M, WTN = BN / WARPS_N;
   constexpr int MI = WTM / 16, NI = WTN / 8;

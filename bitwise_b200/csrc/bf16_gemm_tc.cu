@@ -272,8 +272,7 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 // the additions stay in order.
 __global__ void reduce_chunks_kernel(const float* __restrict__ partials, int num_chunks, void* Y, int y_is_f32,
                                      const float* residual, int M, int N) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const size_t total = static_cast<size_t>(M) * N;
   const size_t o = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (o >= total) return;
@@ -314,8 +313,7 @@ __device__ __forceinline__ float ordered_chunk_sum(const float* __restrict__ par
 // rounded to bfloat16 first, as if the product had been stored, then combined.
 __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num_chunks, __nv_bfloat16* __restrict__ H,
                                      int M, int N) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int inter = N / 2;
   const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   if (idx >= static_cast<size_t>(M) * inter) return;

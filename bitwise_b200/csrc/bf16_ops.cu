@@ -15,8 +15,7 @@ constexpr int kNormThreads = 256;
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
                     const int* __restrict__ rows, int width, float eps) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const float* xr = x + static_cast<size_t>(src) * width;
@@ -67,8 +66,7 @@ __global__ void rope_cache_bf16_kernel(__nv_bfloat16* qkv, int row_stride, const
                                        const float* __restrict__ sin_t, const int* __restrict__ block_table,
                                        int max_blocks, __nv_bfloat16* kcache, __nv_bfloat16* vcache, int heads,
                                        int kv_heads, int hd, int page, int write_kv) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int r = blockIdx.x;
   const int half = hd >> 1, per_head = half >> 3;  // items of 8 pairs per head
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
@@ -121,8 +119,7 @@ using bw::swiglu_one;
 
 __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                        int inter) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int r = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= inter) return;
@@ -142,8 +139,7 @@ __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up
 
 __global__ void swiglu_bf16_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                    int inter) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int r = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= inter) return;

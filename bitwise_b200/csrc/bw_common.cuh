@@ -21,14 +21,25 @@ inline int launch_status() {
 }
 
 // Programmatic dependent launch: every kernel of the serving path is launched with the
-// attribute below and begins with pdl_wait(), which returns once the kernel before it in the
-// stream has completed and its writes are visible; pdl_launch() right after lets the NEXT
-// kernel be set up on the SMs meanwhile, so that launch latency and block scheduling overlap
-// the running kernel instead of following it. Before pdl_wait() a kernel reads only what no
+// attribute below. pdl_launch() at its very start lets the NEXT kernel's blocks be placed on
+// the SMs as soon as all of this kernel's blocks have started; pdl_wait() returns once the
+// kernel before this one in the stream has completed and its writes are visible (and that
+// kernel had itself waited for its predecessor, so everything earlier is complete too). Launch
+// latency and block scheduling thus overlap the running kernels instead of following them. Before pdl_wait() a kernel reads only what no
 // kernel of the same step writes: weights, the step's index arrays (copied to the device
 // before the step's first kernel) and cache entries that earlier steps stored.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// What most kernels begin with. A launch of few blocks (a decode step's kernels) lets its
+// successor be placed at once and then waits; a launch of many blocks waits first, so that the
+// successor's blocks do not take SMs while this kernel still has blocks to place (measured:
+// early placement speeds a decode step up by 4 % and slows a 2,048-token prefill down by 4 %).
+__device__ __forceinline__ void pdl_enter() {
+  const bool few = gridDim.x * gridDim.y * gridDim.z <= 296;
+  if (few) pdl_launch();
+  pdl_wait();
+  if (!few) pdl_launch();
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

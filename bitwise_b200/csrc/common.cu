@@ -23,8 +23,7 @@ BW_API const char* bw_last_error() { return bw::g_error; }
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                   float* __restrict__ out, int n, int width) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int r = blockIdx.x;
   const T* src = table + static_cast<size_t>(tokens[r]) * width;
   float* dst = out + static_cast<size_t>(r) * width;
@@ -55,8 +54,7 @@ constexpr int kSampleThreads = 512;
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
                    const double* __restrict__ uniform, int* __restrict__ out_token) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int row = blockIdx.x;
   const float* l = logits + static_cast<size_t>(row) * vocab;
   const int tid = threadIdx.x;
@@ -168,8 +166,7 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 
 __global__ void fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab,
                                         const int* __restrict__ slot, unsigned long long* __restrict__ state) {
-  bw::pdl_wait();
-  bw::pdl_launch();
+  bw::pdl_enter();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const uint32_t* w = reinterpret_cast<const uint32_t*>(logits + static_cast<size_t>(r) * vocab);
