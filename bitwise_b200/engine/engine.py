@@ -159,11 +159,13 @@ class Engine:
         return self.results[rid]
 
     # -- internals -------------------------------------------------------------------------
-    def _save_fingerprint(self, seq: Sequence) -> None:
-        """Before a request loses its slot, bring its fingerprint to the host."""
-        self._save_fingerprint_final(seq)
-        if seq.running:
-            self.results[seq.id].preemptions += 1
+    def _save_fingerprint(self, seq: Sequence, slot: int) -> None:
+        """A request was preempted and lost its slot: bring its fingerprint to the host (the
+        slot's contents stay as they were until the coming step runs)."""
+        if self.config.fingerprint_logits and seq.id in self._fp_live and slot >= 0:
+            self.results[seq.id].logits_fingerprint = int(self.storage.fingerprints[slot].item()) & ((1 << 64) - 1)
+        self._fp_live.discard(seq.id)
+        self.results[seq.id].preemptions += 1
 
     def _finish(self, seq: Sequence, cancelled: bool) -> None:
         self._save_fingerprint_final(seq)

@@ -1,6 +1,12 @@
 """Continuous batching above the step function: admit, cut prompts into portions under a
 token budget, decode, finish and free; recompute preemption when pages run out.
 
+The decisions are taken in C++ (``Scheduler`` in csrc/host_runtime.cpp, next to the cache
+manager it asks for pages); this class owns the requests' tokens, tells the library before
+every plan how many tokens each running request has and how many of them are computed, and
+mirrors what the plan did (rows to run, requests preempted or admitted) back onto the
+``Sequence`` objects.
+
 The policy is the reference's (src/engine.cpp:304-377), decision for decision:
 
 1. Running requests are served oldest first (by id).  A request needs
@@ -18,16 +24,15 @@ The policy is the reference's (src/engine.cpp:304-377), decision for decision:
    newcomer.  (src/engine.cpp:354-376)
 4. A request that could never fit is refused when it is added (src/engine.cpp:130-133).
 
-This class decides only; it never touches a device.  ``Engine`` (engine/engine.py) runs
-what it plans.
+Nothing here touches a device.  ``Engine`` (engine/engine.py) runs what is planned.
 """
 from __future__ import annotations
 
-import bisect
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Tuple
+import ctypes
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
 
+from .. import host
 from ..cache.manager import CacheManager
 from ..sampling.sampler import SamplingParams
 
@@ -54,113 +59,148 @@ class Planned:
     n: int  # rows to run for it in this step
 
 
-@dataclass
 class SchedulerStats:
-    preemptions: int = 0
-    admitted: int = 0
+    def __init__(self, scheduler: "Scheduler"):
+        self._s = scheduler
+
+    @property
+    def preemptions(self) -> int:
+        return int(self._s._lib.bw_sched_stat(self._s._h, 0))
+
+    @property
+    def admitted(self) -> int:
+        return int(self._s._lib.bw_sched_stat(self._s._h, 1))
+
+
+class SchedulerError(RuntimeError):
+    pass
 
 
 class Scheduler:
     def __init__(self, manager: CacheManager, max_batched_tokens: int, max_num_seqs: int):
         if max_batched_tokens <= 0 or max_num_seqs <= 0:
             raise ValueError("max_batched_tokens and max_num_seqs must be positive")
+        self._lib = host.lib()
         self.manager = manager
         self.max_batched_tokens = max_batched_tokens
         self.max_num_seqs = max_num_seqs
-        self.running: List[Sequence] = []       # sorted by id
-        self.waiting: Deque[Sequence] = deque()  # first in, first out; preempted ones re-enter in id order
-        self.stats = SchedulerStats()
-        self.preempted_log: List[int] = []      # ids in the order they were preempted
-        self.on_preempt = None                  # callback(seq) before its pages go back
+        self._h = self._lib.bw_sched_create(manager._h, max_batched_tokens, max_num_seqs)
+        if not self._h:
+            raise SchedulerError(host.last_error())
+        self._seqs: Dict[int, Sequence] = {}     # the library's key -> request
+        self._key: Dict[int, int] = {}           # request id -> key
+        cap = max(64, 2 * max_num_seqs + 16)
+        self._ids = (ctypes.c_int64 * cap)()
+        self._ints = (ctypes.c_int * cap)()
+        self._ints2 = (ctypes.c_int * cap)()
+        self._cap = cap
+        self.stats = SchedulerStats(self)
+        self.preempted_log: List[int] = []       # ids in the order they were preempted
+        # callback(seq, slot) for a request that has just been preempted: ``slot`` is the state
+        # slot it held (its contents stay untouched until the step that follows runs)
+        self.on_preempt: Optional[Callable[[Sequence, int], None]] = None
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.bw_sched_destroy(self._h)
+            self._h = None
+
+    def _grow(self, n: int) -> None:
+        if n > self._cap:
+            self._cap = 2 * n
+            self._ids = (ctypes.c_int64 * self._cap)()
+            self._ints = (ctypes.c_int * self._cap)()
+            self._ints2 = (ctypes.c_int * self._cap)()
 
     # -- queue operations --------------------------------------------------------------
     def add(self, seq: Sequence) -> None:
-        self.waiting.append(seq)
+        key = self.manager.key_of(seq.id)
+        self.manager.hold_key(seq.id)
+        if self._lib.bw_sched_add(self._h, key, int(seq.id), len(seq.tokens), seq.computed) < 0:
+            raise SchedulerError(host.last_error())
+        self._seqs[key] = seq
+        self._key[seq.id] = key
+
+    def _listed(self, fn) -> List[Sequence]:
+        n = fn(self._h, self._ids, self._cap)
+        if n > self._cap:
+            self._grow(n)
+            n = fn(self._h, self._ids, self._cap)
+        return [self._seqs[self._ids[i]] for i in range(n)]
+
+    @property
+    def running(self) -> List[Sequence]:
+        """Running requests, oldest first."""
+        return self._listed(self._lib.bw_sched_running)
+
+    @property
+    def waiting(self) -> List[Sequence]:
+        """Waiting requests in the order they will be admitted."""
+        return self._listed(self._lib.bw_sched_waiting)
 
     def idle(self) -> bool:
-        return not self.running and not self.waiting
+        return not self._seqs
 
-    def _release(self, seq: Sequence) -> None:
-        if self.manager.has(seq.id):
-            self.manager.release(seq.id)
-        seq.computed = 0
+    def _mirror_preempted(self) -> None:
+        n = self._lib.bw_sched_preempted(self._h, self._ids, self._ints, self._cap)
+        gone = []
+        for i in range(min(n, self._cap)):
+            seq = self._seqs[self._ids[i]]
+            seq.computed = 0
+            seq.running = False
+            gone.append((seq, self._ints[i]))
+        self.manager.sync_with_library([s.id for s, _ in gone])
+        for seq, slot in gone:
+            self.preempted_log.append(seq.id)
+            if self.on_preempt is not None:
+                self.on_preempt(seq, slot)
 
     def preempt(self, seq: Sequence) -> None:
-        if self.on_preempt is not None:
-            self.on_preempt(seq)
-        self._release(seq)
-        seq.running = False
-        self.running.remove(seq)
-        pos = 0
-        while pos < len(self.waiting) and self.waiting[pos].id < seq.id:
-            pos += 1
-        self.waiting.insert(pos, seq)
-        self.stats.preemptions += 1
-        self.preempted_log.append(seq.id)
+        self._push([seq])
+        if self._lib.bw_sched_preempt(self._h, self._key[seq.id]) < 0:
+            raise SchedulerError(host.last_error())
+        self._mirror_preempted()
 
     def finish(self, seq: Sequence) -> None:
         """The request is over (done or cancelled): pages and slot go back, queues forget it."""
-        self._release(seq)
-        if seq.running:
-            self.running.remove(seq)
-        elif seq in self.waiting:
-            self.waiting.remove(seq)
+        key = self._key.pop(seq.id)
+        if self._lib.bw_sched_finish(self._h, key) < 0:
+            raise SchedulerError(host.last_error())
+        del self._seqs[key]
+        seq.computed = 0
         seq.running = False
         seq.done = True
+        self.manager.sync_with_library([seq.id])
+        self.manager.drop_key(seq.id)
 
-    def _pick_victim(self, protect: List[Sequence]) -> Optional[Sequence]:
-        for s in reversed(self.running):
-            if s not in protect:
-                return s
-        return None
+    def _push(self, seqs: List[Sequence]) -> None:
+        n = len(seqs)
+        self._grow(n)
+        for i, s in enumerate(seqs):
+            self._ids[i] = self._key[s.id]
+            self._ints[i] = len(s.tokens)
+            self._ints2[i] = s.computed
+        if n and self._lib.bw_sched_update_many(self._h, n, self._ids, self._ints, self._ints2) < 0:
+            raise SchedulerError(host.last_error())
 
     # -- one step's plan ---------------------------------------------------------------
     def plan(self) -> List[Planned]:
-        budget = self.max_batched_tokens
-        plan: List[Planned] = []
-        scheduled: List[Sequence] = []
-        for s in list(self.running):
+        # the library learns how far every request has come (tokens are appended and rows
+        # computed on this side), then decides
+        self._push(list(self._seqs.values()))
+        waiting_head = self.waiting[:1]
+        n = self._lib.bw_sched_plan(self._h)
+        self._grow(n)
+        self._mirror_preempted()
+        n = self._lib.bw_sched_plan_entries(self._h, self._ids, self._ints, self._cap)
+        plan = [Planned(self._seqs[self._ids[i]], self._ints[i]) for i in range(n)]
+        # requests that the plan admitted hold pages and a slot now; a head that could not be
+        # admitted gave back what it took
+        self.manager.sync_with_library([p.seq.id for p in plan] + [s.id for s in waiting_head])
+        running = self.running
+        for s in running:
             if not s.running:
-                continue  # preempted earlier in this loop
-            need = len(s.tokens) - s.computed
-            n = need
-            if n == 0:
-                continue
-            if n > budget:
-                if budget <= 0:
-                    continue
-                n = budget
-            ok = self.manager.ensure(s.id, s.computed + n)
-            while not ok:
-                victim = self._pick_victim(scheduled + [s])
-                if victim is None:
-                    break
-                self.preempt(victim)
-                ok = self.manager.ensure(s.id, s.computed + n)
-            if not ok:
-                self.preempt(s)
-                continue
-            plan.append(Planned(s, n))
-            scheduled.append(s)
-            budget -= n
-        while self.waiting and len(self.running) < self.max_num_seqs:
-            if budget <= 0:
-                break
-            s = self.waiting[0]
-            need = len(s.tokens) - s.computed
-            n = min(need, budget)
-            if not self.manager.has(s.id):
-                if self.manager.free_slots() == 0:
-                    break
-                self.manager.begin(s.id)
-            if not self.manager.ensure(s.id, s.computed + n):
-                self._release(s)
-                break
-            self.waiting.popleft()
-            s.running = True
-            bisect.insort(self.running, s, key=lambda q: q.id)
-            self.stats.admitted += 1
-            if n > 0:
-                plan.append(Planned(s, n))
-                budget -= n
+                s.running = True
+        if len(running) > len(plan):  # a running request with nothing to do this step may not be listed
+            self.manager.sync_with_library([s.id for s in running])
         return plan

@@ -100,7 +100,16 @@ class Stepper:
         pin = self.device is not None and torch.device(self.device).type == "cuda"
         self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=pin)
         self._host_np = self.host.numpy()
-        self._table_rows: Dict[tuple, tuple] = {}  # (batch row, cache group) -> what its table row holds
+        self._host_address = self.host.data_ptr()
+        import ctypes
+        groups = len(self.layout.max_blocks)
+        self._rows = manager.new_rows(max_seqs)    # what each row of the block tables in the pinned buffer holds
+        self._keys_buf = (ctypes.c_int64 * max_seqs)()
+        self._counts_buf = (ctypes.c_int * max_seqs)()
+        self._starts_buf = (ctypes.c_int * max_seqs)()
+        self._slots_buf = (ctypes.c_int * max_seqs)()
+        self._table_offsets = (ctypes.c_int * max(groups, 1))(*self.layout.tables)
+        self._max_blocks_buf = (ctypes.c_int * max(groups, 1))(*self.layout.max_blocks)
         self._views: Dict[tuple, dict] = {}        # step sizes -> views of the device buffer
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
         self.workspace = Workspace(self.device, max_rows)
@@ -139,18 +148,10 @@ class Stepper:
         if len(entries) > self.max_seqs:
             raise StepError(f"{len(entries)} requests in one step; the stepper was built for {self.max_seqs}")
         seen = set()
-        n = 0
         h = self._host_np
-        seq_rows: List[Tuple[int, int]] = []
-        seq_pos0: List[int] = []
-        seq_slot: List[int] = []
-        after: List[Tuple[Hashable, int]] = []
-        logit_rows: List[int] = []
-        all_tokens: List[int] = []
-        all_pos: List[int] = []
-        all_row_seq: List[int] = []
-        max_keys = 0
         vocab = self.vocab
+        num_seqs = len(entries)
+        rows_total = 0
         for s, e in enumerate(entries):
             if e.rid in seen:
                 raise StepError(f"request {e.rid!r} appears twice in one step")
@@ -158,48 +159,55 @@ class Stepper:
             cnt = len(e.tokens)
             if cnt == 0:
                 raise StepError(f"request {e.rid!r} brings no tokens")
-            if n + cnt > self.max_rows:
+            rows_total += cnt
+            if rows_total > self.max_rows:
                 raise StepError(f"step of more than {self.max_rows} rows")
-            if not mgr.has(e.rid):
-                mgr.begin(e.rid)
-            rc = mgr.get(e.rid)
-            start = rc.length
-            for g, mbg in enumerate(L.max_blocks):
-                if (start + cnt + mgr.page_size - 1) // mgr.page_size > mbg:
-                    raise StepError(f"request {e.rid!r} would hold {start + cnt} tokens; the block table "
-                                    f"covers {mbg * mgr.page_size}")
-            if not mgr.ensure(e.rid, start + cnt):
-                raise OutOfPages(f"no free page for request {e.rid!r} ({start} + {cnt} tokens)")
             toks = e.tokens
             if min(toks) < 0 or max(toks) >= vocab:
                 bad = next(t for t in toks if not (0 <= t < vocab))
                 raise StepError(f"token id {bad} outside the vocabulary of {vocab}")
-            all_tokens.extend(toks)
-            all_pos.extend(range(start, start + cnt))
-            all_row_seq.extend([s] * cnt)
             for w in e.want:
                 if not (0 <= w < cnt):
                     raise StepError(f"request {e.rid!r}: wanted place {w} outside its {cnt} tokens")
+            if not mgr.has(e.rid):
+                mgr.begin(e.rid)
+            self._keys_buf[s] = mgr.get(e.rid)._key
+            self._counts_buf[s] = cnt
+        # Pages and block-table rows, in the library, for all requests at once: every request
+        # takes the pages its new tokens need, and its rows of the block tables in the pinned
+        # buffer are brought up to date (a request that sits in the same row as in the step
+        # before only adds the pages it gained).
+        rc = mgr.prepare_rows(self._rows, num_seqs, self._keys_buf, self._counts_buf, self._host_address,
+                              self._table_offsets, self._max_blocks_buf, self._starts_buf, self._slots_buf)
+        if rc > 0:
+            e = entries[rc - 1]
+            raise OutOfPages(f"no free page for request {e.rid!r} ({mgr.length(e.rid)} + {len(e.tokens)} tokens)")
+        if rc < 0:
+            e = entries[-rc - 2]
+            raise StepError(f"request {e.rid!r} would hold {mgr.length(e.rid) + len(e.tokens)} tokens; the block "
+                            f"table covers {min(L.max_blocks) * mgr.page_size}")
+        n = 0
+        seq_rows: List[Tuple[int, int]] = []
+        seq_pos0: List[int] = self._starts_buf[:num_seqs]
+        seq_slot: List[int] = self._slots_buf[:num_seqs]
+        after: List[Tuple[Hashable, int]] = []
+        logit_rows: List[int] = []
+        all_tokens: List[int] = []
+        all_pos: List[int] = []
+        all_row_seq: List[int] = []
+        max_keys = 0
+        for s, e in enumerate(entries):
+            cnt = len(e.tokens)
+            start = seq_pos0[s]
+            all_tokens.extend(e.tokens)
+            all_pos.extend(range(start, start + cnt))
+            all_row_seq.extend([s] * cnt)
+            for w in e.want:
                 logit_rows.append(n + w)
-            # The row of the block table: the pinned buffer keeps what earlier steps wrote, so a
-            # request that sits in the same row as last time only adds the pages it gained.
-            for g, table in enumerate(rc.tables):
-                base = L.tables[g] + s * L.max_blocks[g]
-                was = self._table_rows.get((s, g))
-                first_live = rc.first_live[g]
-                begin = was[1] if (was is not None and was[0] is rc and was[2] == first_live
-                                   and was[3] == rc.epoch and was[1] <= len(table)) else 0
-                if begin < len(table):
-                    part = table[begin:]
-                    h[base + begin:base + len(table)] = [p if p != FREED else 0 for p in part] if first_live > begin else part
-                self._table_rows[(s, g)] = (rc, len(table), first_live, rc.epoch)
             seq_rows.append((n, cnt))
-            seq_pos0.append(start)
-            seq_slot.append(rc.slot)
             after.append((e.rid, start + cnt))
             max_keys = max(max_keys, start + cnt)
             n += cnt
-        num_seqs = len(entries)
         h[L.tokens:L.tokens + n] = all_tokens
         h[L.pos:L.pos + n] = all_pos
         h[L.row_seq:L.row_seq + n] = all_row_seq

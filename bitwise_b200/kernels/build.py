@@ -156,8 +156,57 @@ def ensure_built(kind: str, defines: Sequence[str] = (), verbose: bool = True) -
     return out
 
 
+# ---- the host runtime (plain C++: page pools, cache manager, scheduler) ------------------
+HOST_SOURCES = ("host_runtime.cpp",)
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def find_cxx() -> str:
+    cands = [os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")]
+    for c in cands:
+        if c and os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    raise BuildError("no C++ compiler found ($CXX, g++, c++, clang++): the host runtime cannot be compiled")
+
+
+def host_library_file() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(HOST_FLAGS).encode())
+    for f in HOST_SOURCES:
+        h.update(f.encode())
+        with open(os.path.join(CSRC, f), "rb") as fh:
+            h.update(fh.read())
+    return os.path.join(_build_root(), f"libbitwise_host-{h.hexdigest()[:12]}.so")
+
+
+def ensure_host_built(verbose: bool = True) -> str:
+    """Return the path of the host runtime's library, compiling it if needed (no CUDA involved)."""
+    out = host_library_file()
+    if os.path.isfile(out):
+        return out
+    cxx = find_cxx()
+    _say(f"compiling the host runtime ({', '.join(HOST_SOURCES)}) with {cxx}", verbose)
+    t0 = time.time()
+    tmp = out + f".tmp{os.getpid()}"
+    cmd = [cxx, *HOST_FLAGS, *[os.path.join(CSRC, f) for f in HOST_SOURCES], "-o", tmp]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"{cxx} failed on the host runtime:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, out)
+    root = os.path.dirname(out)
+    for f in os.listdir(root):
+        if f.startswith("libbitwise_host-") and f.endswith(".so") and os.path.join(root, f) != out:
+            try:
+                os.remove(os.path.join(root, f))
+            except OSError:
+                pass
+    _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s", verbose)
+    return out
+
+
 def build_all(verbose: bool = True) -> List[str]:
     """Compile every kernel set (what a 'does it build' check wants)."""
-    out = [ensure_built(k, (), verbose) for k in ("f32", "bf16")]
+    out = [ensure_host_built(verbose)]
+    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16")]
     out += [ensure_built("bf16_attn", (f"BW_HEAD_DIM={hd}",), verbose) for hd in DEFAULT_HEAD_DIMS]
     return out
