@@ -816,6 +816,17 @@ Plan plan_rows(int m, int n, int k, bool swiglu, int sms, bool allow_wide = true
 
 }  // namespace
 
+// Steps of few rows take the streaming kernel of bf16_gemm_rows.cu (same bits), unless a test
+// or a measurement forces a plan of this file's kernel.
+BW_API int bw_bf16_linear_rows_usable(const void* x, const void* w, int m, int n, int k, int swiglu);
+BW_API int bw_bf16_linear_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_kind, const float* residual,
+                               int m, int n, int k, cudaStream_t stream);
+namespace {
+bool rows_path_takes(int m, int n, int k, int swiglu, const void* x = nullptr, const void* w = nullptr) {
+  return g_tile_width == 0 && g_force_mode == 0 && bw_bf16_linear_rows_usable(x, w, m, n, k, swiglu) != 0;
+}
+}  // namespace
+
 // Forces the width of the output tiles of small batches (a multiple of 16 up to 128, or 256;
 // 0: chosen from the shape) and the mode (0 chosen, 1 whole, 2 split where possible). Every
 // combination gives the same bits. For tests and measurements.
@@ -832,6 +843,7 @@ BW_API int bw_bf16_linear_tc_splits(int m, int n, int k) {
 BW_API int bw_bf16_linear_tc_may_split(int m, int n, int k) { return m <= BM && k > kChunk && n <= kMaxSplitColumns; }
 // Kernels that one call launches (1, or 2 when the product is split): callers count launches.
 BW_API int bw_bf16_linear_tc_kernels(int m, int n, int k, int swiglu, int has_scratch) {
+  if (rows_path_takes(m, n, k, swiglu)) return 1;
   return (m <= BM && has_scratch && plan_rows(m, n, k, swiglu != 0, sm_count_of_device()).split) ? 2 : 1;
 }
 
@@ -966,6 +978,7 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
     bw::set_error("linear (tcgen05): rows must start on 16 bytes (k %% 8 == 0) and the driver must offer tensor maps");
     return -1;
   }
+  if (rows_path_takes(m, n, k, 0, x, w)) return bw_bf16_linear_rows(x, w, y, y_is_f32 ? 2 : 0, residual, m, n, k, stream);
   if (const int rc = ensure_error_word()) return rc;
   const Fused none;
   if (y_is_f32) return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, g_error_flag, partials, none, stream);
@@ -981,6 +994,7 @@ BW_API int bw_bf16_linear_tc_swiglu(const __nv_bfloat16* x, const __nv_bfloat16*
     bw::set_error("linear + SwiGLU: needs n %% 128 == 0 (got %d) and rows that start on 16 bytes", n);
     return -1;
   }
+  if (rows_path_takes(m, n, k, 1, x, w)) return bw_bf16_linear_rows(x, w, h, 1, nullptr, m, n, k, stream);
   if (const int rc = ensure_error_word()) return rc;
   Fused f;
   f.mode = 2;

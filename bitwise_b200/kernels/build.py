@@ -28,7 +28,8 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # kernel set -> list of (source file, extra flags)
 KERNEL_SETS: Dict[str, List[tuple]] = {
     "f32": [("common.cu", []), ("exact_f32.cu", ["-fmad=false"])],
-    "bf16": [("common.cu", []), ("bf16_ops.cu", []), ("bf16_gemm.cu", []), ("bf16_gemm_tc.cu", [])],
+    "bf16": [("common.cu", []), ("bf16_ops.cu", []), ("bf16_gemm.cu", []), ("bf16_gemm_tc.cu", []),
+             ("bf16_gemm_rows.cu", [])],
     # compiled once per head size, with -DBW_HEAD_DIM=<n>
     "bf16_attn": [("common.cu", []), ("bf16_attention.cu", []), ("bf16_attention_tc.cu", [])],
 }

@@ -263,12 +263,22 @@ class KernelOps:
             return False
         return bool(self.lib.bw_bf16_linear_tc_pair_tiles(_c_int(int(on))))
 
+    def rows_path(self, on: bool) -> bool:
+        """Steps of up to 16 rows run their products on the streaming kernel (one kernel per
+        product, chunk sums added inside it; the default) or on the tcgen05 kernel like larger
+        steps; same bits either way.  Returns the previous setting."""
+        if self.kind != "bf16":
+            return False
+        self._kernel_counts.clear()
+        return bool(self.lib.bw_bf16_linear_rows_enable(_c_int(int(on))))
+
     def device_failure(self) -> bool:
         """True (once) when a kernel gave up a bounded wait since the last call.  This reads a
         word from the device, so callers ask now and then, not every step."""
         if self.kind != "bf16":
             return False
         bad = bool(self.lib.bw_bf16_linear_tc_failed())
+        bad = bool(self.lib.bw_bf16_linear_rows_failed()) or bad
         for lib in self._attn_libs.values():
             bad = bool(lib.bw_bf16_attention_tc_failed()) or bad
         return bad

@@ -335,6 +335,65 @@ def test_bf16_linear_two_blocks_per_tile_give_the_same_bits():
     assert not ops.device_failure()
 
 
+def test_bf16_linear_few_rows_kernel_gives_the_same_bits():
+    """Steps of up to 16 rows run their products on the streaming kernel (a warp per 8 columns
+    and chunk, chunk sums added inside the kernel, clusters of blocks when k is long). Same bits
+    as the tcgen05 kernel, for every output kind: bfloat16, float32 with residual, float32
+    without. Sizes: one chunk, a partial chunk, 4 / 8 / 16 / 28 chunks (clusters of 1, 2, 4, 8),
+    columns that are no multiple of 8 or 16, 1 .. 16 rows."""
+    rng = np.random.default_rng(21)
+    ops = _ops("bfloat16")
+    for m, n, k in ((1, 64, 64), (8, 2048, 2048), (3, 100, 200), (5, 1000, 520), (8, 2048, 8192), (2, 77, 4104),
+                    (9, 6144, 2048), (16, 136, 4096), (13, 1001, 8192), (8, 512, 14336), (16, 264, 14336),
+                    (7, 49152 // 8, 2048)):
+        x, w = bf(rnd(rng, m, k)), bf(rnd(rng, n, k, scale=0.05))
+        res = rnd(rng, m, n)
+        outs = {}
+        for on in (True, False):
+            before = ops.rows_path(on)
+            try:
+                a = t(res).clone()
+                ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), a, residual=a)
+                b = torch.empty(m, n, device=DEV)
+                ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), b)
+                c = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+                ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), c)
+                outs[on] = (a.cpu().numpy(), b.cpu().numpy(), c.view(torch.int16).cpu().numpy())
+            finally:
+                ops.rows_path(before)
+        for got, want, what in zip(outs[True], outs[False], ("residual", "float32", "bfloat16")):
+            assert_same_bits(got, want, f"{what} [{m}x{k}] x [{n}x{k}]")
+        exact = res + x.astype(np.float64) @ w.astype(np.float64).T
+        assert np.abs(outs[True][0] - exact).max() <= 1e-4 * np.abs(exact).max()
+    assert not ops.device_failure()
+
+
+def test_bf16_linear_swiglu_fused_equals_product_then_swiglu():
+    """The gate/up product with SwiGLU in the same kernel (interleaved weights) gives the bits
+    of the plain product followed by the SwiGLU kernel, on every path: few rows (streaming
+    kernel), a small batch (tcgen05, whole or split) and a large one."""
+    rng = np.random.default_rng(22)
+    ops = _ops("bfloat16")
+    for m, inter, k in ((1, 128, 64), (8, 8192, 2048), (5, 192, 520), (16, 2560, 960), (12, 256, 4104),
+                        (40, 1024, 2048), (300, 512, 1032)):
+        x = bf(rnd(rng, m, k))
+        gate, up = bf(rnd(rng, inter, k, scale=0.05)), bf(rnd(rng, inter, k, scale=0.05))
+        gu = torch.empty(m, 2 * inter, device=DEV, dtype=torch.bfloat16)
+        ops.linear(t(x, torch.bfloat16), t(np.concatenate([gate, up]), torch.bfloat16), gu)
+        want = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+        ops.swiglu(gu, want)
+        wi = ops.interleave_gate_up(t(gate, torch.bfloat16), t(up, torch.bfloat16))
+        for on in (True, False):
+            before = ops.rows_path(on)
+            try:
+                got = torch.empty(m, inter, device=DEV, dtype=torch.bfloat16)
+                ops.linear_swiglu(t(x, torch.bfloat16), wi, got)
+            finally:
+                ops.rows_path(before)
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"rows path {on} [{m}x{k}] x [{2 * inter}x{k}]"
+    assert not ops.device_failure()
+
+
 def test_bf16_rmsnorm_and_swiglu():
     """Tolerance: one bfloat16 rounding of a float32 result (2^-8 relative) plus 1e-6 absolute."""
     rng = np.random.default_rng(9)
