@@ -9,15 +9,15 @@
 // before (the accumulator dependency), 3.2 us per chunk however narrow the tile, and the
 // chunk sums of a product that is split over the machine pass through scratch memory and a
 // second kernel. Here a block per SM stays for the whole product and walks output tiles of 8
-// or 16 columns. Its four warps share the chunks of a tile (warp w takes chunks w, w + 4, ...);
+// or 16 columns. Four warps share the chunks of 8 columns (warp w takes chunks w, w + 4, ...);
 // a work item is (tile, chunk): 8 KB of W per 8 columns, fetched by ONE TMA copy (a box of
 // 8 rows x 8 k-tiles of 64, 128-byte swizzle) into the warp's own ring of buffers, two items
 // ahead of the arithmetic (the first ones before the wait for the kernel before this one:
 // weights do not depend on it). The step's rows of x are loaded once per block and stay in
 // shared memory. An item's 32 k-steps run on mma.sync (m16n8k16: a dependent step every 28
-// cycles, measured; two independent chains per warp when a tile has 16 columns). The chunk
-// sums of a tile meet in shared memory, are added in ascending order and leave as finished
-// outputs. No scratch, no second kernel.
+// cycles, measured; a tile of 16 columns has a second set of four warps for its second half,
+// so that every warp runs one chain). The chunk sums of a tile meet in shared memory, are
+// added in ascending order and leave as finished outputs. No scratch, no second kernel.
 //
 // Same bits as every other variant of the product (tested against them): inside a chunk the
 // tensor core accumulates from zero in k-steps of 16, ascending; chunk sums are added in
@@ -33,7 +33,7 @@ constexpr int kChunk = 512;            // canonical summation chunk along k (as 
 constexpr int kTileK = 64;             // k-elements of a shared-memory line (128 bytes, swizzled)
 constexpr int kTilesPerChunk = kChunk / kTileK;
 constexpr int kGroupBytes = 8 * kChunk * 2;  // 8 rows x one chunk: [k-tile][row][128 bytes]
-constexpr int kWarps = 4;              // warps of a block; chunk c of a tile belongs to warp c % kWarps
+constexpr int kWarps = 4;              // warps per group of 8 columns; chunk c belongs to warp c % kWarps of the group
 constexpr int kStages = 2;             // buffers in a warp's ring of W items
 constexpr int kSmemLimit = 227 * 1024;
 constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
@@ -105,59 +105,57 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 // y[m][n / 2] = SwiGLU (bfloat16); a tile is 8 outputs (8 gate rows and their 8 up rows, NT 2).
 // EPI 2: y = (residual +) product in float32.
 // ROWS16: up to 16 rows (else up to 8: the upper half of the tensor core's 16 rows is zero).
-// NT: groups of 8 output columns per tile (1 or 2), each a chain of its own in every warp.
+// NT: groups of 8 output columns per tile (1 or 2), each with kWarps warps of its own.
 //
 // Shared memory (1024-byte aligned for the swizzle): the rows of x [chunk][k-tile][R][128 B],
-// the rings [warp][stage][NT][k-tile][8][128 B], the barriers, and the chunk sums of two
-// tiles in turn [2][chunk][NT][R][8].
+// the rings [warp][stage][k-tile][8][128 B], the barriers, and the chunk sums of two tiles in
+// turn [2][chunk][NT][R][8].
 template <int EPI, bool ROWS16, int NT>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(NT * kWarps * 32)
 linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
                    const float* residual, int M, int N, int K, int tiles) {
   constexpr int R = ROWS16 ? 16 : 8;
-  constexpr int kItemBytes = NT * kGroupBytes;
+  constexpr int kItemBytes = kGroupBytes;  // what a warp fetches per (tile, chunk): its group's 8 rows
+  constexpr int kThreads = NT * kWarps * 32;
   constexpr int kXChunkBytes = R * kChunk * 2;
   constexpr int kOutputs = R * NT * 8;                                // outputs of a tile, chunk sums of one chunk
-  constexpr int kMine = (kOutputs + kWarps * 32 - 1) / (kWarps * 32);  // outputs per thread in the epilogue
+  constexpr int kMine = (kOutputs + kThreads - 1) / kThreads;         // outputs per thread in the epilogue
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp_all = tid >> 5;
+  const int grp = warp_all / kWarps, warp = warp_all % kWarps;  // group of 8 columns; which chunks of it
   const int num_chunks = (K + kChunk - 1) / kChunk;
   unsigned char* xs = smem;
-  unsigned char* ring = xs + num_chunks * kXChunkBytes + warp * (kStages * kItemBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xs + num_chunks * kXChunkBytes + kWarps * kStages * kItemBytes);
-  uint64_t* wbar = bars + warp * kStages;           // one barrier per buffer of this warp's ring
-  uint64_t* xbar = bars + kWarps * kStages + warp;  // this warp's chunks of x
-  float* part = reinterpret_cast<float*>(bars + kWarps * (kStages + 1));
+  unsigned char* ring = xs + num_chunks * kXChunkBytes + warp_all * (kStages * kItemBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xs + num_chunks * kXChunkBytes + NT * kWarps * kStages * kItemBytes);
+  uint64_t* wbar = bars + warp_all * kStages;            // one barrier per buffer of this warp's ring
+  uint64_t* xbar = bars + NT * kWarps * kStages + warp;  // the chunks of x that this warp works on
+  float* part = reinterpret_cast<float*>(bars + NT * kWarps * kStages + kWarps);
 #ifdef BW_ROWS_TRACE
   int tr = 0;
 #endif
 
   if (tid == 0) {
-    for (int i = 0; i < kWarps * (kStages + 1); ++i) mbar_init(bars + i, 1);
+    for (int i = 0; i < NT * kWarps * kStages + kWarps; ++i) mbar_init(bars + i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
   // This warp's items: for tile = blockIdx.x, + gridDim.x, ...: chunks warp, warp + kWarps, ...
   const int my_chunks = warp < num_chunks ? (num_chunks - warp + kWarps - 1) / kWarps : 0;
-  // Requests item (tile, chunk) into buffer `stage`: one box per group of 8 rows of W (with
-  // interleaved gate/up weights the up rows of 8 outputs lie 64 rows after their gate rows).
+  // Requests item (tile, chunk) into buffer `stage`: one box of this warp's group of 8 rows of W
+  // (with interleaved gate/up weights the up rows of 8 outputs lie 64 rows after their gate rows).
   auto request = [&](int tile, int chunk, int stage) {
     if (lane == 0) {
-      unsigned char* buf = ring + stage * kItemBytes;
-      mbar_expect_tx(wbar + stage, kItemBytes);
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        int row;
-        if (EPI == 1) {
-          const int c0 = tile * 8;
-          row = 128 * (c0 >> 6) + (c0 & 63) + 64 * t;
-        } else {
-          row = (tile * NT + t) * 8;
-        }
-        tma_load_box(buf + t * kGroupBytes, &map_w, row, chunk * kTilesPerChunk, wbar + stage);
+      int row;
+      if (EPI == 1) {
+        const int c0 = tile * 8;
+        row = 128 * (c0 >> 6) + (c0 & 63) + 64 * grp;
+      } else {
+        row = (tile * NT + grp) * 8;
       }
+      mbar_expect_tx(wbar + stage, kItemBytes);
+      tma_load_box(ring + stage * kItemBytes, &map_w, row, chunk * kTilesPerChunk, wbar + stage);
     }
   };
 
@@ -171,9 +169,10 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   }
   bw::pdl_launch();
   bw::pdl_wait();
-  // x, once per block: every warp brings the chunks it works on (rows beyond the step's arrive as zeros)
+  // x, once per block: the warps of the first group bring the chunks they work on, which are
+  // those of their namesakes in the other group too (rows beyond the step's arrive as zeros)
   if (my_chunks > 0) {
-    if (lane == 0) {
+    if (lane == 0 && grp == 0) {
       mbar_expect_tx(xbar, static_cast<uint32_t>(my_chunks * kXChunkBytes));
       for (int cc = 0; cc < my_chunks; ++cc) {
         const int chunk = warp + cc * kWarps;
@@ -204,7 +203,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     for (int e = 0; e < kMine; ++e) {
       res[e] = 0.0f;
       if (EPI == 2 && residual) {
-        const int o = tid + e * kWarps * 32;
+        const int o = tid + e * kThreads;
         const int r = o / (NT * 8), n = tile * (NT * 8) + o % (NT * 8);
         if (o < kOutputs && r < M && n < N) res[e] = residual[static_cast<size_t>(r) * N + n];
       }
@@ -220,12 +219,10 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       TR();
       const int k_here = min(kChunk, K - chunk * kChunk);
       const int pairs = (k_here / kTileK) * 2;  // pairs of k-steps of 16 (k is a multiple of 64)
-      float d[NT][4];
-#pragma unroll
-      for (int t = 0; t < NT; ++t) d[t][0] = d[t][1] = d[t][2] = d[t][3] = 0.0f;
+      float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       // fragments of pair p: k-tile p / 2, k-blocks 4 (p % 2) .. + 3 of it; those of the next
       // pair are fetched before this pair's MMAs are issued
-      uint32_t a[2][ROWS16 ? 8 : 4], b[2][NT][4];
+      uint32_t a[2][ROWS16 ? 8 : 4], b[2][4];
       auto fetch = [&](int p, int slot) {
         const int kt = p >> 1, q0 = (p & 1) * 4;
         if (ROWS16) {
@@ -240,20 +237,15 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 #pragma unroll
           for (int e = 0; e < 4; ++e) a[slot][e] = v[e];
         }
-#pragma unroll
-        for (int t = 0; t < NT; ++t)
-          ldmatrix_x4(b[slot][t], wb + t * kGroupBytes + kt * 1024 + (((q0 + lblk) ^ lrow) << 4));
+        ldmatrix_x4(b[slot], wb + kt * 1024 + (((q0 + lblk) ^ lrow) << 4));
       };
       auto steps = [&](int slot) {
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (ROWS16) {
-            mma_bf16(d[t], a[slot][0], a[slot][1], a[slot][2], a[slot][3], b[slot][t][0], b[slot][t][1]);
-            mma_bf16(d[t], a[slot][4], a[slot][5], a[slot][6], a[slot][7], b[slot][t][2], b[slot][t][3]);
-          } else {
-            mma_bf16(d[t], a[slot][0], 0u, a[slot][1], 0u, b[slot][t][0], b[slot][t][1]);
-            mma_bf16(d[t], a[slot][2], 0u, a[slot][3], 0u, b[slot][t][2], b[slot][t][3]);
-          }
+        if (ROWS16) {
+          mma_bf16(d, a[slot][0], a[slot][1], a[slot][2], a[slot][3], b[slot][0], b[slot][1]);
+          mma_bf16(d, a[slot][4], a[slot][5], a[slot][6], a[slot][7], b[slot][2], b[slot][3]);
+        } else {
+          mma_bf16(d, a[slot][0], 0u, a[slot][1], 0u, b[slot][0], b[slot][1]);
+          mma_bf16(d, a[slot][2], 0u, a[slot][3], 0u, b[slot][2], b[slot][3]);
         }
       };
       fetch(0, 0);
@@ -271,13 +263,12 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         request(req_tile, warp + req_cc * kWarps, stage);
         if (++req_cc == my_chunks) req_cc = 0, req_tile += gridDim.x;
       }
-      // chunk sums: d[t][0..1] are columns 2 (lane % 4) + {0, 1} of row lane / 4 of group t,
-      // d[t][2..3] of row lane / 4 + 8
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        float* mine = sums + chunk * kOutputs + t * (R * 8) + (lane >> 2) * 8 + 2 * (lane & 3);
-        *reinterpret_cast<float2*>(mine) = make_float2(d[t][0], d[t][1]);
-        if (ROWS16) *reinterpret_cast<float2*>(mine + 64) = make_float2(d[t][2], d[t][3]);
+      // chunk sums: d[0..1] are columns 2 (lane % 4) + {0, 1} of row lane / 4 of this group,
+      // d[2..3] of row lane / 4 + 8
+      {
+        float* mine = sums + chunk * kOutputs + grp * (R * 8) + (lane >> 2) * 8 + 2 * (lane & 3);
+        *reinterpret_cast<float2*>(mine) = make_float2(d[0], d[1]);
+        if (ROWS16) *reinterpret_cast<float2*>(mine + 64) = make_float2(d[2], d[3]);
       }
     }
     TR();
@@ -293,7 +284,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     };
     if (EPI == 1) {
       const int inter = N / 2;
-      for (int o = tid; o < R * 8; o += kWarps * 32) {
+      for (int o = tid; o < R * 8; o += kThreads) {
         const int r = o >> 3, j = o & 7;
         if (r >= M) continue;
         const float g = __bfloat162float(__float2bfloat16_rn(chunk_sum(0, r, j)));
@@ -304,7 +295,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     } else {
 #pragma unroll
       for (int e = 0; e < kMine; ++e) {
-        const int o = tid + e * kWarps * 32;
+        const int o = tid + e * kThreads;
         const int r = o / (NT * 8), cj = o % (NT * 8);
         const int n = tile * (NT * 8) + cj;
         if (o >= kOutputs || r >= M || n >= N) continue;
@@ -381,7 +372,7 @@ bool rows_shape(int m, int n, int k, bool swiglu, RowsShape* s) {
   for (int nt = 2; nt >= 1; --nt) {
     if (swiglu && nt != 2) break;
     const long long smem = 1024 + chunks * R * kChunk * 2 + static_cast<long long>(kWarps) * kStages * nt * kGroupBytes +
-                           kWarps * (kStages + 1) * 8 + 2 * chunks * nt * R * 8 * 4;
+                           (nt * kWarps * kStages + kWarps) * 8 + 2 * chunks * nt * R * 8 * 4;
     if (smem > kSmemLimit) continue;
     const long long tiles = swiglu ? n / 16 : (n + nt * 8 - 1) / (nt * 8);
     if (tiles > 0x7fffffffLL) return false;
@@ -413,7 +404,7 @@ int launch_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const f
     bw::set_error("linear (few rows): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
     return -1;
   }
-  bw::launch_pdl(kernel, dim3(s.grid), dim3(kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles);
+  bw::launch_pdl(kernel, dim3(s.grid), dim3(NT * kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles);
   return bw::launch_status();
 }
 
