@@ -18,6 +18,8 @@
 // its position and the cached keys: tiles that lie wholly outside a row's range merge as an
 // exact no-op, so the result does not depend on which other rows share the block, on how the
 // prompt was cut, on the batch, or on which pages hold the keys.
+#include <cuda.h>
+
 #include "bw_common.cuh"
 
 #ifndef BW_HEAD_DIM
@@ -119,6 +121,8 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
   for (int i = 0; i < kTileKV / 8; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) s[i][e] = 0.0f;
+  // The fragments of a k-step are all fetched before its MMAs are issued (the statements keep
+  // their order in the machine code): the loads' latencies overlap instead of adding up.
 #pragma unroll
   for (int kk = 0; kk < HD / 16; ++kk) {
     uint32_t a[4];
@@ -126,13 +130,16 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
       const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
       ldmatrix_x4(a, smem_u32(sq + piece_offset(row, kk * 2 + (lane >> 4))));
     }
+    uint32_t b[kTileKV / 16][4];
 #pragma unroll
     for (int np = 0; np < kTileKV / 16; ++np) {
-      uint32_t b[4];
       const int key = np * 16 + (lane & 7) + (lane >> 4) * 8;
-      ldmatrix_x4(b, smem_u32(sk + piece_offset(key, kk * 2 + ((lane >> 3) & 1))));
-      mma_bf16(s[2 * np], a, b[0], b[1]);
-      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+      ldmatrix_x4(b[np], smem_u32(sk + piece_offset(key, kk * 2 + ((lane >> 3) & 1))));
+    }
+#pragma unroll
+    for (int np = 0; np < kTileKV / 16; ++np) {
+      mma_bf16(s[2 * np], a, b[np][0], b[np][1]);
+      mma_bf16(s[2 * np + 1], a, b[np][2], b[np][3]);
     }
   }
   // maximum of the raw scores (scaling by a positive factor commutes with the maximum), then
@@ -192,13 +199,24 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
     for (int e = 0; e < 4; ++e) r.o[i][e] = 0.0f;
 #pragma unroll
   for (int kp = 0; kp < kTileKV / 16; ++kp) {
+    // four value fragments at a time: fetched together, then their MMAs
 #pragma unroll
-    for (int dp = 0; dp < HD / 16; ++dp) {
-      uint32_t b[4];
-      const int key = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      ldmatrix_x4_trans(b, smem_u32(sv + piece_offset(key, dp * 2 + (lane >> 4))));
-      mma_bf16(r.o[2 * dp], p[kp], b[0], b[1]);
-      mma_bf16(r.o[2 * dp + 1], p[kp], b[2], b[3]);
+    for (int d0 = 0; d0 < HD / 16; d0 += 4) {
+      uint32_t b[4][4];
+#pragma unroll
+      for (int dd = 0; dd < 4; ++dd) {
+        if (d0 + dd < HD / 16) {
+          const int key = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4_trans(b[dd], smem_u32(sv + piece_offset(key, (d0 + dd) * 2 + (lane >> 4))));
+        }
+      }
+#pragma unroll
+      for (int dd = 0; dd < 4; ++dd) {
+        if (d0 + dd < HD / 16) {
+          mma_bf16(r.o[2 * (d0 + dd)], p[kp], b[dd][0], b[dd][1]);
+          mma_bf16(r.o[2 * (d0 + dd) + 1], p[kp], b[dd][2], b[dd][3]);
+        }
+      }
     }
   }
   r.max_lo = tmax_lo;
@@ -401,6 +419,233 @@ attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, cons
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Split mode for head size 64, as a stream (decode steps, where the cache is all that is read).
+// One block per SM stays for the whole launch; each of its warps walks work items (row,
+// key/value head, key tile) and keeps a ring of three of them in shared memory. An item is
+// fetched by TMA: the page of a head is one box of 2 KB (a row of 64 values is a 128-byte line,
+// and the 128-byte swizzle of the copy is the layout that attend_tile reads), so a tile of keys
+// and values is eight copies instead of a thousand 16-byte ones, and the query row is one
+// more. Tiles that earlier steps stored are requested before the wait for the kernel before
+// this one. The arithmetic and the records are those of attention_split_kernel (same bits).
+#if BW_HEAD_DIM == 64
+constexpr int kStreamWarps = 6;
+constexpr int kStreamStages = 2;
+constexpr int kStreamMaxRows = 512;  // rows of a step whose positions fit into shared memory beside the rings
+constexpr int kStreamQBytes = 16 * 128;                       // 16 stacked rows; a step's row fills `group` of them
+constexpr int kStreamItemBytes = kStreamQBytes + 2 * kKVBytes;  // 18 KB, a multiple of 1024
+constexpr uint32_t kStreamSpinLimit = 20000000u;              // about a second of polling
+
+__device__ int g_stream_failed = 0;  // raised when a bounded wait ran out
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// raises the bytes that the barrier's current phase expects, without arriving
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kStreamSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return;
+  }
+  g_stream_failed = 1;  // the outputs of this launch are worthless; the host learns of it
+}
+__device__ __forceinline__ void tma_box_4d(void* dst, const CUtensorMap* map, int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(0), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// map_q: [row][kv head][head of the group][64], box = the group's heads of one row and kv head.
+// map_k / map_v: [page][kv head][slot][64], box = one page of one kv head.
+//
+// Work items are the (row, key tile) pairs that hold a key of the row's range, in row order,
+// times the key/value heads, heads fastest (neighbouring items read neighbouring heads of the
+// same pages). Warp w of block b takes items b * kStreamWarps + w, + gridDim.x * kStreamWarps, ...
+// Positions, the rows' sequences and the running count of tiles per row are put into shared
+// memory once, so that finding an item costs no trip to global memory; the page numbers of
+// an item are fetched one item before they are needed.
+__global__ void __launch_bounds__(kStreamWarps * 32)
+attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ row_seq, const int* __restrict__ pos, int n, int heads, int kv_heads,
+                        int page, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = heads / kv_heads;
+  unsigned char* ring = smem + warp * (kStreamStages * kStreamItemBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStreamWarps * kStreamStages * kStreamItemBytes) + warp * kStreamStages;
+  int* s_cum = reinterpret_cast<int*>(smem + kStreamWarps * kStreamStages * (kStreamItemBytes + 8));  // [n + 1] tiles before row r
+  int* s_pos = s_cum + n + 1;
+  int* s_seq = s_pos + n;
+  const int pages_per_tile = kTileKV / page;
+  const int stride = static_cast<int>(gridDim.x) * kStreamWarps;
+
+  // rows of the query tiles beyond the group stay zero for the whole launch
+  for (int s = 0; s < kStreamStages; ++s)
+    for (int b = lane * 16; b < kStreamQBytes; b += 32 * 16)
+      *reinterpret_cast<uint4*>(ring + s * kStreamItemBytes + b) = make_uint4(0u, 0u, 0u, 0u);
+  if (lane == 0) {
+    for (int s = 0; s < kStreamStages; ++s) mbar_init(bars + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // the zeros above were written through the generic proxy; the copies go through the async one
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  auto first_key = [&](int p) { return (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0; };
+  // positions and sequences were copied to the device before the step's first kernel
+  for (int r = tid; r < n; r += kStreamWarps * 32) {
+    const int p = pos[r];
+    s_pos[r] = p;
+    s_seq[r] = row_seq[r];
+    s_cum[r + 1] = p / kTileKV - first_key(p) / kTileKV + 1;  // tiles of row r, summed up below
+  }
+  __syncthreads();
+  if (warp == 0) {  // running sum over the rows, 32 at a time
+    int base = 0;
+    for (int r0 = 0; r0 < n; r0 += 32) {
+      int v = r0 + lane < n ? s_cum[r0 + lane + 1] : 0;
+      for (int d = 1; d < 32; d <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += u;
+      }
+      if (r0 + lane < n) s_cum[r0 + lane + 1] = base + v;
+      base += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) s_cum[0] = 0;
+  }
+  __syncthreads();
+  const int total = s_cum[n] * kv_heads;
+
+  struct Item {
+    int row, g, t, p;
+  };
+  // item `id` (< total); `row` is a cursor that only moves forward
+  auto find_item = [&](int id, int& row, Item& it) {
+    const int j = id / kv_heads;
+    it.g = id - j * kv_heads;
+    while (j >= s_cum[row + 1]) ++row;
+    it.row = row;
+    it.p = s_pos[row];
+    it.t = first_key(it.p) / kTileKV + (j - s_cum[row]);
+  };
+  // the page of the item's tile that lane `lane` (< pages_per_tile) looks up
+  auto lookup_page = [&](const Item& it) {
+    // pages wholly beyond the last key are not in the table: any valid page will do, its keys are masked
+    const int blk = min((it.t * kTileKV) / page + lane, it.p / page);
+    return block_table[static_cast<size_t>(s_seq[it.row]) * max_blocks + blk];
+  };
+  // requests keys and values of an item, given the pages that lanes 0 .. pages_per_tile - 1 hold
+  auto request_kv = [&](const Item& it, int my_page, unsigned char* buf, uint64_t* bar) {
+    for (int pg = 0; pg < pages_per_tile; ++pg) {
+      const int blk = __shfl_sync(0xffffffffu, my_page, pg);
+      if (lane == 0) {
+        tma_box_4d(buf + kStreamQBytes + pg * page * 128, &map_k, it.g, blk, bar);
+        tma_box_4d(buf + kStreamQBytes + kKVBytes + pg * page * 128, &map_v, it.g, blk, bar);
+      }
+    }
+  };
+  const uint32_t q_bytes = static_cast<uint32_t>(group) * 128, kv_bytes = 2 * kKVBytes;
+
+  // The ring's first items. Keys and values that earlier steps stored do not depend on the
+  // kernel before this one (which rotates q and stores this step's key and value).
+  int req_id = static_cast<int>(blockIdx.x) * kStreamWarps + warp, req_row = 0;
+  Item first_items[kStreamStages];
+  int first_pages[kStreamStages];
+  bool early[kStreamStages];
+  int primed = 0;
+  for (; primed < kStreamStages && req_id < total; ++primed, req_id += stride) {
+    Item& it = first_items[primed];
+    find_item(req_id, req_row, it);
+    first_pages[primed] = lane < pages_per_tile ? lookup_page(it) : 0;
+    early[primed] = (it.t + 1) * kTileKV <= it.p;
+    if (early[primed]) {
+      if (lane == 0) mbar_expect_tx(bars + primed, kv_bytes);
+      __syncwarp();
+      request_kv(it, first_pages[primed], ring + primed * kStreamItemBytes, bars + primed);
+    }
+  }
+  bw::pdl_launch();
+  bw::pdl_wait();
+  for (int s = 0; s < primed; ++s) {
+    const Item& it = first_items[s];
+    unsigned char* buf = ring + s * kStreamItemBytes;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bars + s, early[s] ? q_bytes : q_bytes + kv_bytes);
+      tma_box_4d(buf, &map_q, it.g, it.row, bars + s);
+    }
+    __syncwarp();
+    if (!early[s]) request_kv(it, first_pages[s], buf, bars + s);
+  }
+  // the item that the next request will bring, and its pages
+  Item nx;
+  int nx_page = 0;
+  bool nx_ok = req_id < total;
+  if (nx_ok) {
+    find_item(req_id, req_row, nx);
+    nx_page = lane < pages_per_tile ? lookup_page(nx) : 0;
+  }
+
+  int use_row = 0;
+  uint32_t used = 0;
+  for (int use_id = static_cast<int>(blockIdx.x) * kStreamWarps + warp; use_id < total; use_id += stride, ++used) {
+    Item it;
+    find_item(use_id, use_row, it);
+    const int first = first_key(it.p);
+    const int stage = used % kStreamStages;
+    unsigned char* buf = ring + stage * kStreamItemBytes;
+    mbar_wait_bounded(bars + stage, (used / kStreamStages) & 1);
+    TileResult r;
+    attend_tile(buf, buf + kStreamQBytes, buf + kStreamQBytes + kKVBytes, lane, it.t * kTileKV, it.p, it.p, first, first,
+                scale_log2, r);
+    // the buffer is free (every ldmatrix of the item has delivered): the next item of the ring
+    // takes it; the pages of the one after are looked up now and used a whole item later
+    __syncwarp();
+    if (nx_ok) {
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bars + stage, q_bytes + kv_bytes);
+        tma_box_4d(buf, &map_q, nx.g, nx.row, bars + stage);
+      }
+      __syncwarp();
+      request_kv(nx, nx_page, buf, bars + stage);
+      req_id += stride;
+      nx_ok = req_id < total;
+      if (nx_ok) {
+        find_item(req_id, req_row, nx);
+        nx_page = lane < pages_per_tile ? lookup_page(nx) : 0;
+      }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = (lane >> 2) + half * 8;
+      if (m >= group) continue;
+      float* dst = tile_out + ((static_cast<size_t>(it.row) * heads + (it.g * group + m)) * max_tiles + it.t) * (HD + 2);
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * (lane & 3)) = make_float2(r.o[i][half * 2], r.o[i][half * 2 + 1]);
+      if ((lane & 3) == 0) {
+        dst[HD] = half ? r.max_hi : r.max_lo;
+        dst[HD + 1] = half ? r.sum_hi : r.sum_lo;
+      }
+    }
+  }
+}
+#endif  // BW_HEAD_DIM == 64
+
 // Second half of split mode: per (row, head) the tile results are merged in ascending tile
 // order with the same formula as in whole mode; thread d carries output element d. The records
 // of up to kMergeBatch tiles are brought into shared memory by all threads together (one
@@ -510,3 +755,136 @@ BW_API int bw_bf16_attention(const __nv_bfloat16* qkv, int q_stride, const __nv_
   }
   return bw::launch_status();
 }
+
+#if BW_HEAD_DIM == 64
+namespace {
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled stream_encoder() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+bool stream_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
+                const cuuint32_t (&box)[4]) {
+  EncodeTiled enc = stream_encoder();
+  if (!enc) return false;
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+int g_stream_mode = 1;  // 0 never, 1 for steps of many rows, 2 whenever the shape allows
+constexpr int kStreamMinRows = 32;
+}  // namespace
+
+// When the streaming decode kernel runs: 0 never, 1 (the default) for steps of 32 rows or more
+// (measured on B200: with fewer rows its set-up per block costs more than its steadier stream
+// of loads gains), 2 whenever the shape allows. Returns the previous setting. Tests compare it
+// with attention_split_kernel bit for bit.
+BW_API int bw_bf16_attention_stream_mode(int mode) {
+  const int before = g_stream_mode;
+  if (mode >= 0 && mode <= 2) g_stream_mode = mode;
+  return before;
+}
+
+// Whether decode steps of this shape can take the streaming kernel: head size 64, pages of 8
+// keys or more that divide a tile of 64, a group of at most 16 heads, rows that start on 16
+// bytes, and a step of at most 512 rows.
+BW_API int bw_bf16_attention_stream_usable(int n, int heads, int kv_heads, int hd, int page, int q_stride) {
+  if (!g_stream_mode || (g_stream_mode == 1 && n < kStreamMinRows) || hd != HD || kv_heads <= 0 || heads % kv_heads ||
+      n > kStreamMaxRows)
+    return 0;
+  const int group = heads / kv_heads;
+  return group <= 16 && page >= 8 && kTileKV % page == 0 && q_stride % 8 == 0 && stream_encoder() != nullptr;
+}
+
+BW_API int bw_bf16_attention_stream_failed() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_stream_failed, sizeof(int)) != cudaSuccess) return 0;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_stream_failed, &zero, sizeof(int));
+  }
+  return v;
+}
+
+// A decode step (one query row per sequence): tile results by the streaming kernel, then the
+// ordered merge. `scratch` as for bw_bf16_attention (bw_bf16_attention_scratch_floats).
+BW_API int bw_bf16_attention_stream(const __nv_bfloat16* qkv, int q_stride, const __nv_bfloat16* kcache,
+                                    const __nv_bfloat16* vcache, int num_pages, const int* block_table, int max_blocks,
+                                    const int* row_seq, const int* pos, __nv_bfloat16* out, int out_stride, int n,
+                                    int heads, int kv_heads, int hd, int page, int window, float scale, int max_keys,
+                                    float* scratch, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!bw_bf16_attention_stream_usable(n, heads, kv_heads, hd, page, q_stride) || !scratch || out_stride % 2) {
+    bw::set_error("attention (stream): unsupported shape (heads %d/%d, head size %d, page %d)", heads, kv_heads, hd, page);
+    return -1;
+  }
+  const int key_tiles = (max_keys + kTileKV - 1) / kTileKV;
+  const long long items = static_cast<long long>(n) * kv_heads * key_tiles;
+  if (items > 0x3fffffffLL || heads > 65535 || n > kStreamMaxRows) {
+    bw::set_error("attention (stream): %lld work items exceed the limit", items);
+    return -1;
+  }
+  const int group = heads / kv_heads;
+  const int smem = kStreamWarps * kStreamStages * (kStreamItemBytes + 8) + (3 * n + 1) * 4 + 1024;
+  constexpr int smem_max = kStreamWarps * kStreamStages * (kStreamItemBytes + 8) + (3 * kStreamMaxRows + 1) * 4 + 1024;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    if (e != cudaSuccess) {
+      bw::set_error("attention (stream): cannot raise shared memory to %d: %s", smem_max, cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    configured = true;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  {  // queries: [row][kv head][head of the group][d], box = the group's heads of one row
+    const cuuint64_t dims[4] = {HD, static_cast<cuuint64_t>(group), static_cast<cuuint64_t>(kv_heads),
+                                static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[3] = {HD * 2, static_cast<cuuint64_t>(group) * HD * 2, static_cast<cuuint64_t>(q_stride) * 2};
+    const cuuint32_t box[4] = {HD, static_cast<cuuint32_t>(group), 1, 1};
+    if (!stream_map(&map_q, qkv, dims, strides, box)) {
+      bw::set_error("attention (stream): cuTensorMapEncodeTiled refused the query map");
+      return -1;
+    }
+  }
+  {  // cache: [page][kv head][slot][d], box = one page of one kv head
+    const cuuint64_t dims[4] = {HD, static_cast<cuuint64_t>(page), static_cast<cuuint64_t>(kv_heads),
+                                static_cast<cuuint64_t>(num_pages)};
+    const cuuint64_t strides[3] = {HD * 2, static_cast<cuuint64_t>(page) * HD * 2,
+                                   static_cast<cuuint64_t>(kv_heads) * page * HD * 2};
+    const cuuint32_t box[4] = {HD, static_cast<cuuint32_t>(page), 1, 1};
+    if (!stream_map(&map_k, kcache, dims, strides, box) || !stream_map(&map_v, vcache, dims, strides, box)) {
+      bw::set_error("attention (stream): cuTensorMapEncodeTiled refused the cache map");
+      return -1;
+    }
+  }
+  const float scale_log2 = scale * 1.44269504088896341f;
+  const long long warps_needed = (items + 0) / 1;
+  const unsigned grid = static_cast<unsigned>(
+      warps_needed < static_cast<long long>(sms) * kStreamWarps ? (warps_needed + kStreamWarps - 1) / kStreamWarps : sms);
+  bw::launch_pdl(attention_stream_kernel, dim3(grid), dim3(kStreamWarps * 32), smem, stream, map_q, map_k, map_v,
+                 block_table, max_blocks, row_seq, pos, n, heads, kv_heads, page, window, scale_log2, scratch, key_tiles);
+  bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(kMergeThreads), 0, stream, scratch, key_tiles, pos, out,
+                 out_stride, heads, window);
+  return bw::launch_status();
+}
+#else
+BW_API int bw_bf16_attention_stream_mode(int) { return 0; }
+BW_API int bw_bf16_attention_stream_usable(int, int, int, int, int, int) { return 0; }
+BW_API int bw_bf16_attention_stream_failed() { return 0; }
+#endif

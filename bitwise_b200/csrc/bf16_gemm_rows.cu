@@ -88,19 +88,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-#ifdef BW_ROWS_TRACE
-#define TR()                                                              \
-  do {                                                                    \
-    if (blockIdx.x == 3 && lane == 0 && tr < 64) {                        \
-      unsigned long long t_;                                              \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));              \
-      g_trace[warp * 64 + tr++] = t_;                                     \
-    }                                                                     \
-  } while (0)
-#else
-#define TR()
-#endif
-
 // EPI 0: y = product in bfloat16.  EPI 1: W holds gate/up rows interleaved in blocks of 64 and
 // y[m][n / 2] = SwiGLU (bfloat16); a tile is 8 outputs (8 gate rows and their 8 up rows, NT 2).
 // EPI 2: y = (residual +) product in float32.
@@ -131,9 +118,6 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   uint64_t* wbar = bars + warp_all * kStages;            // one barrier per buffer of this warp's ring
   uint64_t* xbar = bars + NT * kWarps * kStages + warp;  // the chunks of x that this warp works on
   float* part = reinterpret_cast<float*>(bars + NT * kWarps * kStages + kWarps);
-#ifdef BW_ROWS_TRACE
-  int tr = 0;
-#endif
 
   if (tid == 0) {
     for (int i = 0; i < NT * kWarps * kStages + kWarps; ++i) mbar_init(bars + i, 1);
@@ -181,7 +165,6 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     }
     mbar_wait(xbar, 0);
   }
-  TR();
 
   // Shared-memory addresses of this lane's ldmatrix rows. A line of 128 bytes holds 64
   // k-elements of one row; its 16-byte pieces are swizzled with the row's low three bits.
@@ -214,9 +197,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       const int stage = used % kStages;
       const uint32_t wb = smem_u32(ring + stage * kItemBytes) + b_off;
       const uint32_t xa = smem_u32(xs + chunk * kXChunkBytes) + a_off;
-      TR();
       mbar_wait(wbar + stage, (used / kStages) & 1);
-      TR();
       const int k_here = min(kChunk, K - chunk * kChunk);
       const int pairs = (k_here / kTileK) * 2;  // pairs of k-steps of 16 (k is a multiple of 64)
       float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -255,7 +236,6 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         if (p + 2 < pairs) fetch(p + 2, 0);
         steps(1);
       }
-      TR();
       // The buffer is free: the item two ahead takes it. Every ldmatrix of this item has
       // delivered (the MMAs that consumed them were issued), so the copy may overwrite it.
       __syncwarp();
@@ -271,9 +251,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         if (ROWS16) *reinterpret_cast<float2*>(mine + 64) = make_float2(d[2], d[3]);
       }
     }
-    TR();
     __syncthreads();  // the chunk sums of this tile are complete (the next tile writes the other half)
-    TR();
 
     // the ordered sum of the chunk sums, then what follows the product
     auto chunk_sum = [&](int t, int r, int j) {

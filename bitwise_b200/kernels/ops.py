@@ -272,6 +272,15 @@ class KernelOps:
         self._kernel_counts.clear()
         return bool(self.lib.bw_bf16_linear_rows_enable(_c_int(int(on))))
 
+    def stream_attention(self, head_dim: int, mode: int) -> int:
+        """When decode steps with head size 64 read the cache through the streaming kernel
+        (persistent blocks, TMA rings) instead of the kernel that gives every key tile a thread
+        block of its own: 0 never, 1 for steps of 32 rows or more (the default), 2 whenever
+        the shape allows.  Same bits either way.  Returns the previous setting."""
+        if self.kind != "bf16":
+            return 0
+        return int(self._attention_lib(head_dim).bw_bf16_attention_stream_mode(_c_int(int(mode))))
+
     def device_failure(self) -> bool:
         """True (once) when a kernel gave up a bounded wait since the last call.  This reads a
         word from the device, so callers ask now and then, not every step."""
@@ -281,6 +290,7 @@ class KernelOps:
         bad = bool(self.lib.bw_bf16_linear_rows_failed()) or bad
         for lib in self._attn_libs.values():
             bad = bool(lib.bw_bf16_attention_tc_failed()) or bad
+            bad = bool(lib.bw_bf16_attention_stream_failed()) or bad
         return bad
 
     def attention_tile_rows(self, heads: int, kv_heads: int) -> int:
@@ -399,6 +409,20 @@ class KernelOps:
                     return
             if split:
                 scratch = self._attention_scratch(lib, qkv.device, n, heads, max_keys)
+                # head size 64: the cache streams through TMA rings, one block per SM (same bits)
+                if lib.bw_bf16_attention_stream_usable(_c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page),
+                                                       _c_int(qkv.shape[1])):
+                    fn = lib.bw_bf16_attention_stream
+                    fn.restype = _c_int
+                    rc = fn(_p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _c_int(kcache.shape[0]),
+                            _p(block_table), _c_int(block_table.shape[1]), _p(row_seq), _p(pos), _p(out),
+                            _c_int(out.shape[1]), _c_int(n), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+                            _c_int(page), _c_int(window), _c_float(scale), _c_int(max_keys), _p(scratch), self._stream())
+                    if rc != 0:
+                        raise KernelError(f"bw_bf16_attention_stream failed ({rc}): "
+                                          + lib.bw_last_error().decode("utf-8", "replace"))
+                    self.launches += 2
+                    return
             fn = lib.bw_bf16_attention
             fn.restype = _c_int
             rc = fn(_p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),

@@ -534,6 +534,32 @@ def test_bf16_attention_decode_rows_split_over_chunks_give_the_same_bits():
             assert_same_bits(got[s], alone[0], f"sequence {s} in a batch of three")
 
 
+def test_bf16_attention_streaming_decode_kernel_gives_the_same_bits():
+    """Head size 64: decode steps read the cache through a persistent kernel whose warps keep
+    rings of key tiles filled by TMA (a page of a head per copy). Same bits as the kernel that
+    gives every key tile a block of its own: groups of 1 .. 16 heads, pages of 8 .. 64 keys, a
+    window, sequences of very different lengths in one step (one shorter than a tile)."""
+    rng = np.random.default_rng(17)
+    ops = _ops("bfloat16")
+    hd = 64
+    for heads, kv_heads, page, window in ((4, 4, 16, 0), (8, 2, 16, 0), (3, 1, 8, 0), (4, 2, 64, 200), (16, 1, 32, 0),
+                                          (6, 3, 16, 0)):
+        lens = [700, 40, 1030, 129, 64]
+        k, v, table, _, _ = _paged(rng, lens, kv_heads, hd, page)
+        k, v = bf(k), bf(v)
+        q = bf(rnd(rng, len(lens), heads, hd))
+        rows = [(n - 1, 1) for n in lens]
+        outs = {}
+        for mode in (2, 0):
+            before = ops.stream_attention(hd, mode)
+            try:
+                outs[mode], _, _ = _run_bf16_attention(q, rows, k, v, table, heads, kv_heads, hd, window)
+            finally:
+                ops.stream_attention(hd, before)
+        assert_same_bits(outs[2], outs[0], f"heads {heads}/{kv_heads} page {page} window {window}")
+    assert not ops.device_failure()
+
+
 def test_bf16_attention_tensor_core_generations_agree_bit_for_bit():
     """The tcgen05 prefill kernel (head size 64) and the mma.sync kernels give the same bits:
     whole prompts, late portions, with a window, grouped heads, several sequences in a step."""
