@@ -91,16 +91,34 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 // EPI 0: y = product in bfloat16.  EPI 1: W holds gate/up rows interleaved in blocks of 64 and
 // y[m][n / 2] = SwiGLU (bfloat16); a tile is 8 outputs (8 gate rows and their 8 up rows, NT 2).
 // EPI 2: y = (residual +) product in float32.
+// EPI 3: W is the fused q/k/v projection; the tile's two groups are the two halves of a head
+// (columns i .. i + 7 and i + hd / 2 .. of it), so that a thread holds both partners of a
+// rotation: the outputs are rounded to bfloat16, q and k are rotated by their row's position,
+// q goes to y, k and v go straight into their page of the cache (what rope_cache_bf16_kernel
+// does to a stored product, with its arithmetic: same bits).
 // ROWS16: up to 16 rows (else up to 8: the upper half of the tensor core's 16 rows is zero).
 // NT: groups of 8 output columns per tile (1 or 2), each with kWarps warps of its own.
 //
 // Shared memory (1024-byte aligned for the swizzle): the rows of x [chunk][k-tile][R][128 B],
 // the rings [warp][stage][k-tile][8][128 B], the barriers, and the chunk sums of two tiles in
 // turn [2][chunk][NT][R][8].
+struct RopeCache {
+  const int* pos;            // position of every row
+  const int* row_seq;        // its sequence's row of the block table
+  const float* cos_t;        // [positions][hd / 2], or null: nothing is rotated
+  const float* sin_t;
+  const int* block_table;
+  int max_blocks;
+  __nv_bfloat16* kcache;     // [pages][kv_heads][page][hd]
+  __nv_bfloat16* vcache;
+  int heads, kv_heads, hd, page, write_kv;
+};
+
 template <int EPI, bool ROWS16, int NT>
 __global__ void __launch_bounds__(NT * kWarps * 32)
 linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
-                   const float* residual, int M, int N, int K, int tiles) {
+                   const float* residual, int M, int N, int K, int tiles, RopeCache rc) {
+  static_assert(EPI != 3 || NT == 2, "a rotation needs both halves of a head in the tile");
   constexpr int R = ROWS16 ? 16 : 8;
   constexpr int kItemBytes = kGroupBytes;  // what a warp fetches per (tile, chunk): its group's 8 rows
   constexpr int kThreads = NT * kWarps * 32;
@@ -135,6 +153,10 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       if (EPI == 1) {
         const int c0 = tile * 8;
         row = 128 * (c0 >> 6) + (c0 & 63) + 64 * grp;
+      } else if (EPI == 3) {
+        const int per_head = rc.hd >> 4;  // tiles per head
+        const int head = tile / per_head;
+        row = head * rc.hd + grp * (rc.hd >> 1) + (tile - head * per_head) * 8;
       } else {
         row = (tile * NT + grp) * 8;
       }
@@ -260,7 +282,36 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       for (int c = 1; c < num_chunks; ++c) v = v + p[c * kOutputs];
       return v;
     };
-    if (EPI == 1) {
+    if (EPI == 3) {
+      const int per_head = rc.hd >> 4, half = rc.hd >> 1;
+      const int head = tile / per_head, i0 = (tile - head * per_head) * 8;  // head among q, k, v heads
+      for (int o = tid; o < R * 8; o += kThreads) {
+        const int r = o >> 3, i = i0 + (o & 7);
+        if (r >= M) continue;
+        const float x1 = __bfloat162float(__float2bfloat16_rn(chunk_sum(0, r, o & 7)));
+        const float x2 = __bfloat162float(__float2bfloat16_rn(chunk_sum(1, r, o & 7)));
+        const int p = rc.pos[r];
+        float o1 = x1, o2 = x2;
+        if (rc.cos_t && head < rc.heads + rc.kv_heads) {
+          const float c = rc.cos_t[static_cast<size_t>(p) * half + i], sn = rc.sin_t[static_cast<size_t>(p) * half + i];
+          o1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+          o2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+        }
+        if (head < rc.heads) {
+          __nv_bfloat16* q = static_cast<__nv_bfloat16*>(Y) + static_cast<size_t>(r) * N + head * rc.hd + i;
+          q[0] = __float2bfloat16_rn(o1);
+          q[half] = __float2bfloat16_rn(o2);
+        } else if (rc.write_kv) {
+          const bool is_k = head < rc.heads + rc.kv_heads;
+          const int kvh = head - rc.heads - (is_k ? 0 : rc.kv_heads);
+          const int blk = rc.block_table[static_cast<size_t>(rc.row_seq[r]) * rc.max_blocks + p / rc.page];
+          __nv_bfloat16* dst = (is_k ? rc.kcache : rc.vcache) +
+                               ((static_cast<size_t>(blk) * rc.kv_heads + kvh) * rc.page + p % rc.page) * rc.hd + i;
+          dst[0] = __float2bfloat16_rn(o1);
+          dst[half] = __float2bfloat16_rn(o2);
+        }
+      }
+    } else if (EPI == 1) {
       const int inter = N / 2;
       for (int o = tid; o < R * 8; o += kThreads) {
         const int r = o >> 3, j = o & 7;
@@ -366,7 +417,7 @@ bool rows_shape(int m, int n, int k, bool swiglu, RowsShape* s) {
 
 template <int EPI, bool ROWS16, int NT>
 int launch_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const float* residual, int m, int n, int k,
-                const RowsShape& s, cudaStream_t stream) {
+                const RowsShape& s, cudaStream_t stream, const RopeCache& rc = RopeCache{}) {
   auto kernel = linear_rows_kernel<EPI, ROWS16, NT>;
   static bool configured = false;
   if (!configured) {
@@ -382,7 +433,7 @@ int launch_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const f
     bw::set_error("linear (few rows): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
     return -1;
   }
-  bw::launch_pdl(kernel, dim3(s.grid), dim3(NT * kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles);
+  bw::launch_pdl(kernel, dim3(s.grid), dim3(NT * kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles, rc);
   return bw::launch_status();
 }
 
@@ -439,4 +490,34 @@ BW_API int bw_bf16_linear_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, v
   if (y_kind == 1) return launch_rows_epi<1>(x, w, y, nullptr, m, n, k, s, stream);
   if (y_kind == 2) return launch_rows_epi<2>(x, w, y, residual, m, n, k, s, stream);
   return launch_rows_epi<0>(x, w, y, nullptr, m, n, k, s, stream);
+}
+
+// Whether the fused q/k/v projection of a step can rotate and store its outputs itself
+// (bw_bf16_linear_rows_rope): a shape of this path whose tiles hold both halves of a head.
+BW_API int bw_bf16_linear_rows_rope_usable(const void* x, const void* w, int m, int n, int k, int heads, int kv_heads,
+                                           int hd) {
+  RowsShape s;
+  return g_rows_enabled && hd >= 16 && hd % 16 == 0 && heads > 0 && kv_heads > 0 && n == (heads + 2 * kv_heads) * hd &&
+         (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
+         rows_shape(m, n, k, true, &s) && rows_encoder() != nullptr;
+}
+
+// qkv = x W^T for the fused q/k/v weights, then what bw_bf16_rope_cache does to it, in the same
+// kernel: q rotated into qkv[:, :heads * hd]; k rotated and v as it is into the pages
+// block_table[row_seq[r]][pos[r] / page] of the cache (not when write_kv is 0; the k and v
+// columns of qkv are not written). cos_t / sin_t null: nothing is rotated.
+BW_API int bw_bf16_linear_rows_rope(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* qkv, int m, int n, int k,
+                                    const int* pos, const int* row_seq, const float* cos_t, const float* sin_t,
+                                    const int* block_table, int max_blocks, __nv_bfloat16* kcache, __nv_bfloat16* vcache,
+                                    int heads, int kv_heads, int hd, int page, int write_kv, cudaStream_t stream) {
+  if (m <= 0 || n <= 0) return 0;
+  RowsShape s;
+  if (!bw_bf16_linear_rows_rope_usable(x, w, m, n, k, heads, kv_heads, hd) || !rows_shape(m, n, k, true, &s) || page <= 0) {
+    bw::set_error("linear with rotation (few rows): shape [%d x %d] x [%d x %d], %d/%d heads of %d is not for this path", m,
+                  k, n, k, heads, kv_heads, hd);
+    return -1;
+  }
+  const RopeCache rc{pos, row_seq, cos_t, sin_t, block_table, max_blocks, kcache, vcache, heads, kv_heads, hd, page, write_kv};
+  return s.rows16 ? launch_rows<3, true, 2>(x, w, qkv, nullptr, m, n, k, s, stream, rc)
+                  : launch_rows<3, false, 2>(x, w, qkv, nullptr, m, n, k, s, stream, rc);
 }

@@ -350,6 +350,53 @@ class KernelOps:
                    _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(kcache.shape[2]),
                    _c_int(int(write_kv)), self._stream())
 
+    def fuses_rope(self, m: int, width: int, heads: int, kv_heads: int, head_dim: int) -> bool:
+        """Whether ``linear_rope_cache`` takes a step of m rows: then the fused q/k/v product
+        rotates q and k and stores k and v in the cache itself (steps of up to 16 rows on the
+        serving precision)."""
+        if self.kind != "bf16":
+            return False
+        key = ("rope", m, width, heads, kv_heads, head_dim)
+        c = self._kernel_counts.get(key)
+        if c is None:
+            c = int(self.lib.bw_bf16_linear_rows_rope_usable(None, None, _c_int(m), _c_int((heads + 2 * kv_heads) * head_dim),
+                                                             _c_int(width), _c_int(heads), _c_int(kv_heads),
+                                                             _c_int(head_dim)))
+            self._kernel_counts[key] = c
+        return bool(c)
+
+    def linear_rope_cache(self, x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, pos: torch.Tensor,
+                          row_seq: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                          block_table: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, heads: int,
+                          kv_heads: int, head_dim: int, write_kv: bool = True) -> None:
+        """``linear(x, w_qkv, qkv)`` followed by ``rope_cache(qkv, ...)`` in one kernel: the
+        rotated q lands in qkv's first heads * head_dim columns, the rotated k and v in their
+        pages; the k and v columns of qkv are NOT written.  Same bits as the two calls.  Only
+        where ``fuses_rope`` says so."""
+        m, k = x.shape
+        n = w_qkv.shape[0]
+        _need(x, self.act_dtype, "linear_rope_cache x", 2)
+        _need(w_qkv, self.act_dtype, "linear_rope_cache w", 2)
+        _need(qkv, self.act_dtype, "linear_rope_cache qkv", 2)
+        _need(pos, torch.int32, "linear_rope_cache pos")
+        _need(row_seq, torch.int32, "linear_rope_cache row_seq")
+        _need(block_table, torch.int32, "linear_rope_cache block_table", 2)
+        _need(kcache, self.act_dtype, "linear_rope_cache kcache", 4)
+        _need(vcache, self.act_dtype, "linear_rope_cache vcache", 4)
+        if self.kind != "bf16" or w_qkv.shape[1] != k or tuple(qkv.shape) != (m, n) or n != (heads + 2 * kv_heads) * head_dim:
+            raise KernelError("linear_rope_cache: shapes do not fit the fused q/k/v projection")
+        if tuple(kcache.shape[1:]) != (kv_heads, kcache.shape[2], head_dim) or kcache.shape != vcache.shape:
+            raise KernelError("linear_rope_cache: cache shape is not [pages, kv_heads, page, head_dim]")
+        if cos is not None:
+            _need(cos, torch.float32, "linear_rope_cache cos", 2)
+            _need(sin, torch.float32, "linear_rope_cache sin", 2)
+            if cos.shape[1] != head_dim // 2 or cos.shape != sin.shape:
+                raise KernelError("linear_rope_cache: table width is not head_dim / 2")
+        self._call("bw_bf16_linear_rows_rope", _p(x), _p(w_qkv), _p(qkv), _c_int(m), _c_int(n), _c_int(k), _p(pos),
+                   _p(row_seq), _p(cos), _p(sin), _p(block_table), _c_int(block_table.shape[1]), _p(kcache), _p(vcache),
+                   _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(kcache.shape[2]), _c_int(int(write_kv)),
+                   self._stream())
+
     def attention(self, qkv: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                   block_table: torch.Tensor, row_seq: torch.Tensor, pos: torch.Tensor, out: torch.Tensor,
                   heads: int, kv_heads: int, head_dim: int, window: int, max_keys: int, scale: float,

@@ -71,11 +71,17 @@ class GQAAttention(Mixer):
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView, then_norm=None):
         ops, n = ctx.ops, ctx.n
         qkv = ctx.workspace.rows("qkv", n, self.q_dim + 2 * self.kv_dim, ctx.act_dtype)
-        ops.linear(xn, self.w_qkv, qkv)
         tables = self.position.rotary_tables(x.device) if self.position is not None else None
         cos, sin = tables if tables is not None else (None, None)
-        ops.rope_cache(qkv, ctx.pos, ctx.row_seq, cos, sin, cache.block_table, cache.k, cache.v,
-                       self.heads, self.kv_heads, self.head_dim, write_kv=cache.writable)
+        fuses = getattr(ops, "fuses_rope", None)
+        if fuses and fuses(n, self.width, self.heads, self.kv_heads, self.head_dim):
+            # a step of few rows: the projection rotates and stores its outputs itself
+            ops.linear_rope_cache(xn, self.w_qkv, qkv, ctx.pos, ctx.row_seq, cos, sin, cache.block_table, cache.k,
+                                  cache.v, self.heads, self.kv_heads, self.head_dim, write_kv=cache.writable)
+        else:
+            ops.linear(xn, self.w_qkv, qkv)
+            ops.rope_cache(qkv, ctx.pos, ctx.row_seq, cos, sin, cache.block_table, cache.k, cache.v,
+                           self.heads, self.kv_heads, self.head_dim, write_kv=cache.writable)
         attn = ctx.workspace.rows("attn", n, self.q_dim, ctx.act_dtype)
         ops.attention(qkv, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.pos, attn, self.heads,
                       self.kv_heads, self.head_dim, self.window or 0, ctx.max_keys, self.scale, batch=ctx)

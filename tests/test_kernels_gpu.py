@@ -394,6 +394,45 @@ def test_bf16_linear_swiglu_fused_equals_product_then_swiglu():
     assert not ops.device_failure()
 
 
+def test_bf16_qkv_product_that_rotates_and_stores_equals_product_then_rope():
+    """Steps of few rows: the fused q/k/v projection rotates q and k and writes k and v into
+    their pages in its own epilogue. Same bits as the product followed by the rotation
+    kernel: rotated q, and every byte of both caches; also without tables (no rotation) and
+    for a run that only reads a cache (nothing stored)."""
+    rng = np.random.default_rng(24)
+    ops = _ops("bfloat16")
+    from bitwise_b200.parts.rope import RotaryEncoding
+    for m, width, heads, kv_heads, hd, page in ((8, 2048, 32, 32, 64, 16), (1, 960, 15, 5, 64, 16), (13, 512, 4, 2, 128, 32),
+                                                (5, 192, 6, 3, 16, 8), (16, 1024, 8, 1, 48, 16)):
+        assert ops.fuses_rope(m, width, heads, kv_heads, hd), (m, width, heads, kv_heads, hd)
+        n = (heads + 2 * kv_heads) * hd
+        x, w = bf(rnd(rng, m, width)), bf(rnd(rng, n, width, scale=0.05))
+        cos, sin = RotaryEncoding(hd, 10000.0, None, positions=256).rotary_tables(DEV)
+        pos = rng.integers(0, 250, m).astype(np.int32)
+        seq = np.arange(m, dtype=np.int32)
+        pages = m * (256 // page) + 2
+        table = rng.permutation(pages)[:m * (256 // page)].reshape(m, -1).astype(np.int32)
+        for tables, write in (((cos, sin), True), ((None, None), True), ((cos, sin), False)):
+            outs = []
+            for fused in (False, True):
+                k = torch.full((pages, kv_heads, page, hd), 0.5, device=DEV, dtype=torch.bfloat16)
+                v = torch.full((pages, kv_heads, page, hd), -0.25, device=DEV, dtype=torch.bfloat16)
+                qkv = torch.zeros(m, n, device=DEV, dtype=torch.bfloat16)
+                args = (t(pos, torch.int32), t(seq, torch.int32), tables[0], tables[1], t(table, torch.int32), k, v,
+                        heads, kv_heads, hd)
+                if fused:
+                    ops.linear_rope_cache(t(x, torch.bfloat16), t(w, torch.bfloat16), qkv, *args, write_kv=write)
+                else:
+                    ops.linear(t(x, torch.bfloat16), t(w, torch.bfloat16), qkv)
+                    ops.rope_cache(qkv, *args, write_kv=write)
+                outs.append((qkv[:, :heads * hd].float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy()))
+            for got, want, what in zip(outs[1], outs[0], ("q", "key cache", "value cache")):
+                assert_same_bits(got, want, f"{what}: {heads}/{kv_heads} heads of {hd}, {m} rows, rotate "
+                                            f"{tables[0] is not None}, store {write}")
+    assert not ops.fuses_rope(40, 2048, 32, 32, 64)
+    assert not ops.device_failure()
+
+
 def test_bf16_rmsnorm_and_swiglu():
     """Tolerance: one bfloat16 rounding of a float32 result (2^-8 relative) plus 1e-6 absolute."""
     rng = np.random.default_rng(9)
