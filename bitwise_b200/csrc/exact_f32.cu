@@ -119,6 +119,84 @@ gemm_exact_kernel(const float* __restrict__ X, const float* __restrict__ W, floa
 }
 
 // ---------------------------------------------------------------------------------------
+// The same product for steps of few rows (decode steps, up to 16 rows), where the weights are
+// all that is read: one chain per output as above (a thread carries two rows of one column,
+// k ascending, fma after fma), but tiles of 16 columns, so that every SM streams weights (a
+// product with 2,048 columns is 128 blocks instead of 32), and the tiles of W and x come
+// through a ring of cp.async stages instead of a load, a barrier, the arithmetic and a
+// barrier in turn. Shared memory holds a stage as [k / 4][column or row][4 values]: a lane's
+// 16-byte read of its column meets no other lane's bank, the rows of x are broadcast.
+constexpr int kRowsBN = 16;      // columns per block
+constexpr int kRowsBK = 64;      // k per stage
+constexpr int kRowsStages = 6;
+
+__device__ __forceinline__ void cp_async16_f32(void* dst, const void* src, bool valid) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  const int bytes = valid ? 16 : 0;  // 0: zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+
+template <int R>  // rows of the tile: 8 or 16
+__global__ void __launch_bounds__(kRowsBN * R / 2)
+gemm_exact_rows_kernel(const float* __restrict__ X, const float* __restrict__ W, float* Y, const float* residual, int M,
+                       int N, int K) {
+  constexpr int kThreads = kRowsBN * R / 2;
+  __shared__ __align__(16) float Ws[kRowsStages][kRowsBK / 4][kRowsBN][4];
+  __shared__ __align__(16) float Xs[kRowsStages][kRowsBK / 4][R][4];
+  const int tid = threadIdx.x;
+  const int col = tid % kRowsBN, rp = tid / kRowsBN;  // this thread's column and pair of rows
+  const int n0 = blockIdx.x * kRowsBN;
+  const int stages_total = (K + kRowsBK - 1) / kRowsBK;
+  auto load_stage = [&](int st) {
+    const int slot = st % kRowsStages, k0 = st * kRowsBK;
+    for (int idx = tid; idx < kRowsBN * (kRowsBK / 4); idx += kThreads) {
+      const int c = idx / (kRowsBK / 4), k4 = idx % (kRowsBK / 4);  // a thread walks k: 16 bytes after 16 bytes of a row
+      const int gn = n0 + c, gk = k0 + k4 * 4;
+      const bool ok = gn < N && gk < K;  // K is a multiple of 4
+      cp_async16_f32(&Ws[slot][k4][c][0], W + (ok ? static_cast<size_t>(gn) * K + gk : 0), ok);
+    }
+    for (int idx = tid; idx < R * (kRowsBK / 4); idx += kThreads) {
+      const int r = idx / (kRowsBK / 4), k4 = idx % (kRowsBK / 4);
+      const int gk = k0 + k4 * 4;
+      const bool ok = r < M && gk < K;
+      cp_async16_f32(&Xs[slot][k4][r][0], X + (ok ? static_cast<size_t>(r) * K + gk : 0), ok);
+    }
+  };
+  for (int st = 0; st < kRowsStages - 1; ++st) {
+    if (st < stages_total) load_stage(st);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  float acc0 = 0.0f, acc1 = 0.0f;
+  for (int st = 0; st < stages_total; ++st) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(kRowsStages - 2));
+    __syncthreads();  // stage st has landed for every thread; the slot of stage st - 1 is free
+    if (st + kRowsStages - 1 < stages_total) load_stage(st + kRowsStages - 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    const int slot = st % kRowsStages;
+#pragma unroll
+    for (int k4 = 0; k4 < kRowsBK / 4; ++k4) {
+      const float4 w = *reinterpret_cast<const float4*>(&Ws[slot][k4][col][0]);
+      const float4 a = *reinterpret_cast<const float4*>(&Xs[slot][k4][2 * rp][0]);
+      const float4 b = *reinterpret_cast<const float4*>(&Xs[slot][k4][2 * rp + 1][0]);
+      acc0 = __fmaf_rn(a.x, w.x, acc0), acc1 = __fmaf_rn(b.x, w.x, acc1);
+      acc0 = __fmaf_rn(a.y, w.y, acc0), acc1 = __fmaf_rn(b.y, w.y, acc1);
+      acc0 = __fmaf_rn(a.z, w.z, acc0), acc1 = __fmaf_rn(b.z, w.z, acc1);
+      acc0 = __fmaf_rn(a.w, w.w, acc0), acc1 = __fmaf_rn(b.w, w.w, acc1);
+    }
+  }
+  const int gn = n0 + col;
+  if (gn >= N) return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int gm = 2 * rp + i;
+    if (gm >= M) continue;
+    const size_t o = static_cast<size_t>(gm) * N + gn;
+    const float v = i ? acc1 : acc0;
+    Y[o] = residual ? __fadd_rn(residual[o], v) : v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Rotary encoding in the rotate-half pairing (i, i + hd/2) with separate roundings of the
 // products (src/kernels.cpp:273-289), then the write of K and V into the paged cache
 // (src/model.cpp:285-297). cos/sin come from a host-built table [position][hd/2]. Queries
@@ -168,14 +246,16 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
 // (src/kernels.cpp:312-338,361-364). `window` > 0 limits the keys to the last `window`
 // positions. Every thread carries the running sum itself, so all hold the same value.
 constexpr int kAttnThreads = 128;
+constexpr int kAttnTileKeys = 64;  // keys per tile of values in shared memory
 
+template <bool STAGED>
 __global__ void __launch_bounds__(kAttnThreads)
 attention_exact_kernel(const float* __restrict__ qkv, int q_stride, const float* __restrict__ kcache,
                        const float* __restrict__ vcache, const int* __restrict__ block_table,
                        int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos,
                        float* __restrict__ out, int out_stride, int heads, int kv_heads, int hd, int page,
-                       int window, float scale) {
-  extern __shared__ float smem[];
+                       int window, float scale, int score_floats) {
+  extern __shared__ __align__(16) float smem[];
   float* q = smem;          // [hd]
   float* scores = smem + hd;  // [len]
   __shared__ float red[kAttnThreads / 32];
@@ -220,23 +300,81 @@ attention_exact_kernel(const float* __restrict__ qkv, int q_stride, const float*
   for (int j = tid; j < len; j += kAttnThreads) scores[j] = bw::det_expf(__fsub_rn(scores[j], mx));
   __syncthreads();
 
-  for (int d = tid; d < hd; d += kAttnThreads) {
-    float acc = 0.0f, sum = 0.0f;
-    int j = lo;
-    while (j <= p) {
-      const int b = j / page;
-      const int first = j - b * page;
-      const int last = (p - b * page < page - 1) ? p - b * page : page - 1;
-      const float* vp = vcache + ((static_cast<size_t>(table[b]) * kv_heads + g) * page) * hd + d;
+  // Second pass, in key order: thread d walks the keys for output element d: sum += e,
+  // acc = fma(e, v, acc). With many blocks (prefill) it reads the values straight from the
+  // cache: other blocks hide the latency of its loads.
+  if (!STAGED) {
+    for (int d = tid; d < hd; d += kAttnThreads) {
+      float acc = 0.0f, sum = 0.0f;
+      int j = lo;
+      while (j <= p) {
+        const int b = j / page;
+        const int first = j - b * page;
+        const int last = (p - b * page < page - 1) ? p - b * page : page - 1;
+        const float* vp = vcache + ((static_cast<size_t>(table[b]) * kv_heads + g) * page) * hd + d;
 #pragma unroll 4
-      for (int s = first; s <= last; ++s) {
-        const float e = scores[j - lo + (s - first)];
-        sum = __fadd_rn(sum, e);
-        acc = __fmaf_rn(e, vp[static_cast<size_t>(s) * hd], acc);
+        for (int s = first; s <= last; ++s) {
+          const float e = scores[j - lo + (s - first)];
+          sum = __fadd_rn(sum, e);
+          acc = __fmaf_rn(e, vp[static_cast<size_t>(s) * hd], acc);
+        }
+        j += last - first + 1;
       }
-      j += last - first + 1;
+      out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc, __fdiv_rn(1.0f, sum));
     }
-    out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc, __fdiv_rn(1.0f, sum));
+    return;
+  }
+  // With few blocks (decode steps) a walk through the cache is a chain of load latencies. The
+  // values then come through shared memory in tiles of 64 keys that all threads fetch
+  // together (cp.async, the next tile on its way while this one is used); the same operations
+  // in the same order.
+  float* vt = scores + score_floats;  // [2][kAttnTileKeys][hd]
+  constexpr int kMaxD = 256 / kAttnThreads;  // output elements per thread (head sizes up to 256)
+  float acc[kMaxD], sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kMaxD; ++i) acc[i] = 0.0f;
+  const int tiles = (len + kAttnTileKeys - 1) / kAttnTileKeys;
+  const int pieces = hd / 4;  // 16-byte pieces of a value row
+  auto fetch = [&](int t) {
+    float* dst = vt + (t & 1) * kAttnTileKeys * hd;
+    for (int idx = tid; idx < kAttnTileKeys * pieces; idx += kAttnThreads) {
+      const int key = idx / pieces, piece = idx - key * pieces;
+      const int j = lo + t * kAttnTileKeys + key;
+      const bool ok = j <= p;
+      const float* src = vcache;
+      if (ok) src += ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + j % page) * hd + piece * 4;
+      const unsigned d32 = static_cast<unsigned>(__cvta_generic_to_shared(dst + key * hd + piece * 4));
+      const int bytes = ok ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d32), "l"(src), "r"(bytes));
+    }
+  };
+  fetch(0);
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (int t = 0; t < tiles; ++t) {
+    if (t + 1 < tiles) fetch(t + 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 1;\n" ::);
+    __syncthreads();
+    const float* v = vt + (t & 1) * kAttnTileKeys * hd;
+    const int keys = min(kAttnTileKeys, len - t * kAttnTileKeys);
+    const float* e_t = scores + t * kAttnTileKeys;
+#pragma unroll 8
+    for (int s2 = 0; s2 < keys; ++s2) {
+      const float e = e_t[s2];
+      sum = __fadd_rn(sum, e);
+#pragma unroll
+      for (int i = 0; i < kMaxD; ++i) {
+        const int d = tid + i * kAttnThreads;
+        if (d < hd) acc[i] = __fmaf_rn(e, v[s2 * hd + d], acc[i]);
+      }
+    }
+    __syncthreads();  // the tile may be overwritten by the fetch after next
+  }
+  const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+  for (int i = 0; i < kMaxD; ++i) {
+    const int d = tid + i * kAttnThreads;
+    if (d < hd) out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc[i], inv);
   }
 }
 
@@ -280,7 +418,13 @@ BW_API int bw_f32_linear(const float* x, const float* w, float* y, const float* 
     return -1;
   }
   const unsigned gx = (n + kGemmBN - 1) / kGemmBN;
-  if (m <= 16) {
+  if (m <= 16 && k % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    const unsigned blocks = (n + kRowsBN - 1) / kRowsBN;  // rows that start on 16 bytes: the streaming tile
+    if (m <= 8)
+      gemm_exact_rows_kernel<8><<<blocks, kRowsBN * 4, 0, stream>>>(x, w, y, residual, m, n, k);
+    else
+      gemm_exact_rows_kernel<16><<<blocks, kRowsBN * 8, 0, stream>>>(x, w, y, residual, m, n, k);
+  } else if (m <= 16) {
     gemm_exact_kernel<16><<<dim3(gx, (m + 15) / 16), 256, 0, stream>>>(x, w, y, residual, m, n, k);
   } else {
     const unsigned gy = (m + 63) / 64;
@@ -320,7 +464,13 @@ BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache,
     bw::set_error("attention: %d heads are not a multiple of %d key/value heads", heads, kv_heads);
     return -1;
   }
-  const size_t smem = (static_cast<size_t>(hd) + max_keys) * sizeof(float);
+  if (hd > 256) {
+    bw::set_error("attention (32-bit): head size %d exceeds 256", hd);
+    return -1;
+  }
+  const int score_floats = (max_keys + 3) / 4 * 4;  // keeps the value tiles behind the scores on 16 bytes
+  const bool staged = static_cast<long long>(n) * heads <= 148 * 16;  // few blocks: a decode step
+  const size_t smem = (static_cast<size_t>(hd) + score_floats + (staged ? 2 * kAttnTileKeys * hd : 0)) * sizeof(float);
   if (smem > 220 * 1024) {
     bw::set_error("attention (32-bit): %d keys exceed the shared-memory score buffer", max_keys);
     return -1;
@@ -329,19 +479,26 @@ BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache,
     bw::set_error("attention: %d heads exceed the grid limit", heads);
     return -1;
   }
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static bool configured = false;
+  if (smem > 48 * 1024 && !configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_exact_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          220 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_exact_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) {
       bw::set_error("attention: cannot raise shared memory: %s", cudaGetErrorString(e));
       return static_cast<int>(e);
     }
-    configured = 220 * 1024;
+    configured = true;
   }
-  attention_exact_kernel<<<dim3(n, heads), kAttnThreads, smem, stream>>>(
-      qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads, kv_heads, hd,
-      page, window, scale);
+  if (staged)
+    attention_exact_kernel<true><<<dim3(n, heads), kAttnThreads, smem, stream>>>(
+        qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads, kv_heads, hd,
+        page, window, scale, score_floats);
+  else
+    attention_exact_kernel<false><<<dim3(n, heads), kAttnThreads, smem, stream>>>(
+        qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads, kv_heads, hd,
+        page, window, scale, score_floats);
   return bw::launch_status();
 }
 
