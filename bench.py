@@ -11,7 +11,8 @@ synthetic prompt ids uniform over the vocabulary; batch of 8 requests decoding a
   value        decoded tokens per second, timed on the device with CUDA events
   e2e          the same through the Python entry point (Engine.step): host tokens in from
                pinned memory, sampled tokens read back to the host, every step
-  prefill      one step of 2,048 prompt tokens; frac = flops / time / bf16 peak
+  prefill      one step of 2,048 prompt tokens; frac = flops / time / bf16 peak (float32 runs:
+               / the float32 peak of the CUDA cores)
   roofline     decode step: bytes it must read (every weight once + the cache of the live
                requests) / time, against the copy bandwidth
   points       decode tokens per second at batch 1 and 64
@@ -38,6 +39,24 @@ sys.path.insert(0, HERE)
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 REFERENCE_DECODE_TOKS = 7.26  # tkran2/bitwise README.md:142, SmolLM2-1.7B single stream on a 4-core AVX-512 VM
+
+
+def fp32_simt_tflops():
+    """The float32 peak of the CUDA cores, from the device's own figures: SMs x 128 lanes x 2
+    flops x the highest SM clock (what the true 32-bit path, which uses no tensor core, is
+    measured against)."""
+    import torch
+    props = torch.cuda.get_device_properties(0)
+    mhz = 0.0
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits", "-i", "0"],
+                             capture_output=True, text=True, timeout=10).stdout.strip().splitlines()
+        mhz = float(out[0])
+    except Exception:
+        mhz = 0.0
+    if mhz <= 0:
+        mhz = 1965.0
+    return props.multi_processor_count * 128 * 2 * mhz * 1e6 / 1e12
 
 
 def peaks():
@@ -336,8 +355,11 @@ def main():
     if not args.skip_prefill:
         pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
         fl = prefill_flops(cfg, 2048)
+        peak_tf = pk["bf16_tflops"] if args.dtype == "bfloat16" else fp32_simt_tflops()
         line["prefill"] = {"value": round(2048 / (pms / 1e3), 1), "tokens": 2048, "ms": round(pms, 3),
-                           "frac": round(fl / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4), "flops": fl}
+                           "frac": round(fl / (pms / 1e3) / 1e12 / peak_tf, 4), "flops": fl}
+        if args.dtype != "bfloat16":
+            line["prefill"]["peak"] = "float32 on the CUDA cores, %.1f TFLOP/s nominal" % peak_tf
     if not args.skip_points:
         pts = {}
         for b in (1, 64):
@@ -359,6 +381,8 @@ def main():
             fp = run_prefill(m32, 2048, reps=3, warmup=3, page=args.page)
             f32["prefill"] = round(2048 / (fp / 1e3), 1)
             f32["prefill_ms"] = round(fp, 2)
+            # against the float32 peak of the CUDA cores (no tensor core on this path)
+            f32["prefill_frac"] = round(prefill_flops(cfg, 2048) / (fp / 1e3) / 1e12 / fp32_simt_tflops(), 4)
         line["fp32"] = f32
     print(json.dumps(line))
     return 0

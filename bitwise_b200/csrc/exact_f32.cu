@@ -119,6 +119,88 @@ gemm_exact_kernel(const float* __restrict__ X, const float* __restrict__ W, floa
 }
 
 // ---------------------------------------------------------------------------------------
+// The same product for large batches (prefill) whose rows start on 16 bytes: tiles of
+// 128 x 128 outputs, a thread carries 8 x 8 of them (each still one chain, k ascending), so that
+// four 16-byte reads from shared memory feed 64 multiply-adds; the next k-tile is fetched
+// into registers while this one is used, and two buffers in shared memory leave one barrier
+// per k-tile.
+constexpr int kBigBM = 128, kBigBN = 128, kBigBK = 16;
+
+__global__ void __launch_bounds__(256, 2)
+gemm_exact_big_kernel(const float* __restrict__ X, const float* __restrict__ W, float* Y, const float* residual, int M,
+                      int N, int K) {
+  __shared__ __align__(16) float As[2][kBigBK][kBigBM + 4];
+  __shared__ __align__(16) float Bs[2][kBigBK][kBigBN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;  // columns 4 tx .. + 3 and 64 + 4 tx .. + 3, rows 8 ty .. + 7
+  const int m0 = blockIdx.y * kBigBM, n0 = blockIdx.x * kBigBN;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+  // a thread fetches two 16-byte pieces of x and two of W per k-tile: piece p = tid + 256 i is
+  // row p / 4, k-quarter p % 4
+  float4 xa[2], wb[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int pc = tid + 256 * i, row = pc >> 2, gk = k0 + (pc & 3) * 4;
+      const int gm = m0 + row, gn = n0 + row;
+      xa[i] = (gm < M && gk < K) ? *reinterpret_cast<const float4*>(X + static_cast<size_t>(gm) * K + gk)
+                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // K is a multiple of 4
+      wb[i] = (gn < N && gk < K) ? *reinterpret_cast<const float4*>(W + static_cast<size_t>(gn) * K + gk)
+                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int pc = tid + 256 * i, row = pc >> 2, kq = (pc & 3) * 4;
+      As[buf][kq + 0][row] = xa[i].x, As[buf][kq + 1][row] = xa[i].y;
+      As[buf][kq + 2][row] = xa[i].z, As[buf][kq + 3][row] = xa[i].w;
+      Bs[buf][kq + 0][row] = wb[i].x, Bs[buf][kq + 1][row] = wb[i].y;
+      Bs[buf][kq + 2][row] = wb[i].z, Bs[buf][kq + 3][row] = wb[i].w;
+    }
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  const int tiles = (K + kBigBK - 1) / kBigBK;
+  for (int t = 0; t < tiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < tiles) fetch((t + 1) * kBigBK);
+#pragma unroll
+    for (int k = 0; k < kBigBK; ++k) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8 + 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][64 + tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+    }
+    if (t + 1 < tiles) stash(buf ^ 1);  // nobody reads that buffer: its tile was used before the last barrier
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + ty * 8 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (gn >= N) continue;
+      const size_t o = static_cast<size_t>(gm) * N + gn;
+      Y[o] = residual ? __fadd_rn(residual[o], acc[i][j]) : acc[i][j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // The same product for steps of few rows (decode steps, up to 16 rows), where the weights are
 // all that is read: one chain per output as above (a thread carries two rows of one column,
 // k ascending, fma after fma), but tiles of 16 columns, so that every SM streams weights (a
@@ -426,6 +508,13 @@ BW_API int bw_f32_linear(const float* x, const float* w, float* y, const float* 
       gemm_exact_rows_kernel<16><<<blocks, kRowsBN * 8, 0, stream>>>(x, w, y, residual, m, n, k);
   } else if (m <= 16) {
     gemm_exact_kernel<16><<<dim3(gx, (m + 15) / 16), 256, 0, stream>>>(x, w, y, residual, m, n, k);
+  } else if (m > 64 && k % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    const unsigned gy = (m + kBigBM - 1) / kBigBM;
+    if (gy > 65535u) {
+      bw::set_error("linear: %d rows exceed the grid limit", m);
+      return -1;
+    }
+    gemm_exact_big_kernel<<<dim3((n + kBigBN - 1) / kBigBN, gy), 256, 0, stream>>>(x, w, y, residual, m, n, k);
   } else {
     const unsigned gy = (m + 63) / 64;
     if (gy > 65535u) {
