@@ -38,7 +38,7 @@ from tiny_configs import TINY, tiny_tokens, write_tiny_folder  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="a checkout of tkran2/bitwise (its src/ is compiled)")
     args = ap.parse_args()
     ref = args.reference
     work = tempfile.mkdtemp(prefix="golden-")
