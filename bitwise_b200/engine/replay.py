@@ -30,7 +30,7 @@ MAX_LIVE_REQUESTS = 4
 
 
 def make_replay_stepper(model: Model, max_tokens: int, page_size: int = 16, max_live: int = MAX_LIVE_REQUESTS,
-                        max_rows: Optional[int] = None) -> Stepper:
+                        max_rows: Optional[int] = None, use_graphs: Optional[bool] = None) -> Stepper:
     """A stepper over a pool that holds ``max_tokens`` tokens (each live request's count
     rounded up to a multiple of 64; the page size divides 64)."""
     if 64 % page_size:
@@ -39,7 +39,7 @@ def make_replay_stepper(model: Model, max_tokens: int, page_size: int = 16, max_
     manager, storage = build_cache(model.decoder, pages, page_size, max_live, _TORCH_DTYPE[model.dtype],
                                    model.device)
     return Stepper(model.decoder, manager, storage, model.ops, max_rows=max_rows or max(max_tokens, 1),
-                   max_seqs=max_live, max_tokens_per_request=max_tokens)
+                   max_seqs=max_live, max_tokens_per_request=max_tokens, use_graphs=use_graphs)
 
 
 def replay(model: Model, lines: IO[str], out_dir: str, max_tokens: int, page_size: int = 16,

@@ -87,7 +87,7 @@ class Stepper:
     """Owns the step's device buffers and runs steps for one model and one cache."""
 
     GRAPH_MAX_ROWS = 256   # steps up to this many rows are replayed as CUDA graphs
-    GRAPH_CACHE = 256      # graphs kept (one per batch shape and context length in steps of 256)
+    GRAPH_CACHE = 256      # graphs kept (one per batch shape and bound on the context length)
 
     def __init__(self, model, manager: CacheManager, storage: CacheStorage, ops, max_rows: int,
                  max_seqs: int, max_tokens_per_request: int, use_graphs: Optional[bool] = None):
@@ -128,6 +128,8 @@ class Stepper:
         if use_graphs is None:
             use_graphs = pin and getattr(ops, "kind", "") == "bf16"
         self.use_graphs = bool(use_graphs) and getattr(model, "graph_safe", lambda: False)()
+        # contexts reach the kernels rounded up to this many keys (1: as they are)
+        self.key_granule = max(1, int(getattr(ops, "key_granule", 1)))
         self._graphs: Dict[tuple, tuple] = {}
         self._seen: Dict[tuple, int] = {}
         self.graph_replays = 0
@@ -208,6 +210,12 @@ class Stepper:
             after.append((e.rid, start + cnt))
             max_keys = max(max_keys, start + cnt)
             n += cnt
+        # What the kernels get is a bound on the context, rounded up to the library's granule:
+        # launchers size grids, scratch and record strides from it, so everything that a launch
+        # derives on the host is a function of the rounded value, which is also part of the key
+        # under which a step's graph is kept.  Rows are bounded on the device by their own position.
+        granule = self.key_granule
+        max_keys = (max_keys + granule - 1) // granule * granule
         h[L.tokens:L.tokens + n] = all_tokens
         h[L.pos:L.pos + n] = all_pos
         h[L.row_seq:L.row_seq + n] = all_row_seq
@@ -279,9 +287,9 @@ class Stepper:
         views = ctx.cache_views
         key = None
         if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:
-            # the longest context enters in steps of 256 keys: the attention kernel of a decode
-            # step launches one thread block per 256 keys
-            key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows, (ctx.max_keys + 255) // 256) + tuple(
+            # everything a launcher computes on the host is a function of these: the step's sizes,
+            # the (rounded) bound on the context and the numbers of query tiles
+            key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows, ctx.max_keys) + tuple(
                 t[3] for t in ctx.tile_sets.values())
         if key is not None and key in self._graphs:
             graph, logits, launches = self._graphs[key]

@@ -51,6 +51,11 @@ class KernelOps:
         self.dtype = dtype
         self.act_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
         self.kind = "f32" if dtype == "float32" else "bf16"
+        # The step function hands contexts to the kernels rounded up to this many keys.  The
+        # serving kernels derive grids and record strides from that bound, and a step replayed
+        # as a CUDA graph keeps what its capture derived: with the bound in steps of 256 a graph
+        # serves 256 positions, and a replay launches exactly what an eager step would.
+        self.key_granule = 1 if dtype == "float32" else 256
         path = build.ensure_built(self.kind, (), verbose_build)
         try:
             self.lib = ctypes.CDLL(path)

@@ -100,8 +100,9 @@ class DecoderModel:
         return self.embedding.param_bytes() + sum(b.param_bytes() for b in self.blocks) + self.head.param_bytes()
 
     def graph_safe(self) -> bool:
-        """True when every part runs kernels only (no host decisions inside forward), so a
-        step's launches can be captured into a CUDA graph."""
+        """True when every part only launches kernels in forward and decides nothing on the host
+        beyond what the step's sizes and ``ctx.max_keys`` determine, so that a step's launches
+        can be captured into a CUDA graph and replayed for steps with the same sizes."""
         parts = [self.embedding, self.head, self.head.norm] + list(self.position_encodings)
         for b in self.blocks:
             parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm]

@@ -20,7 +20,10 @@ from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, StepContext
 
 
 class GQAAttention(Mixer):
-    graph_safe = True  # kernels only: a step through this part can be captured
+    # Kernels only.  What forward and the launchers decide on the host depends on the step's
+    # sizes (rows, sequences, query tiles) and on ctx.max_keys, the rounded bound on the context;
+    # the stepper keeps a captured step under exactly these.
+    graph_safe = True
 
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int,
                  position: Optional[PositionEncoding] = None, window: Optional[int] = None,

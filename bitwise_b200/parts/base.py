@@ -107,7 +107,8 @@ class StepContext:
     seq_slot: torch.Tensor       # int32 [num_seqs] state slot of each sequence
     logit_rows: torch.Tensor     # int32 [c] rows whose logits are wanted
     num_logit_rows: int
-    max_keys: int                # largest pos + 1 in this step (host copy)
+    max_keys: int                # bound on pos + 1 over the step's rows, rounded up to ops.key_granule:
+                                 # for sizing launches on the host; rows are bounded by ``pos`` on the device
     # query tiles for kernels that tile rows by sequence (sequence, first row, row count)
     tile_seq: Optional[torch.Tensor] = None
     tile_row0: Optional[torch.Tensor] = None

@@ -15,6 +15,6 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def tiny_folders(tmp_path_factory):
     """Model folders of the tiny configurations, written once per session into a temporary place."""
-    from tiny_configs import TINY, write_tiny_folder
+    from tiny_configs import LONG, TINY, write_tiny_folder
     root = tmp_path_factory.mktemp("tiny-models")
-    return {name: write_tiny_folder(str(root / name), name) for name in TINY}
+    return {name: write_tiny_folder(str(root / name), name) for name in list(TINY) + list(LONG)}

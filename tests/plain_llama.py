@@ -221,26 +221,33 @@ def attention(q, k, v, exp="libm", window=0, round_bf16=False):
     scale = f32(1.0) / np.sqrt(f32(hd), dtype=f32)
     kk = np.repeat(k, grp, axis=1)  # [T, heads, hd]
     vv = np.repeat(v, grp, axis=1)
-    # scores[t, h, j]
-    s = dot16(q[:, :, None, :], np.transpose(kk, (1, 0, 2))[None, :, :, :])
-    s = (s * scale).astype(f32)
-    t_idx = np.arange(T)[:, None, None]
-    j_idx = np.arange(T)[None, None, :]
-    valid = j_idx <= t_idx
-    if window and window > 0:
-        valid &= j_idx > t_idx - window
-    mx = np.max(np.where(valid, s, f32(-np.inf)), axis=2, keepdims=True)
-    e = np.where(valid, expf(np.where(valid, s - mx, f32(0.0)).astype(f32)), f32(0.0)).astype(f32)
-    e_pv = bf16_round(e) if round_bf16 else e
-    ssum = np.zeros((T, heads), dtype=f32)
-    acc = np.zeros((T, heads, hd), dtype=f32)
-    for j in range(T):
-        m = valid[:, :, j] if valid.shape[1] == heads else np.broadcast_to(valid[:, :, j], (T, heads))
-        ssum = np.where(m, (ssum + e[:, :, j]).astype(f32), ssum)
-        upd = fma32(e_pv[:, :, j, None], vv[j][None, :, :], acc)
-        acc = np.where(m[:, :, None], upd, acc)
-    inv = (f32(1.0) / ssum).astype(f32)
-    return (acc * inv[:, :, None]).astype(f32)
+    out = np.empty((T, heads, hd), dtype=f32)
+    # Query rows are taken in blocks only to bound the memory of the broadcast below; a row's
+    # arithmetic does not depend on the block it is in.
+    for t0 in range(0, T, 32):
+        t1 = min(T, t0 + 32)
+        R, J = t1 - t0, t1  # rows of the block, keys 0 .. t1-1
+        # scores[t, h, j]
+        s = dot16(q[t0:t1, :, None, :], np.transpose(kk[:J], (1, 0, 2))[None, :, :, :])
+        s = (s * scale).astype(f32)
+        t_idx = np.arange(t0, t1)[:, None, None]
+        j_idx = np.arange(J)[None, None, :]
+        valid = j_idx <= t_idx
+        if window and window > 0:
+            valid &= j_idx > t_idx - window
+        mx = np.max(np.where(valid, s, f32(-np.inf)), axis=2, keepdims=True)
+        e = np.where(valid, expf(np.where(valid, s - mx, f32(0.0)).astype(f32)), f32(0.0)).astype(f32)
+        e_pv = bf16_round(e) if round_bf16 else e
+        ssum = np.zeros((R, heads), dtype=f32)
+        acc = np.zeros((R, heads, hd), dtype=f32)
+        for j in range(J):
+            m = np.broadcast_to(valid[:, :, j], (R, heads))
+            ssum = np.where(m, (ssum + e[:, :, j]).astype(f32), ssum)
+            upd = fma32(e_pv[:, :, j, None], vv[j][None, :, :], acc)
+            acc = np.where(m[:, :, None], upd, acc)
+        inv = (f32(1.0) / ssum).astype(f32)
+        out[t0:t1] = (acc * inv[:, :, None]).astype(f32)
+    return out
 
 
 def swiglu(gate_up, inter, exp="libm"):

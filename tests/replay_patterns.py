@@ -101,12 +101,14 @@ def collect(steps, logits_by_step, vocab):
     return {rid: np.stack([d[i] for i in sorted(d)]) for rid, d in rows.items()}
 
 
-def run_in_process(model, steps, max_tokens, page_size=16):
-    """Replay through the package's stepper (what bin/trace_run drives), in this process."""
+def run_in_process(model, steps, max_tokens, page_size=16, use_graphs=None, max_live=4, info=None):
+    """Replay through the package's stepper (what bin/trace_run drives), in this process.
+    ``use_graphs``: None leaves the stepper's default, False runs every step eagerly.  ``info``:
+    a dict that receives the stepper's counters."""
     import torch
     from bitwise_b200.engine.replay import make_replay_stepper
     from bitwise_b200.engine.step import StepEntry
-    stepper = make_replay_stepper(model, max_tokens, page_size)
+    stepper = make_replay_stepper(model, max_tokens, page_size, max_live=max_live, use_graphs=use_graphs)
     outs = {}
     for st in steps:
         entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in st["entries"]]
@@ -117,4 +119,6 @@ def run_in_process(model, steps, max_tokens, page_size=16):
             stepper.finish(rid)
     stepper.manager.check_consistency()
     assert stepper.manager.all_free(), "pages or slots were not given back"
+    if info is not None:
+        info.update(graph_replays=stepper.graph_replays, steps=stepper.steps, use_graphs=stepper.use_graphs)
     return outs

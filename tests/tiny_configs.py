@@ -26,13 +26,25 @@ TINY = {
 }
 
 
+# For contexts of several hundred keys (key tiles, graph buckets, the streaming decode kernel
+# and the tensor-core prefill attention want head size 64); not part of TINY, whose members every
+# parametrised test runs.
+LONG = {
+    "tiny_long": dict(
+        config=LlamaConfig(vocab_size=320, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=64, intermediate_size=192, rope_theta=50000.0,
+                           rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024),
+        seed=31, norm_jitter=0.05, file_dtype="bfloat16", tokens=640),
+}
+
+
 def tiny_tokens(name, count=None, salt=0):
-    spec = TINY[name]
+    spec = TINY.get(name) or LONG[name]
     rng = np.random.default_rng(1000 + spec["seed"] + salt)
     return rng.integers(0, spec["config"].vocab_size, count or spec["tokens"]).tolist()
 
 
 def write_tiny_folder(folder, name):
-    spec = TINY[name]
+    spec = TINY.get(name) or LONG[name]
     return Model.write_random_folder(folder, spec["config"], seed=spec["seed"], dtype=spec["file_dtype"],
                                      norm_jitter=spec["norm_jitter"])
