@@ -11,6 +11,9 @@ from a config.json and a seed.
     bitwise_b200 generate --model DIR --prompt-ids 5,17,3 --max-new-tokens 16
     bitwise_b200 sim --model DIR --traces 100
     bitwise_b200 random --config config.json --seed 1 --out DIR
+
+Exit codes: 0 done, 1 a violation found by ``sim`` or an error in the model folder or the
+request (one line on standard error), 2 an unknown or malformed option, 3 no CUDA device.
 """
 from __future__ import annotations
 
@@ -27,7 +30,14 @@ def _add_model_args(p):
     p.add_argument("--device", default="cuda:0")
 
 
+class _NoDevice(Exception):
+    pass
+
+
 def _load_model(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise _NoDevice("no CUDA device is visible; this engine has no CPU path")
     from .config.registry import architecture_of
     from .model import Model
     if args.model:
@@ -130,7 +140,15 @@ def main(argv=None) -> int:
     r.set_defaults(fn=cmd_random)
 
     args = ap.parse_args(argv)
-    return args.fn(args)
+    try:
+        return args.fn(args)
+    except _NoDevice as e:
+        print(f"bitwise_b200: {e}", file=sys.stderr)
+        return 3
+    except (OSError, ValueError, RuntimeError) as e:
+        # configuration, weight, kernel and request errors carry their own one-line messages
+        print(f"bitwise_b200: {type(e).__name__}: {e}", file=sys.stderr)
+        return 1
 
 
 if __name__ == "__main__":

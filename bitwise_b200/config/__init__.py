@@ -1,4 +1,5 @@
-from .llama import ConfigError, LlamaConfig, RopeScaling, read_config_json
+from .base import ConfigError, read_config_json
+from .llama import LlamaConfig, RopeScaling
 from .registry import (Architecture, architecture_of, config_from_folder, known_architectures,
                        lookup_architecture, register_architecture)
 

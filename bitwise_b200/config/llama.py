@@ -15,14 +15,10 @@ them as constructor parameters from this object.
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass, field, asdict
 from typing import Optional
 
-
-class ConfigError(ValueError):
-    """A config.json that cannot describe a runnable model."""
+from .base import ConfigError, read_config_json  # noqa: F401  (read_config_json is re-exported)
 
 
 @dataclass(frozen=True)
@@ -38,7 +34,7 @@ class RopeScaling:
     @staticmethod
     def from_json(d: dict) -> "RopeScaling":
         kind = d.get("rope_type", d.get("type"))
-        if kind != "llama3":
+        if kind != "llama3":  # "default" (no rescaling) is handled by the caller
             raise ConfigError(
                 f"rope_scaling of type {kind!r} is not supported (supported: 'llama3')")
         try:
@@ -126,6 +122,16 @@ class LlamaConfig:
         bos = d.get("bos_token_id", -1)
         known = set(LlamaConfig.__dataclass_fields__) | {"architectures"}
         scaling = d.get("rope_scaling")
+        if scaling and scaling.get("rope_type", scaling.get("type")) == "default":
+            scaling = None  # the plain rotary table
+        # Options that would change the arithmetic and that this model does not have: the
+        # reference's Llama has SiLU only and no biases (src/kernels.cpp:291-298; src/model.cpp:150-164).
+        act = d.get("hidden_act", "silu")
+        if act not in ("silu", "swish"):
+            raise ConfigError(f"hidden_act {act!r} is not supported (the feed-forward is SwiGLU: 'silu')")
+        for key in ("attention_bias", "mlp_bias"):
+            if d.get(key):
+                raise ConfigError(f"{key} = true is not supported (the projections have no bias)")
         return LlamaConfig(
             vocab_size=d["vocab_size"],
             hidden_size=d["hidden_size"],
@@ -167,14 +173,3 @@ class LlamaConfig:
         if self.rope_scaling is not None:
             d["rope_scaling"] = asdict(self.rope_scaling)
         return d
-
-
-def read_config_json(folder: str) -> dict:
-    path = os.path.join(folder, "config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            return json.load(f)
-    except FileNotFoundError:
-        raise ConfigError(f"no config.json in {folder}") from None
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path} is not valid JSON: {e}") from None

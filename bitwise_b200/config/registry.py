@@ -10,7 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, Dict
 
-from .llama import ConfigError, read_config_json
+from .base import ConfigError, read_config_json
 
 
 @dataclass(frozen=True)

@@ -185,15 +185,6 @@ class KernelOps:
                        _c_int(int(legacy)), self._stream(),
                        launches=1 if legacy else self._linear_kernels(m, n, k, False, partials is not None))
 
-    def linear_norm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor],
-                    norm_weight: torch.Tensor, eps: float, norm_out: torch.Tensor) -> None:
-        """out = residual + x @ w.T in float32, then norm_out = rmsnorm(out) * norm_weight in
-        act_dtype.  Two kernels today (a fused variant for small batches was slower than
-        the pair: one block per row cannot hide the latency of adding the chunk sums); parts
-        call this one name so that a fused kernel can take its place."""
-        self.linear(x, w, out, residual=residual)
-        self.rmsnorm(out, norm_weight, eps, norm_out)
-
     def fuses_swiglu(self, width: int, intermediate: int) -> bool:
         """Whether ``linear_swiglu`` can take a feed-forward of these sizes (then its gate/up
         weights are to be interleaved with ``interleave_gate_up``)."""

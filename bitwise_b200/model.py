@@ -54,7 +54,8 @@ class Model:
         arch, config = config_from_folder(folder)
         decoder = arch.build(config)
         ops = ops or _default_ops(dtype)
-        state = load_state(folder, decoder.param_specs(), _TORCH_DTYPE[dtype], device)
+        state = load_state(folder, decoder.param_specs(), _TORCH_DTYPE[dtype], device,
+                           ignorable=decoder.ignorable_tensor, aliases=decoder.tensor_aliases())
         decoder.load_params(state, dtype, device)
         decoder.prepare(ops)
         return Model(decoder, dtype, device, ops)

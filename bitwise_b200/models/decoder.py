@@ -79,6 +79,8 @@ class DecoderModel:
     # -- parameters --------------------------------------------------------------------
     def param_specs(self) -> List[ParamSpec]:
         specs = self.embedding.param_specs(self.embed_prefix)
+        for pe in self.position_encodings:  # encodings with weights of their own (a learned table)
+            specs += pe.param_specs(self.embed_prefix)
         for i, b in enumerate(self.blocks):
             specs += b.param_specs(self.block_prefix.format(i))
         specs += self.head.param_specs()
@@ -86,10 +88,23 @@ class DecoderModel:
 
     def load_params(self, state: Dict[str, torch.Tensor], dtype: str, device) -> None:
         self.embedding.load_params(state, self.embed_prefix)
+        for pe in self.position_encodings:
+            pe.load_params(state, self.embed_prefix)
         for i, b in enumerate(self.blocks):
             b.load_params(state, self.block_prefix.format(i))
         self.head.load_params(state)
         self.dtype, self.device = dtype, device
+
+    def ignorable_tensor(self, name: str) -> bool:
+        """Stored tensors that the model has no use for: the rotary tables that older exports
+        keep as buffers (the engine builds its own from the configuration)."""
+        return name.endswith(".rotary_emb.inv_freq")
+
+    def tensor_aliases(self) -> Dict[str, str]:
+        """Stored name -> declared tensor it must repeat: a tied head stored a second time."""
+        if self.head.tied_to is not None:
+            return {f"{self.head.head_name}.weight": f"{self.embed_prefix}.{self.head.tied_to.name}.weight"}
+        return {}
 
     def prepare(self, ops) -> None:
         """Let every part lay out its weights for the kernel library it will run on."""
@@ -97,7 +112,8 @@ class DecoderModel:
             b.prepare(ops)
 
     def param_bytes(self) -> int:
-        return self.embedding.param_bytes() + sum(b.param_bytes() for b in self.blocks) + self.head.param_bytes()
+        return (self.embedding.param_bytes() + sum(b.param_bytes() for b in self.blocks) + self.head.param_bytes()
+                + sum(pe.param_bytes() for pe in self.position_encodings))
 
     def graph_safe(self) -> bool:
         """True when every part only launches kernels in forward and decides nothing on the host
@@ -121,12 +137,9 @@ class DecoderModel:
         self.embedding.forward(ctx, x)
         for pe in self.position_encodings:
             pe.on_embed(ctx, x)
-        normed = False
-        for i, run in enumerate(self.schedule):
+        for run in self.schedule:
             view = cache_views[run.cache]
             if not run.owns_cache and hasattr(view, "writable"):
                 view = type(view)(**{**view.__dict__, "writable": False})
-            # the norm the next run starts with may ride on this run's last kernel
-            nxt = self.blocks[self.schedule[i + 1].block].mixer_norm if i + 1 < len(self.schedule) else None
-            normed = self.blocks[run.block].forward(ctx, x, view, normed=normed, next_norm=nxt)
+            self.blocks[run.block].forward(ctx, x, view)
         return self.head.forward(ctx, x)

@@ -69,9 +69,7 @@ class GQAAttention(Mixer):
     def param_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
 
-    fuses_following_norm = True
-
-    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView, then_norm=None):
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView) -> None:
         ops, n = ctx.ops, ctx.n
         qkv = ctx.workspace.rows("qkv", n, self.q_dim + 2 * self.kv_dim, ctx.act_dtype)
         tables = self.position.rotary_tables(x.device) if self.position is not None else None
@@ -88,12 +86,7 @@ class GQAAttention(Mixer):
         attn = ctx.workspace.rows("attn", n, self.q_dim, ctx.act_dtype)
         ops.attention(qkv, cache.k, cache.v, cache.block_table, ctx.row_seq, ctx.pos, attn, self.heads,
                       self.kv_heads, self.head_dim, self.window or 0, ctx.max_keys, self.scale, batch=ctx)
-        if then_norm is not None and hasattr(then_norm[0], "fused_arguments"):
-            weight, eps = then_norm[0].fused_arguments()
-            ops.linear_norm(attn, self.w_o, x, x, weight, eps, then_norm[1])
-            return True
         ops.linear(attn, self.w_o, x, residual=x)
-        return False
 
 
 register_mixer("gqa_attention", GQAAttention)

@@ -34,7 +34,9 @@ class PagedKVNeed:
 
 @dataclass(frozen=True)
 class SlotStateNeed:
-    """State of fixed size per request, one slot each: ``shape`` elements of ``dtype``."""
+    """State of fixed size per request, one slot each: ``shape`` elements of ``dtype``.
+    A slot is handed out as the request that held it before left it: the mixer starts its state
+    itself at a request's first position (``seq_pos0 == 0``), as pages are not cleared either."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
 
@@ -181,11 +183,6 @@ class Mixer(Part):
     def cache_need(self):
         return None
 
-    # A mixer or feed-forward whose last operation can also apply the norm that follows it
-    # sets this to True and accepts ``then_norm=(norm, out)`` in forward: after adding into x
-    # it writes ``norm(x)`` into ``out`` and returns True (same bits as the separate norm).
-    fuses_following_norm = False
-
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache) -> None:
         """Read the normed rows ``xn`` (act dtype), add the mixer's output into the float32
         stream ``x`` in place.  ``cache`` is the view that fits ``cache_need``."""
@@ -193,8 +190,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    fuses_following_norm = False  # see Mixer
-
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
         """Read ``xn``, add the feed-forward's output into ``x`` in place."""
         raise NotImplementedError

@@ -48,22 +48,10 @@ class PreNormBlock(Part):
         for part, _ in self._children(""):
             part.prepare(ops)
 
-    def forward(self, ctx: StepContext, x: torch.Tensor, cache, normed: bool = False, next_norm=None) -> bool:
-        """Run the block on the stream ``x``.  ``normed``: the workspace's "normed" rows
-        already hold this block's mixer norm of x (the previous block's last kernel wrote
-        them).  ``next_norm``: the norm that the next block starts with; when this block's
-        feed-forward can apply it in its last kernel, the return value is True."""
+    def forward(self, ctx: StepContext, x: torch.Tensor, cache) -> None:
+        """Run the block on the float32 stream ``x`` in place."""
         xn = ctx.workspace.rows("normed", ctx.n, self.width, ctx.act_dtype)
-        if not normed:
-            self.mixer_norm.forward(ctx, x, xn)
-        done = False
-        if self.mixer.fuses_following_norm:
-            done = bool(self.mixer.forward(ctx, xn, x, cache, then_norm=(self.ffn_norm, xn)))
-        else:
-            self.mixer.forward(ctx, xn, x, cache)
-        if not done:
-            self.ffn_norm.forward(ctx, x, xn)
-        if next_norm is not None and self.feed_forward.fuses_following_norm:
-            return bool(self.feed_forward.forward(ctx, xn, x, then_norm=(next_norm, xn)))
+        self.mixer_norm.forward(ctx, x, xn)
+        self.mixer.forward(ctx, xn, x, cache)
+        self.ffn_norm.forward(ctx, x, xn)
         self.feed_forward.forward(ctx, xn, x)
-        return False

@@ -44,9 +44,7 @@ class SwiGLU(FeedForward):
             self.w_gate_up = ops.interleave_gate_up(gate, up)
             self.fused = True
 
-    fuses_following_norm = True
-
-    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, then_norm=None):
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
         ops, n = ctx.ops, ctx.n
         h = ctx.workspace.rows("ffn_h", n, self.intermediate, ctx.act_dtype)
         if self.fused:
@@ -55,12 +53,7 @@ class SwiGLU(FeedForward):
             gate_up = ctx.workspace.rows("gate_up", n, 2 * self.intermediate, ctx.act_dtype)
             ops.linear(xn, self.w_gate_up, gate_up)
             ops.swiglu(gate_up, h)
-        if then_norm is not None and hasattr(then_norm[0], "fused_arguments"):
-            weight, eps = then_norm[0].fused_arguments()
-            ops.linear_norm(h, self.w_down, x, x, weight, eps, then_norm[1])
-            return True
         ops.linear(h, self.w_down, x, residual=x)
-        return False
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -27,10 +27,6 @@ class RMSNorm(Norm):
     def param_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def fused_arguments(self):
-        """(weight, eps) for kernels that apply this norm inside their own epilogue."""
-        return self.weight, self.eps
-
     def forward(self, ctx: StepContext, x, out, rows=None) -> None:
         ctx.ops.rmsnorm(x, self.weight, self.eps, out, rows)
 

@@ -54,14 +54,23 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def _ignorable(ignorable) -> "callable":
+    """``ignorable`` as a predicate: a callable stays, names become a membership test."""
+    if callable(ignorable):
+        return ignorable
+    names = set(ignorable)
+    return lambda n: n in names
+
+
 def check_against_specs(available: Mapping[str, tuple], specs: Iterable[ParamSpec],
-                        ignorable: Iterable[str] = (), source: str = "") -> None:
-    """Raise :class:`WeightError` unless ``available`` (name -> shape) fits ``specs``."""
+                        ignorable=(), source: str = "") -> None:
+    """Raise :class:`WeightError` unless ``available`` (name -> shape) fits ``specs``.
+    ``ignorable``: names, or a predicate on names, of stored tensors the model has no use for."""
     specs = list(specs)
     by_name = {s.name: s for s in specs}
     missing = [s.name for s in specs if s.name not in available and not s.optional]
-    ignorable = set(ignorable)
-    unexpected = [n for n in available if n not in by_name and n not in ignorable]
+    skip = _ignorable(ignorable)
+    unexpected = [n for n in available if n not in by_name and not skip(n)]
     wrong = [(n, tuple(available[n]), by_name[n].shape) for n in available
              if n in by_name and tuple(available[n]) != tuple(by_name[n].shape)]
     if missing or unexpected or wrong:
@@ -82,8 +91,11 @@ def _convert(t: torch.Tensor, spec: ParamSpec, matrix_dtype: torch.dtype, device
 
 
 def load_state(folder: str, specs: Iterable[ParamSpec], matrix_dtype: torch.dtype, device,
-               ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
-    """Read every declared tensor of ``folder`` onto ``device``."""
+               ignorable=(), aliases: Mapping[str, str] = {}) -> Dict[str, torch.Tensor]:
+    """Read every declared tensor of ``folder`` onto ``device``.  ``aliases`` maps the name of
+    a stored tensor that the model does not declare to the declared tensor it must repeat bit
+    for bit (a tied head that an exporter stored a second time): equal copies are passed over,
+    a copy that differs is an error."""
     specs = list(specs)
     shards = open_model_shards(folder)
     where: Dict[str, object] = {}
@@ -95,7 +107,16 @@ def load_state(folder: str, specs: Iterable[ParamSpec], matrix_dtype: torch.dtyp
             where[n] = sh
     if duplicates:
         raise SafetensorsError("tensors stored more than once in " + folder + ": " + ", ".join(duplicates))
-    check_against_specs({n: sh.entries[n].shape for n, sh in where.items()}, specs, ignorable, folder)
+    skip = _ignorable(ignorable)
+    declared = {s.name for s in specs}
+    copies = {a: t for a, t in aliases.items() if a in where and a not in declared and t in where}
+    check_against_specs({n: sh.entries[n].shape for n, sh in where.items()}, specs,
+                        lambda n: n in copies or skip(n), folder)
+    for alias, target in copies.items():
+        a, b = where[alias].tensor(alias), where[target].tensor(target)
+        if a.shape != b.shape or a.dtype != b.dtype or not torch.equal(a, b):
+            raise SafetensorsError(f"{folder}: {alias} is stored although the model ties it to {target}, "
+                                   f"and the two differ")
     out = {}
     for s in specs:
         if s.name in where:
@@ -106,7 +127,7 @@ def load_state(folder: str, specs: Iterable[ParamSpec], matrix_dtype: torch.dtyp
 
 
 def state_from_tensors(tensors: Mapping[str, torch.Tensor], specs: Iterable[ParamSpec],
-                       matrix_dtype: torch.dtype, device, ignorable: Iterable[str] = (),
+                       matrix_dtype: torch.dtype, device, ignorable=(),
                        source: str = "(in memory)") -> Dict[str, torch.Tensor]:
     """The same check and conversion for tensors that are already in memory."""
     specs = list(specs)

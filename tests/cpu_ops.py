@@ -34,10 +34,6 @@ class CpuOps:
             y = residual + y
         out.copy_(y.to(out.dtype))
 
-    def linear_norm(self, x, w, out, residual, norm_weight, eps, norm_out):
-        self.linear(x, w, out, residual=residual)
-        self.rmsnorm(out, norm_weight, eps, norm_out)
-
     def fuses_swiglu(self, width, intermediate):
         return False
 

@@ -40,11 +40,21 @@ def test_every_key_is_read():
     (dict(rms_norm_eps=0.0), "rms_norm_eps"),
     (dict(rope_scaling=dict(rope_type="yarn", factor=2.0)), "not supported"),
     (dict(rope_scaling=dict(rope_type="llama3", factor=2.0)), "lacks the key"),
+    (dict(hidden_act="gelu"), "hidden_act"),
+    (dict(attention_bias=True), "attention_bias"),
+    (dict(mlp_bias=True), "mlp_bias"),
 ])
 def test_bad_configurations_are_refused(patch, word):
     with pytest.raises(ConfigError) as e:
         LlamaConfig.from_json(dict(BASE, **patch))
     assert word in str(e.value)
+
+
+def test_options_that_change_nothing_are_accepted():
+    c = LlamaConfig.from_json(dict(BASE, hidden_act="silu", attention_bias=False, mlp_bias=False,
+                                   rope_scaling=dict(rope_type="default")))
+    assert c.rope_scaling is None
+    assert LlamaConfig.from_json(dict(BASE, rope_scaling=None)).rope_scaling is None
 
 
 def test_missing_keys_are_listed_together():

@@ -33,8 +33,10 @@ def test_generation_float32_equals_plain_tokens_and_fingerprints(name, tiny_fold
     plain = P.PlainLlama(tiny_folders[name], exp="det")
     want = [P.generate(plain, p, sp.max_new_tokens, sp.temperature, sp.seed, ignore_eos=True) for p in prompts]
     model = _model(tiny_folders[name], "float32")
+    # the second pool is too small for the requests together: they preempt each other
+    scarce = 6 if name == "tiny_a" else 10
     for cfg in (EngineConfig(num_blocks=64, max_batched_tokens=256, max_num_seqs=8),
-                EngineConfig(num_blocks=10, max_batched_tokens=24, max_num_seqs=3)):
+                EngineConfig(num_blocks=scarce, max_batched_tokens=24, max_num_seqs=len(prompts))):
         eng = Engine(model, cfg)
         ids = [eng.add_request(p, sp) for p in prompts]
         steps = 0
@@ -46,6 +48,7 @@ def test_generation_float32_equals_plain_tokens_and_fingerprints(name, tiny_fold
             assert eng.result(rid).tokens == toks
             assert eng.result(rid).logits_fingerprint == fp
         assert eng.free_blocks == cfg.num_blocks and eng.manager.all_free()
+        assert (eng.stats.preemptions > 0) == (cfg.num_blocks == scarce), eng.stats
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -73,11 +73,10 @@ def test_plain_reproduces_the_reference_bit_for_bit(name, tiny_folders):
     assert np.abs(det - gold).max() < 2e-6
 
 
-def test_counter_uniform_known_values():
-    # a pure function of (seed, position, stream), in [0, 1) (src/engine.cpp:35-38)
+def test_counter_uniform_is_a_pure_function_in_the_unit_interval():
+    # (seed, position, stream) -> [0, 1) (src/engine.cpp:35-38); the values themselves are pinned on
+    # the reference's own function in test_scheduler_vs_reference.py
     u = [P.counter_uniform(7, p) for p in range(1000)]
     assert all(0.0 <= x < 1.0 for x in u) and len(set(u)) == 1000
     assert P.counter_uniform(7, 5) == P.counter_uniform(7, 5) != P.counter_uniform(8, 5)
     assert P.counter_uniform(7, 5, 0) != P.counter_uniform(7, 5, 1)
-    from bitwise_b200.sampling import counter_uniform
-    assert [counter_uniform(3, p) for p in range(50)] == [P.counter_uniform(3, p) for p in range(50)]

@@ -106,3 +106,35 @@ def test_random_folder_is_a_function_of_config_and_seed(tmp_path):
     d = Model.write_random_folder(str(tmp_path / "d"), CFG, seed=5, norm_jitter=0.1)
     n = SafetensorsFile(os.path.join(d, "model.safetensors")).tensor("model.norm.weight")
     assert float(n.min()) >= 0.9 and float(n.max()) <= 1.1 and float(n.std()) > 0.02
+
+
+def test_model_load_passes_over_rotary_buffers_and_a_repeated_tied_head(tmp_path):
+    """Older exports keep ``rotary_emb.inv_freq`` buffers, and some store ``lm_head.weight``
+    although the head is tied: the first is of no use (the table is built from the
+    configuration), the second is passed over when it repeats the embedding bit for bit and
+    refused when it does not."""
+    from cpu_ops import CpuOps
+    tied = LlamaConfig(vocab_size=50, hidden_size=32, num_hidden_layers=1, num_attention_heads=2,
+                       intermediate_size=40, head_dim=16, tie_word_embeddings=True)
+    folder = Model.write_random_folder(str(tmp_path / "m"), tied, seed=2)
+    path = os.path.join(folder, "model.safetensors")
+    f = SafetensorsFile(path)
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    assert "lm_head.weight" not in tensors
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    write_safetensors(path, list(tensors.items()))
+    m = Model.load(folder, "float32", device="cpu", ops=CpuOps("float32"))
+    assert m.decoder.head.weight is m.decoder.embedding.table
+    tensors["lm_head.weight"][3, 4] += 1.0
+    write_safetensors(path, list(tensors.items()))
+    with pytest.raises(SafetensorsError) as e:
+        Model.load(folder, "float32", device="cpu", ops=CpuOps("float32"))
+    assert "lm_head.weight" in str(e.value) and "differ" in str(e.value)
+    # anything else that the model does not declare is still reported
+    del tensors["lm_head.weight"]
+    tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(32)
+    write_safetensors(path, list(tensors.items()))
+    with pytest.raises(WeightError) as e:
+        Model.load(folder, "float32", device="cpu", ops=CpuOps("float32"))
+    assert e.value.unexpected == ["model.layers.0.self_attn.q_proj.bias"]

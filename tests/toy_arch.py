@@ -127,24 +127,16 @@ class LearnedPositions(PositionEncoding):
         self.table = None
 
     def param_specs(self, prefix):
-        return [ParamSpec(prefix + ".weight", (self.positions, self.width), KEEP32)]
+        return [ParamSpec(prefix + ".positions.weight", (self.positions, self.width), KEEP32)]
 
     def load_params(self, state, prefix):
-        self.table = state[prefix + ".weight"]
+        self.table = state[prefix + ".positions.weight"]
+
+    def param_bytes(self):
+        return self.table.numel() * self.table.element_size()
 
     def on_embed(self, ctx, x):
         x += self.table[ctx.pos.long()]
-
-
-class ToyDecoder(DecoderModel):
-    """Adds the learned position table to the decoder's parameters."""
-
-    def param_specs(self):
-        return super().param_specs() + self.learned.param_specs("model.positions")
-
-    def load_params(self, state, dtype, device):
-        super().load_params(state, dtype, device)
-        self.learned.load_params(state, "model.positions")
 
 
 def build_toy(c: ToyConfig) -> DecoderModel:
@@ -163,10 +155,9 @@ def build_toy(c: ToyConfig) -> DecoderModel:
         blocks.append(PreNormBlock(c.hidden_size, mixer, ff, RMSNorm(c.hidden_size, c.eps),
                                    RMSNorm(c.hidden_size, c.eps), NAMES))
     head = OutputHead(c.vocab_size, c.hidden_size, RMSNorm(c.hidden_size, c.eps), tied_to=emb)
-    model = ToyDecoder(c, emb, blocks, head, schedule=[LayerRun(*s) for s in c.schedule],
-                       position_encodings=[rotary, learned])
-    model.learned = learned
-    return model
+    # the decoder declares and loads the parameters of its position encodings itself
+    return DecoderModel(c, emb, blocks, head, schedule=[LayerRun(*s) for s in c.schedule],
+                        position_encodings=[rotary, learned])
 
 
 def register():
