@@ -434,9 +434,6 @@ constexpr int kStreamStages = 2;
 constexpr int kStreamMaxRows = 512;  // rows of a step whose positions fit into shared memory beside the rings
 constexpr int kStreamQBytes = 16 * 128;                       // 16 stacked rows; a step's row fills `group` of them
 constexpr int kStreamItemBytes = kStreamQBytes + 2 * kKVBytes;  // 18 KB, a multiple of 1024
-constexpr uint32_t kStreamSpinLimit = 20000000u;              // about a second of polling
-
-__device__ int g_stream_failed = 0;  // raised when a bounded wait ran out
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -448,20 +445,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kStreamSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return;
-  }
-  g_stream_failed = 1;  // the outputs of this launch are worthless; the host learns of it
+// gives up after a limit and raises the library's failure word: the outputs of this launch are
+// then worthless, and the host learns of it
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* failure) {
+  bw::mbar_wait_bounded(bar, parity, reinterpret_cast<volatile uint32_t*>(failure));
 }
 __device__ __forceinline__ void tma_box_4d(void* dst, const CUtensorMap* map, int c2, int c3, uint64_t* bar) {
   asm volatile(
@@ -483,7 +470,8 @@ __global__ void __launch_bounds__(kStreamWarps * 32)
 attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
                         const int* __restrict__ row_seq, const int* __restrict__ pos, int n, int heads, int kv_heads,
-                        int page, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles) {
+                        int page, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles,
+                        int* failure) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -608,7 +596,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int first = first_key(it.p);
     const int stage = used % kStreamStages;
     unsigned char* buf = ring + stage * kStreamItemBytes;
-    mbar_wait_bounded(bars + stage, (used / kStreamStages) & 1);
+    mbar_wait_bounded(bars + stage, (used / kStreamStages) & 1, failure);
     TileResult r;
     attend_tile(buf, buf + kStreamQBytes, buf + kStreamQBytes + kKVBytes, lane, it.t * kTileKV, it.p, it.p, first, first,
                 scale_log2, r);
@@ -806,16 +794,6 @@ BW_API int bw_bf16_attention_stream_usable(int n, int heads, int kv_heads, int h
   return group <= 16 && page >= 8 && kTileKV % page == 0 && q_stride % 8 == 0 && stream_encoder() != nullptr;
 }
 
-BW_API int bw_bf16_attention_stream_failed() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_stream_failed, sizeof(int)) != cudaSuccess) return 0;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_stream_failed, &zero, sizeof(int));
-  }
-  return v;
-}
-
 // A decode step (one query row per sequence): tile results by the streaming kernel, then the
 // ordered merge. `scratch` as for bw_bf16_attention (bw_bf16_attention_scratch_floats).
 BW_API int bw_bf16_attention_stream(const __nv_bfloat16* qkv, int q_stride, const __nv_bfloat16* kcache,
@@ -873,12 +851,15 @@ BW_API int bw_bf16_attention_stream(const __nv_bfloat16* qkv, int q_stride, cons
       return -1;
     }
   }
+  int* word = bw::failure_word();
+  if (!word) return -1;
   const float scale_log2 = scale * 1.44269504088896341f;
   const long long warps_needed = (items + 0) / 1;
   const unsigned grid = static_cast<unsigned>(
       warps_needed < static_cast<long long>(sms) * kStreamWarps ? (warps_needed + kStreamWarps - 1) / kStreamWarps : sms);
   bw::launch_pdl(attention_stream_kernel, dim3(grid), dim3(kStreamWarps * 32), smem, stream, map_q, map_k, map_v,
-                 block_table, max_blocks, row_seq, pos, n, heads, kv_heads, page, window, scale_log2, scratch, key_tiles);
+                 block_table, max_blocks, row_seq, pos, n, heads, kv_heads, page, window, scale_log2, scratch, key_tiles,
+                 word);
   bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(kMergeThreads), 0, stream, scratch, key_tiles, pos, out,
                  out_stride, heads, window);
   return bw::launch_status();
@@ -886,5 +867,4 @@ BW_API int bw_bf16_attention_stream(const __nv_bfloat16* qkv, int q_stride, cons
 #else
 BW_API int bw_bf16_attention_stream_mode(int) { return 0; }
 BW_API int bw_bf16_attention_stream_usable(int, int, int, int, int, int) { return 0; }
-BW_API int bw_bf16_attention_stream_failed() { return 0; }
 #endif

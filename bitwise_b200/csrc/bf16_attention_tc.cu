@@ -36,7 +36,6 @@ constexpr int kQBytes = kTileM * 128;          // 16 KB
 constexpr int kKBytes = kTileKV * 128;         // 8 KB
 constexpr int kPBytes = kTileM * 128;          // 16 KB per weight buffer
 constexpr int kTmemCols = 256;                 // S0 S1 O0 O1, 64 columns each
-constexpr uint32_t kSpinLimit = 20000000u;
 
 struct __align__(8) Barriers {
   uint64_t q_full;
@@ -62,21 +61,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* failed) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((spin & 1023u) == 1023u && *failed) return false;
-  }
-  *failed = 1;
-  return false;
+  return bw::mbar_wait_bounded(bar, parity, failed);
 }
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
                                             uint64_t* bar) {
@@ -429,8 +414,6 @@ bool make_map4(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], 
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int* g_error_flag = nullptr;
-
 }  // namespace
 
 // Query rows per block, or 0 when this kernel cannot take the shape: head size 64, a page size
@@ -440,14 +423,6 @@ BW_API int bw_bf16_attention_tc_tile_rows(int heads, int kv_heads, int hd, int p
   const int group = heads / kv_heads;
   if (group > kTileM || kTileM % group || page <= 0 || kTileKV % page || q_stride % 8 || !encoder()) return 0;
   return kTileM / group;
-}
-
-BW_API int bw_bf16_attention_tc_failed() {
-  if (!g_error_flag) return 0;
-  int v = 0;
-  cudaMemcpy(&v, g_error_flag, sizeof(int), cudaMemcpyDeviceToHost);
-  if (v) cudaMemset(g_error_flag, 0, sizeof(int));
-  return v;
 }
 
 BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __nv_bfloat16* kcache,
@@ -467,14 +442,8 @@ BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __
     return -1;
   }
   const int group = heads / kv_heads;
-  if (!g_error_flag) {
-    cudaError_t e = cudaMalloc(&g_error_flag, sizeof(int));
-    if (e != cudaSuccess) {
-      bw::set_error("attention (tcgen05): cannot allocate the error word: %s", cudaGetErrorString(e));
-      return static_cast<int>(e);
-    }
-    cudaMemset(g_error_flag, 0, sizeof(int));
-  }
+  int* word = bw::failure_word();
+  if (!word) return -1;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -509,13 +478,12 @@ BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __
   const float scale_log2 = scale * 1.44269504088896341f;
   bw::launch_pdl(attention_tc_kernel, dim3(kv_heads, num_tiles), dim3(kThreads), kSmemBytes, stream, map_q, map_k, map_v,
                  block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out, out_stride, heads,
-                 kv_heads, page, window, scale_log2, g_error_flag);
+                 kv_heads, page, window, scale_log2, word);
   return bw::launch_status();
 }
 
 #else  // other head sizes use the kernels of bf16_attention.cu
 
 BW_API int bw_bf16_attention_tc_tile_rows(int, int, int, int, int) { return 0; }
-BW_API int bw_bf16_attention_tc_failed() { return 0; }
 
 #endif

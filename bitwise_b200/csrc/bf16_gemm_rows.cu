@@ -36,9 +36,6 @@ constexpr int kGroupBytes = 8 * kChunk * 2;  // 8 rows x one chunk: [k-tile][row
 constexpr int kWarps = 4;              // warps per group of 8 columns; chunk c belongs to warp c % kWarps of the group
 constexpr int kStages = 2;             // buffers in a warp's ring of W items
 constexpr int kSmemLimit = 227 * 1024;
-constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
-
-__device__ int g_rows_failed = 0;  // raised when a bounded wait ran out
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -49,22 +46,11 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for a phase of a barrier; when the limit runs out the kernel raises its flag
-// and goes on (its outputs are then worthless, and the host learns of it).
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return;
-  }
-  g_rows_failed = 1;
+// Bounded wait for a phase of a barrier; when the limit runs out the thread raises the
+// library's failure word and the kernel goes on (its outputs are then worthless, and the host
+// learns of it).
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* failure) {
+  bw::mbar_wait_bounded(bar, parity, reinterpret_cast<volatile uint32_t*>(failure));
 }
 // One box of the view (64 k-elements, rows, k-tiles) of a row-major matrix: the box's rows
 // from `row` on, 8 k-tiles from `ktile` on, laid out [k-tile][row][128 bytes] with the
@@ -117,7 +103,7 @@ struct RopeCache {
 template <int EPI, bool ROWS16, int NT>
 __global__ void __launch_bounds__(NT * kWarps * 32)
 linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
-                   const float* residual, int M, int N, int K, int tiles, RopeCache rc) {
+                   const float* residual, int M, int N, int K, int tiles, RopeCache rc, int* failure) {
   static_assert(EPI != 3 || NT == 2, "a rotation needs both halves of a head in the tile");
   constexpr int R = ROWS16 ? 16 : 8;
   constexpr int kItemBytes = kGroupBytes;  // what a warp fetches per (tile, chunk): its group's 8 rows
@@ -185,7 +171,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         tma_load_box(xs + chunk * kXChunkBytes, &map_x, 0, chunk * kTilesPerChunk, xbar);
       }
     }
-    mbar_wait(xbar, 0);
+    mbar_wait(xbar, 0, failure);
   }
 
   // Shared-memory addresses of this lane's ldmatrix rows. A line of 128 bytes holds 64
@@ -219,7 +205,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
       const int stage = used % kStages;
       const uint32_t wb = smem_u32(ring + stage * kItemBytes) + b_off;
       const uint32_t xa = smem_u32(xs + chunk * kXChunkBytes) + a_off;
-      mbar_wait(wbar + stage, (used / kStages) & 1);
+      mbar_wait(wbar + stage, (used / kStages) & 1, failure);
       const int k_here = min(kChunk, K - chunk * kChunk);
       const int pairs = (k_here / kTileK) * 2;  // pairs of k-steps of 16 (k is a multiple of 64)
       float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -433,7 +419,10 @@ int launch_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, const f
     bw::set_error("linear (few rows): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
     return -1;
   }
-  bw::launch_pdl(kernel, dim3(s.grid), dim3(NT * kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles, rc);
+  int* word = bw::failure_word();
+  if (!word) return -1;
+  bw::launch_pdl(kernel, dim3(s.grid), dim3(NT * kWarps * 32), s.smem, stream, map_x, map_w, y, residual, m, n, k, s.tiles, rc,
+                 word);
   return bw::launch_status();
 }
 
@@ -456,17 +445,6 @@ BW_API int bw_bf16_linear_rows_enable(int on) {
   const int before = g_rows_enabled;
   g_rows_enabled = on ? 1 : 0;
   return before;
-}
-
-// Reads and clears the flag that a kernel raises when one of its bounded waits ran out.
-BW_API int bw_bf16_linear_rows_failed() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_rows_failed, sizeof(int)) != cudaSuccess) return 0;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_rows_failed, &zero, sizeof(int));
-  }
-  return v;
 }
 
 // Whether a product of this shape runs on this path (rows that start on 16 bytes, at most 16

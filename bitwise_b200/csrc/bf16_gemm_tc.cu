@@ -1,6 +1,6 @@
 // The bfloat16 matrix product on the fifth-generation tensor cores: tcgen05.mma with the
 // accumulator in tensor memory, operands brought into shared memory by TMA. One summation
-// order for every batch size: chunks of 2048 along k at fixed positions, inside a chunk the
+// order for every batch size: chunks of 512 along k at fixed positions, inside a chunk the
 // tensor core accumulates in steps of 16 along k, the chunk sums are added in float32 in
 // ascending order. A product with many output tiles walks the chunks of a tile inside one
 // block ("whole" mode). A product with few output tiles and few rows (decode steps) gives
@@ -59,7 +59,6 @@ __host__ __device__ inline RingShape ring_shape(int a_rows, int w_rows) {
   r.ring_bytes = r.stages * r.stage_bytes + r.pad_bytes;
   return r;
 }
-constexpr uint32_t kSpinLimit = 20000000u;  // about a second of polling
 
 struct __align__(8) Barriers {
   uint64_t full[kMaxStages];
@@ -85,21 +84,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 // Bounded wait: false when the limit ran out (or another thread of the block already gave up).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* failed) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((spin & 1023u) == 1023u && *failed) return false;
-  }
-  *failed = 1;
-  return false;
+  return bw::mbar_wait_bounded(bar, parity, failed);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -722,7 +707,6 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows 
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int* g_error_flag = nullptr;  // one word of device memory, allocated on first use
 int g_pair_tiles = 1;         // large batches: two blocks per 256 x 256 tile (0: one block per 128 x 256 tile)
 
 }  // namespace
@@ -741,15 +725,6 @@ BW_API int bw_bf16_linear_tc_pair_tiles(int on) {
   return before;
 }
 
-// Reads and clears the flag that a kernel raises when one of its bounded waits ran out.
-BW_API int bw_bf16_linear_tc_failed() {
-  if (!g_error_flag) return 0;
-  int v = 0;
-  cudaMemcpy(&v, g_error_flag, sizeof(int), cudaMemcpyDeviceToHost);
-  if (v) cudaMemset(g_error_flag, 0, sizeof(int));
-  return v;
-}
-
 // Scratch of split mode: chunk sums [chunks][m][n] float32 and one counter per column block.
 BW_API long long bw_bf16_linear_tc_scratch_floats(int m, int n, int k) {
   return static_cast<long long>((k + kChunk - 1) / kChunk) * m * n;
@@ -760,15 +735,22 @@ BW_API int bw_bf16_linear_tc_counters(int n) { return (n + BN - 1) / BN; }
 // few output tiles to occupy the machine. Both modes give the same bits.
 namespace {
 
+constexpr int kMaxDevices = 64;  // per-device state below is kept for device ordinals up to this
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+
 int sm_count_of_device() {
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
+  static int sm_count[kMaxDevices] = {0};
+  const int dev = current_device();
+  if (!sm_count[dev]) {
+    cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count[dev] <= 0) sm_count[dev] = 148;
   }
-  return sm_count;
+  return sm_count[dev];
 }
 
 // How a product with one block of rows (m <= 128) runs. A tcgen05.mma that adds to the
@@ -854,48 +836,64 @@ struct Fused {
   int mode = 0;  // 0 none, 2 swiglu (y is [m][n / 2] bfloat16)
 };
 
+// Once per device and kernel variant: the shared-memory limit of the kernel is raised and, for
+// the variant that runs pairs of blocks, the number of pairs the device runs at a time is
+// asked. Neither allocates. Returns 0 or an error; *pairs receives the number of pairs.
 template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR = false>
-int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m, int n,
-              int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream, int narrow_bn = BN) {
-  constexpr int BNT = WIDE ? 2 * BN : BN;
-  constexpr int BNW = PAIR ? BN : BNT;
-  constexpr int BMT = PAIR ? 2 * BM : BM;
+int configure_tc(int* pairs = nullptr) {
   constexpr int smem_max = kSmemBudget + sizeof(Barriers) + 1024;
   constexpr int threads = WIDE ? 384 : 192;
   static_assert(smem_max <= 227 * 1024, "ring does not fit");
-  const int chunks = (k + kChunk - 1) / kChunk;
-  const int bn = WIDE ? BNT : narrow_bn;
-  const RingShape ring = ring_shape(A_ROWS, WIDE ? BNW : bn);
-  const int smem = ring.ring_bytes + static_cast<int>(sizeof(Barriers)) + 1024;
+  static bool configured[kMaxDevices] = {false};
+  static int max_pairs[kMaxDevices] = {0};  // pairs that the device runs at the same time
+  const int dev = current_device();
   auto kernel = gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE, PAIR>;
-  static bool configured = false;
-  static int max_pairs = 0;  // pairs that the device runs at the same time
-  if (!configured) {
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
     if (e != cudaSuccess) {
       bw::set_error("linear (tcgen05): cannot raise shared memory: %s", cudaGetErrorString(e));
       return static_cast<int>(e);
     }
     if (PAIR) {
+      constexpr int BNW = BN;
+      const RingShape ring = ring_shape(A_ROWS, BNW);
       cudaLaunchConfig_t probe = {};
       probe.gridDim = dim3(2 * (sm_count_of_device() / 2));
       probe.blockDim = dim3(threads);
-      probe.dynamicSmemBytes = smem;
+      probe.dynamicSmemBytes = ring.ring_bytes + static_cast<int>(sizeof(Barriers)) + 1024;
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
       probe.attrs = attr;
       probe.numAttrs = 1;
-      e = cudaOccupancyMaxActiveClusters(&max_pairs, kernel, &probe);
-      if (e != cudaSuccess || max_pairs <= 0) {
+      e = cudaOccupancyMaxActiveClusters(&max_pairs[dev], kernel, &probe);
+      if (e != cudaSuccess || max_pairs[dev] <= 0) {
         bw::set_error("linear (tcgen05): the device offers no cluster of two blocks for this kernel: %s",
                       cudaGetErrorString(e));
         cudaGetLastError();
         return e != cudaSuccess ? static_cast<int>(e) : -1;
       }
     }
-    configured = true;
+    configured[dev] = true;
   }
+  if (pairs) *pairs = max_pairs[dev];
+  return 0;
+}
+
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR = false>
+int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, const float* residual, int m, int n,
+              int k, int* error_word, float* partials, const Fused& fused, cudaStream_t stream, int narrow_bn = BN) {
+  constexpr int BNT = WIDE ? 2 * BN : BN;
+  constexpr int BNW = PAIR ? BN : BNT;
+  constexpr int BMT = PAIR ? 2 * BM : BM;
+  constexpr int threads = WIDE ? 384 : 192;
+  const int chunks = (k + kChunk - 1) / kChunk;
+  const int bn = WIDE ? BNT : narrow_bn;
+  const RingShape ring = ring_shape(A_ROWS, WIDE ? BNW : bn);
+  const int smem = ring.ring_bytes + static_cast<int>(sizeof(Barriers)) + 1024;
+  auto kernel = gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE, PAIR>;
+  int max_pairs = 0;
+  if (const int rc = configure_tc<SPLIT, A_ROWS, EPI, WIDE, PAIR>(&max_pairs)) return rc;
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, x, m, k, A_ROWS) || !make_map(&map_w, w, n, k, WIDE ? BNW : bn)) {
     bw::set_error("linear (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
@@ -955,16 +953,24 @@ int launch_tc_rows(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int 
   return launch_tc<false, 128, EPI, true>(x, w, y, y_is_f32, residual, m, n, k, error_word, nullptr, fused, stream);
 }
 
-int ensure_error_word() {
-  if (!g_error_flag) {
-    cudaError_t e = cudaMalloc(&g_error_flag, sizeof(int));
-    if (e != cudaSuccess) {
-      bw::set_error("linear (tcgen05): cannot allocate the error word: %s", cudaGetErrorString(e));
-      return static_cast<int>(e);
-    }
-    cudaMemset(g_error_flag, 0, sizeof(int));
-  }
-  return 0;
+// Every kernel variant that launch_tc_rows<EPI> can choose, configured for the current device.
+template <int EPI>
+int configure_reachable() {
+  int rc = 0;
+#define BW_CONF(...) if (!rc) rc = configure_tc<__VA_ARGS__>()
+#define BW_CONF_ROWS(SPLIT_, EPI_, WIDE_) \
+  BW_CONF(SPLIT_, 16, EPI_, WIDE_);      \
+  BW_CONF(SPLIT_, 32, EPI_, WIDE_);      \
+  BW_CONF(SPLIT_, 64, EPI_, WIDE_);      \
+  BW_CONF(SPLIT_, 128, EPI_, WIDE_)
+  BW_CONF_ROWS(true, 0, true);
+  BW_CONF_ROWS(true, 0, false);
+  BW_CONF_ROWS(false, EPI, true);
+  BW_CONF_ROWS(false, EPI, false);
+  BW_CONF(false, 128, EPI, true, true);
+#undef BW_CONF_ROWS
+#undef BW_CONF
+  return rc;
 }
 
 }  // namespace
@@ -979,10 +985,11 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
     return -1;
   }
   if (rows_path_takes(m, n, k, 0, x, w)) return bw_bf16_linear_rows(x, w, y, y_is_f32 ? 2 : 0, residual, m, n, k, stream);
-  if (const int rc = ensure_error_word()) return rc;
+  int* word = bw::failure_word();
+  if (!word) return -1;
   const Fused none;
-  if (y_is_f32) return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, g_error_flag, partials, none, stream);
-  return launch_tc_rows<0>(x, w, y, 0, nullptr, m, n, k, g_error_flag, partials, none, stream);
+  if (y_is_f32) return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, word, partials, none, stream);
+  return launch_tc_rows<0>(x, w, y, 0, nullptr, m, n, k, word, partials, none, stream);
 }
 
 // h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows
@@ -995,10 +1002,11 @@ BW_API int bw_bf16_linear_tc_swiglu(const __nv_bfloat16* x, const __nv_bfloat16*
     return -1;
   }
   if (rows_path_takes(m, n, k, 1, x, w)) return bw_bf16_linear_rows(x, w, h, 1, nullptr, m, n, k, stream);
-  if (const int rc = ensure_error_word()) return rc;
+  int* word = bw::failure_word();
+  if (!word) return -1;
   Fused f;
   f.mode = 2;
-  return launch_tc_rows<1>(x, w, h, 0, nullptr, m, n, k, g_error_flag, partials, f, stream);
+  return launch_tc_rows<1>(x, w, h, 0, nullptr, m, n, k, word, partials, f, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1014,11 +1022,17 @@ namespace {
 static __device__ __align__(256) float g_noalloc_scratch[BW_NOALLOC_MAX_SCRATCH_FLOATS];
 static __device__ __align__(256) int g_noalloc_error[64];
 
-constexpr int kMaxDevices = 64;
 float* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
 int* g_noalloc_error_ptr[kMaxDevices] = {nullptr};
 
 }  // namespace
+
+// Floats of the library's scratch array that a product of this shape uses: chunks of 512 along
+// k times m times n when the product is split along k, else 0.
+BW_API long long bw_bf16_linear_noalloc_scratch_floats(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0 || !bw_bf16_linear_tc_splits(m, n, k)) return 0;
+  return static_cast<long long>((k + kChunk - 1) / kChunk) * m * n;
+}
 
 BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,
                                   const float* residual, int m, int n, int k, cudaStream_t stream) {
@@ -1035,9 +1049,8 @@ BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w
     bw::set_error("linear (no allocation): a residual needs a float32 output");
     return -1;
   }
-  const int chunks = (k + kChunk - 1) / kChunk;
-  const bool split = bw_bf16_linear_tc_splits(m, n, k) != 0;
-  const long long need = split ? static_cast<long long>(chunks) * m * n : 0;
+  const long long need = bw_bf16_linear_noalloc_scratch_floats(m, n, k);
+  const bool split = need > 0;
   if (need > BW_NOALLOC_MAX_SCRATCH_FLOATS) {
     bw::set_error("linear (no allocation): [%d x %d] x [%d x %d] needs %lld floats of scratch, the library holds %d",
                   m, k, n, k, need, BW_NOALLOC_MAX_SCRATCH_FLOATS);
@@ -1059,12 +1072,15 @@ BW_API int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w
       bw::set_error("linear (no allocation): set-up on device %d failed: %s", dev, cudaGetErrorString(e));
       return static_cast<int>(e);
     }
+    // every kernel variant that a later call may pick gets its shared-memory limit now, so that
+    // no later call has set-up left to do, whatever its shape
+    if (const int rc = configure_reachable<0>()) return rc;
+    if (const int rc = configure_reachable<2>()) return rc;
     g_noalloc_error_ptr[dev] = ep;  // the array is zero when the library is loaded; kernels only ever set word 0
     g_noalloc_scratch_ptr[dev] = sp;
   }
   // Nothing in the scratch has to start at zero: every chunk sum that the second kernel reads
-  // is written by the first one in this same call. The launcher raises the kernel's
-  // shared-memory limit at its first use (no allocation either).
+  // is written by the first one in this same call.
   float* scratch = split ? g_noalloc_scratch_ptr[dev] : nullptr;
   if (y_is_f32)
     return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, g_noalloc_error_ptr[dev], scratch, Fused(), stream);

@@ -78,6 +78,41 @@ inline cudaError_t launch_pdl_cluster2(void (*kernel)(KArgs...), dim3 grid, dim3
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- bounded waits and the failure word --------------------------------------------------
+// No wait in these libraries is endless. A thread that polls an mbarrier gives up after
+// kSpinLimit polls (about a second); it then raises a word, the kernel drains and returns, and
+// its outputs are worthless. The word the host reads is one int of device memory per library:
+// the caller's (bw_set_failure_word) or, if none was given, one the library allocates at first
+// use. bw_device_failure() reads and clears it.
+constexpr uint32_t kSpinLimit = 20000000u;
+
+// Polls phase `parity` of the barrier at most `limit` times. False when the limit ran out, or
+// when `gave_up` was already raised (by another thread of the block when it points into shared
+// memory, by any thread of the launch when it points at the failure word itself); raises
+// `gave_up` when it gives up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* gave_up,
+                                                  uint32_t limit = kSpinLimit) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(bar));
+  for (uint32_t spin = 0; spin < limit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && *gave_up) return false;
+  }
+  *gave_up = 1;
+  return false;
+}
+
+// The library's failure word (device memory), allocated at first use unless the caller gave
+// one; null with the error text set when that allocation failed.
+int* failure_word();
+
 // exp(x) written only with IEEE multiply, add and fused multiply-add, each rounded to
 // nearest, so that the same sequence on a CPU gives the same bits. The reference calls
 // libm's expf (src/kernels.cpp:296,326; src/engine.cpp:56); libm is not reproducible

@@ -18,10 +18,16 @@
 extern "C" {
 #endif
 
-// Largest scratch the entry point can serve, in floats: ceil(k / 2048) * m * n must not exceed
-// it for a product that is split along k (few rows, few output columns, k > 2048).  16 MiB of
-// device memory per GPU that loads the library, held until the process exits.
+// Largest scratch the entry point can serve, in floats.  A product that the library splits
+// along k (at most 128 rows, more than one chunk of 512 along k, too few output columns to
+// occupy the GPU otherwise) uses ceil(k / 512) * m * n floats of it; other products use none.
+// bw_bf16_linear_noalloc_scratch_floats tells for a shape.  16 MiB of device memory per GPU
+// that loads the library, held until the process exits.
 #define BW_NOALLOC_MAX_SCRATCH_FLOATS (4 * 1024 * 1024)
+
+// Floats of scratch that a product of this shape uses (0 when it is not split along k); the
+// entry point refuses a product that needs more than BW_NOALLOC_MAX_SCRATCH_FLOATS.
+long long bw_bf16_linear_noalloc_scratch_floats(int m, int n, int k);
 
 // y[m][n] = sum_k x[m][k] * w[n][k] (+ residual[m][n]) in bfloat16 with float32 accumulation,
 // the same kernels and the same summation order as bw_bf16_linear, so the same bits.
@@ -32,9 +38,10 @@ extern "C" {
 // supported or needs more scratch than BW_NOALLOC_MAX_SCRATCH_FLOATS; a CUDA error code
 // otherwise.  It calls neither cudaMalloc nor cudaFree nor any routine that allocates.
 //
-// The first call on a device looks up the device address of the library's scratch array
-// (cudaGetSymbolAddress) and raises the kernels' shared-memory limit; make that first call
-// outside any stream capture.  All calls share the one scratch array: two calls whose
+// The first call on a device, with that device current, does the set-up for that device: it
+// looks up the device address of the library's scratch array (cudaGetSymbolAddress) and raises
+// the shared-memory limit of every kernel variant that any later call may choose, whatever
+// its shape.  Make that first call outside any stream capture.  All calls share the one scratch array: two calls whose
 // kernels may run at the same time (different streams, or graphs replayed concurrently) race
 // on it and give wrong results; calls on one stream are safe.
 int bw_bf16_linear_noalloc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32,

@@ -18,6 +18,77 @@ void set_error(const char* fmt, ...) {
 BW_API const char* bw_last_error() { return bw::g_error; }
 
 // ---------------------------------------------------------------------------------------
+// The failure word (see bw_common.cuh).
+namespace bw {
+static int* g_failure_word = nullptr;
+static bool g_failure_word_owned = false;
+int* failure_word() {
+  if (!g_failure_word) {
+    cudaError_t e = cudaMalloc(&g_failure_word, sizeof(int));
+    if (e != cudaSuccess) {
+      g_failure_word = nullptr;
+      set_error("cannot allocate the failure word: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cudaMemset(g_failure_word, 0, sizeof(int));
+    g_failure_word_owned = true;
+  }
+  return g_failure_word;
+}
+}  // namespace bw
+
+// The caller's word of device memory (an int that is zero) for this library's kernels to raise
+// when a bounded wait runs out; several libraries may share one word. Null: back to a word of
+// the library's own.
+BW_API void bw_set_failure_word(int* word) {
+  if (bw::g_failure_word_owned && bw::g_failure_word) cudaFree(bw::g_failure_word);
+  bw::g_failure_word = word;
+  bw::g_failure_word_owned = false;
+}
+
+// Reads and clears the failure word: 1 (once) when a kernel gave up a bounded wait since the
+// last call. A copy of four bytes that waits for the device.
+BW_API int bw_device_failure() {
+  if (!bw::g_failure_word) return 0;
+  int v = 0;
+  if (cudaMemcpy(&v, bw::g_failure_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+  if (v) cudaMemset(bw::g_failure_word, 0, sizeof(int));
+  return v != 0;
+}
+
+// A check of the machinery above that needs no fault: one warp waits, with the helper that
+// every kernel uses, for a barrier on which nothing ever arrives, gives up after `polls` polls,
+// raises the failure word as the kernels do and returns. result[0] becomes 1 when the wait
+// reported success (it must not), 2 when it gave up.
+__global__ void bounded_wait_selftest_kernel(uint32_t polls, int* failure, int* result) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t gave_up;
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&bar))), "r"(1));
+    gave_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const bool ok = bw::mbar_wait_bounded(&bar, 0, &gave_up, polls);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (gave_up) atomicExch(failure, 1);
+    result[0] = ok ? 1 : 2;
+  }
+}
+
+BW_API int bw_selftest_bounded_wait(unsigned polls, int* result, cudaStream_t stream) {
+  if (polls > 1000000u) {
+    bw::set_error("bounded-wait self-test: %u polls is more than a test needs (at most 1000000)", polls);
+    return -1;
+  }
+  int* word = bw::failure_word();
+  if (!word) return -1;
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(polls, word, result);
+  return bw::launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
 // Embedding: x[r][:] = E[token_r][:], widened to float (src/model.cpp:233-239,274).
 
 template <typename T>

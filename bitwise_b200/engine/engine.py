@@ -220,7 +220,16 @@ class Engine:
                 ops.fingerprint_rows(logits, self._s_d[:c], self.storage.fingerprints)
             self._tok_host[:c].copy_(self._tok_dev[:c], non_blocking=True)
             if torch.device(self.model.device).type == "cuda":
+                # the word that a kernel raises when it gave up a bounded wait rides along with
+                # the tokens: a step whose kernels did not finish their work must not be used
+                poll = getattr(ops, "failure_poll", None)
+                if poll is not None:
+                    poll()
                 torch.cuda.current_stream().synchronize()
+                if poll is not None and ops.failure_seen():
+                    from ..kernels.ops import DeviceFailure
+                    raise DeviceFailure("a kernel gave up a bounded wait; the results of this step and of the "
+                                        "steps since the last sampled token are not valid")
             self.d2h_bytes = c * 4
         self.stats.forward_seconds += time.perf_counter() - t0
         toks = self._tok_host[:c].tolist() if c else []

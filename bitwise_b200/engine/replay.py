@@ -59,7 +59,12 @@ def replay(model: Model, lines: IO[str], out_dir: str, max_tokens: int, page_siz
         if entries:
             logits = stepper.run(entries)
             if logits is not None:
+                poll = getattr(model.ops, "failure_poll", None)
+                if poll is not None:
+                    poll()
                 arr = logits.detach().to(torch.float32).cpu().numpy()
+                if poll is not None and model.ops.failure_seen():
+                    raise RuntimeError(f"step {step}: a kernel gave up a bounded wait; its logits are not written")
                 arr.astype("<f4").tofile(os.path.join(out_dir, f"{step}.f32"))
         for rid in rec.get("end", []):
             stepper.finish(rid)

@@ -26,6 +26,10 @@ class KernelError(RuntimeError):
     pass
 
 
+class DeviceFailure(KernelError):
+    """A kernel gave up a bounded wait: what the device computed since the last check is worthless."""
+
+
 def _p(t: Optional[torch.Tensor]):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
@@ -79,6 +83,12 @@ class KernelOps:
         if self.kind == "bf16":
             self.lib.bw_bf16_linear_scratch_floats.restype = ctypes.c_longlong
             self._split_rows = int(self.lib.bw_bf16_linear_split_rows())
+        # One word of device memory that every kernel of this object's libraries raises when a
+        # bounded wait runs out, and its pinned mirror on the host (filled by failure_poll).
+        self._failure_word: Optional[torch.Tensor] = None
+        self._failure_host: Optional[torch.Tensor] = None
+        if torch.cuda.is_available():
+            self._failure_words()  # before any kernel runs: captured graphs keep the word's address
 
     # -- plumbing ----------------------------------------------------------------------
     def _stream(self):
@@ -277,17 +287,49 @@ class KernelOps:
             return 0
         return int(self._attention_lib(head_dim).bw_bf16_attention_stream_mode(_c_int(int(mode))))
 
-    def device_failure(self) -> bool:
-        """True (once) when a kernel gave up a bounded wait since the last call.  This reads a
-        word from the device, so callers ask now and then, not every step."""
-        if self.kind != "bf16":
+    def _failure_words(self):
+        if self._failure_word is None:
+            dev = torch.device("cuda", self._device_index())
+            self._failure_word = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._failure_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+            for lib in [self.lib] + list(self._attn_libs.values()):
+                lib.bw_set_failure_word(_p(self._failure_word))
+        return self._failure_word, self._failure_host
+
+    def failure_poll(self) -> None:
+        """Enqueue a copy of the failure word to the host on the current stream (four bytes,
+        asynchronous).  ``failure_seen`` reads the copy once the stream has been waited for:
+        callers that wait for the device anyway (for a step's tokens) learn of a failure
+        without a wait of their own."""
+        word, host = self._failure_words()
+        host.copy_(word, non_blocking=True)
+
+    def failure_seen(self) -> bool:
+        """True (once) when the last ``failure_poll`` whose copy has arrived saw the word raised."""
+        if self._failure_host is None or int(self._failure_host[0]) == 0:
             return False
-        bad = bool(self.lib.bw_bf16_linear_tc_failed())
-        bad = bool(self.lib.bw_bf16_linear_rows_failed()) or bad
-        for lib in self._attn_libs.values():
-            bad = bool(lib.bw_bf16_attention_tc_failed()) or bad
-            bad = bool(lib.bw_bf16_attention_stream_failed()) or bad
+        self._failure_host[0] = 0
+        self._failure_word.zero_()
+        return True
+
+    def device_failure(self) -> bool:
+        """True (once) when a kernel gave up a bounded wait since the last call.  This waits
+        for the device and reads a word from it; steps use failure_poll / failure_seen."""
+        word, _ = self._failure_words()
+        bad = bool(int(word.item()))
+        if bad:
+            word.zero_()
         return bad
+
+    def selftest_bounded_wait(self, polls: int = 4096) -> int:
+        """Launch the check kernel of the bounded waits: one warp waits with the kernels' own
+        helper for a barrier on which nothing arrives, gives up after ``polls`` polls and
+        raises the failure word.  Returns 2 when the wait gave up (as it must), 1 when it
+        reported success."""
+        self._failure_words()
+        out = torch.zeros(1, dtype=torch.int32, device=self._failure_word.device)
+        self._call("bw_selftest_bounded_wait", ctypes.c_uint(polls), _p(out), self._stream())
+        return int(out.item())
 
     def attention_tile_rows(self, heads: int, kv_heads: int) -> int:
         """Query rows per attention tile: the bfloat16 kernel stacks the heads of a group
@@ -316,6 +358,8 @@ class KernelOps:
             except OSError as e:
                 raise KernelError(f"cannot load the attention library {path}: {e}") from None
             lib.bw_last_error.restype = ctypes.c_char_p
+            if self._failure_word is not None:
+                lib.bw_set_failure_word(_p(self._failure_word))
             self._attn_libs[head_dim] = lib
         return lib
 

@@ -192,3 +192,22 @@ def test_parts_alone(dtype, tiny_folders):
     logits = dec.head.forward(ctx, xf)
     hn = rb(P.rmsnorm(xf0[36:37], w["model.norm.weight"], c.rms_norm_eps))
     close(logits, P.linear(hn, rb(w["lm_head.weight"])), "head")
+
+
+def test_engine_stops_on_a_raised_failure_word(tiny_folders):
+    """The engine reads the kernels' failure word with every step's tokens: a step that follows
+    a bounded wait that ran out raises instead of handing out tokens; after that the engine's
+    device state is usable and generation gives the right tokens again."""
+    from bitwise_b200 import Engine, EngineConfig, SamplingParams
+    from bitwise_b200.kernels.ops import DeviceFailure
+    model = _model(tiny_folders["tiny_a"], "bfloat16")
+    sp = SamplingParams(0.0, 0, 6, True)
+    prompt = tiny_tokens("tiny_a", 12, salt=91)
+    want = Engine(model, EngineConfig(num_blocks=8)).generate([prompt], sp)
+    eng = Engine(model, EngineConfig(num_blocks=8))
+    eng.add_request(prompt, sp)
+    assert model.ops.selftest_bounded_wait(polls=2000) == 2   # a wait ran out somewhere on the device
+    with pytest.raises(DeviceFailure):
+        eng.step()
+    assert not model.ops.device_failure()                     # read and cleared by the engine
+    assert Engine(model, EngineConfig(num_blocks=8)).generate([prompt], sp) == want

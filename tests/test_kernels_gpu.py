@@ -647,3 +647,32 @@ def test_bf16_rope_and_cache_write():
     for r in range(3):
         blk, slot = table[seq[r], pos[r] // page], pos[r] % page
         assert (np.abs(kc[blk, :, slot] - want_k[r]) <= 2.0 ** -7 * np.abs(want_k[r]) + 1e-6).all()
+
+
+def test_a_bounded_wait_that_runs_out_raises_the_failure_word_once():
+    """No wait in the kernels is endless: a thread that polls a barrier gives up after a limit,
+    raises the library's failure word, and the kernel returns.  The check kernel runs the
+    kernels' own wait helper on a barrier on which nothing ever arrives, with a limit of a few
+    thousand polls: it must come back, the word must read raised exactly once, and the device
+    must go on computing right results (nothing faulted, nothing hung)."""
+    ops = _ops("bfloat16")
+    assert not ops.device_failure()
+    assert ops.selftest_bounded_wait(polls=5000) == 2       # the wait gave up and said so
+    assert ops.device_failure() is True                      # raised ...
+    assert ops.device_failure() is False                     # ... once
+    # through the asynchronous route that the engine uses
+    assert ops.selftest_bounded_wait(polls=3000) == 2
+    ops.failure_poll()
+    torch.cuda.synchronize()
+    assert ops.failure_seen() is True and ops.failure_seen() is False
+    ops.failure_poll()
+    torch.cuda.synchronize()
+    assert ops.failure_seen() is False
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(8, 1024, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(256, 1024, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    y = torch.empty(8, 256, device=DEV)
+    ops.linear(x, w, y)
+    ref = x.double() @ w.double().t()
+    assert float((y.double() - ref).abs().max()) <= 1e-3 * float(ref.abs().max())
+    assert not ops.device_failure()

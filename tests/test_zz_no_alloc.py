@@ -46,6 +46,9 @@ def _call(fn, x, w, y, residual, stream):
 def test_no_alloc_entry_gives_the_bits_of_the_ordinary_one_twice_in_a_row(m, n, k, uses_scratch):
     lib, fn, ops = _lib_and_ops()
     assert bool(lib.bw_bf16_linear_tc_splits(m, n, k)) == uses_scratch
+    # what the header promises about the scratch: chunks of 512 along k, times m, times n
+    lib.bw_bf16_linear_noalloc_scratch_floats.restype = ctypes.c_longlong
+    assert lib.bw_bf16_linear_noalloc_scratch_floats(m, n, k) == (((k + 511) // 512) * m * n if uses_scratch else 0)
     g = torch.Generator(device="cuda:0").manual_seed(m + n + k)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     for call in range(2):  # the second call finds the first call's chunk sums in the scratch
