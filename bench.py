@@ -38,7 +38,11 @@ sys.path.insert(0, HERE)
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
-REFERENCE_DECODE_TOKS = 7.26  # tkran2/bitwise README.md:142, SmolLM2-1.7B single stream on a 4-core AVX-512 VM
+# The like-for-like baseline: tkran2/bitwise's Runner::forward on the SmolLM2-1.7B shape, 8 threads on
+# this image's CPU, 2,048-token contexts, as BASELINE.md records it (decode tokens per second by batch).
+# The reference publishes no figure for this batch and context (its README has 7.26 tok/s single stream).
+BASELINE_DECODE_TOKS = {("smollm2-1.7b", 2048, 1): 10.7, ("smollm2-1.7b", 2048, 8): 29.9, ("smollm2-1.7b", 2048, 64): 35.4}
+REFERENCE_SOURCE = "/root/reference"
 
 
 def fp32_simt_tflops():
@@ -246,10 +250,11 @@ def run_prefill(model, tokens, reps, warmup, page):
     return sorted(times)[len(times) // 2]
 
 
-def run_e2e(model, batch, ctx, steps, warmup, page):
+def run_e2e(model, batch, ctx, steps, warmup, page, fingerprint=True):
     """Through Engine.step(): prompts of ctx-1 tokens are prefilled by the engine itself, then
     `steps` decode steps are timed by the host clock, each with its host-to-device copy of the
-    step's inputs and the device-to-host read of the sampled tokens."""
+    step's inputs and the device-to-host read of the sampled tokens.  ``fingerprint``: the
+    engine's default, a hash of every sampled row's logits chained on the device."""
     import numpy as np
     import torch
     from bitwise_b200 import Engine, EngineConfig, SamplingParams
@@ -257,7 +262,8 @@ def run_e2e(model, batch, ctx, steps, warmup, page):
     total = ctx + warmup + steps + batch + 16
     pages_per = (total + page - 1) // page
     eng = Engine(model, EngineConfig(num_blocks=pages_per * batch, block_size=page, max_batched_tokens=2048,
-                                     max_num_seqs=batch, fingerprint_logits=False, max_model_len=pages_per * page))
+                                     max_num_seqs=batch, fingerprint_logits=fingerprint,
+                                     max_model_len=pages_per * page))
     rng = np.random.default_rng(2)
     sp = SamplingParams(temperature=0.0, max_new_tokens=warmup + steps + batch + 8, ignore_eos=True)
     for b in range(batch):
@@ -304,14 +310,12 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "tkran2/bitwise has neither setup.py nor pyproject.toml, so pip cannot install it "
-                          "(a CMake C++ project, CPU only)"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        print(json.dumps(reference_arm(args)))
+        return 0
     warmup = max(3, args.warmup)
 
     import torch
@@ -337,7 +341,7 @@ def main():
         "metric": f"decode tok/s at batch {args.batch}, {args.ctx:,}-token context ({title})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(value / REFERENCE_DECODE_TOKS, 1), "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "vs_baseline": baseline_ratio(args, value), "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
         "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary",
         "impl": "ours",
         "config": {"model": title, "layers": full_layers, "layers_run": args.layers,
@@ -346,7 +350,7 @@ def main():
                    "tied_embeddings": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": args.ctx,
                    "page_size": args.page, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights + cache read per step exceed 126 MB)",
-                   "peaks": "of " + pk["source"]},
+                   "peaks": "of " + pk["source"], "baseline": BASELINE_NOTE},
         "clocks": clocks.summary(),
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -367,8 +371,11 @@ def main():
             pts[f"decode_b{b}"] = round(b / (pm / 1e3), 1)
             pts[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, args.ctx, elt) / (pm / 1e3) / 1e9 / pk["hbm_gbs"], 4)
         line["points"] = pts
-        e, h2d, d2h = run_e2e(model, args.batch, args.ctx, args.steps, warmup, args.page)
-        line["e2e"] = {"value": round(e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        e, h2d, d2h = run_e2e(model, args.batch, args.ctx, args.steps, warmup, args.page, fingerprint=True)
+        e_plain, _, _ = run_e2e(model, args.batch, args.ctx, args.steps, warmup, args.page, fingerprint=False)
+        line["e2e"] = {"value": round(e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "settings": "Engine defaults (fingerprint_logits on)",
+                       "value_without_fingerprint": round(e_plain, 1)}
     if not args.skip_fp32 and args.dtype == "bfloat16" and not args.skip_points:
         # the true 32-bit path of the same shape (no reduced-precision matrix mode anywhere)
         del model
@@ -386,6 +393,104 @@ def main():
         line["fp32"] = f32
     print(json.dumps(line))
     return 0
+
+
+BASELINE_NOTE = ("vs_baseline divides by BASELINE.md's figure for the same shape, batch and context: the reference's "
+                 "Runner::forward on this image's CPU, 8 threads")
+
+
+def baseline_ratio(args, value):
+    base = BASELINE_DECODE_TOKS.get((args.shape, args.ctx, args.batch))
+    if base is None or args.layers != SHAPES[args.shape][1]:
+        return None
+    return round(value / base, 1)
+
+
+def _cpu_flags():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("flags"):
+                return set(line.split(":", 1)[1].split())
+    except OSError:
+        pass
+    return set()
+
+
+def reference_arm(args):
+    """tkran2/bitwise itself, unmodified, on the same shape, batch and context.  It is a CMake
+    C++ project for the CPU without a Python package to install, so its sources are copied
+    beside the harness baseline/ref_bench.cpp into baseline/_ref/ and compiled there with its own
+    flags (CMakeLists.txt:5-18: Release, -ffp-contract=off -fno-fast-math, AVX-512 where the CPU
+    has it); the harness drives Model::random, Runner::forward and argmax_row."""
+    import shutil
+    unavailable = lambda why: {"impl": "reference", "unavailable": why}
+    ref = os.path.join(HERE, "baseline", "_ref")
+    src = os.path.join(ref, "src")
+    names = ("kernels.cpp", "model.cpp", "engine.cpp", "block_manager.cpp")
+    if not all(os.path.isfile(os.path.join(src, f)) for f in names):
+        origin = os.path.join(REFERENCE_SOURCE, "src")
+        if not os.path.isdir(origin):
+            return unavailable("the reference's sources are neither in baseline/_ref/src nor at " + REFERENCE_SOURCE)
+        os.makedirs(ref, exist_ok=True)
+        shutil.copytree(origin, src, dirs_exist_ok=True)
+    cxx = shutil.which("g++") or shutil.which("c++")
+    flags = _cpu_flags()
+    avx = {"avx512f", "avx512bw", "avx512vl", "fma"} <= flags
+    exe = os.path.join(ref, "ref_bench_avx512" if avx else "ref_bench_scalar")
+    harness = os.path.join(HERE, "baseline", "ref_bench.cpp")
+    newest = max(os.path.getmtime(os.path.join(src, f)) for f in os.listdir(src))
+    if not os.path.isfile(exe) or os.path.getmtime(exe) < max(newest, os.path.getmtime(harness)):
+        if not cxx:
+            return unavailable("no C++ compiler on this machine (g++, c++) to build the reference with")
+        cmd = [cxx, "-std=c++20", "-O3", "-DNDEBUG", "-ffp-contract=off", "-fno-fast-math", "-pthread"]
+        cmd += ["-mavx512f", "-mavx512bw", "-mavx512vl", "-mfma"] if avx else []
+        cmd += ["-I", src, harness, *[os.path.join(src, f) for f in names], "-o", exe]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            return unavailable("the reference does not compile here: " + r.stderr.strip().split("\n")[-1][:200])
+    title, full_layers, kw, shape_ctx = SHAPES[args.shape]
+    layers = args.layers or full_layers
+    ctx = args.ctx or shape_ctx
+    warmup = max(3, args.warmup)
+    threads = min(os.cpu_count() or 8, 64)
+    points = [] if args.skip_points else [b for b in (1, 64) if b != args.batch]
+    cmd = [exe, layers, kw["hidden_size"], kw["num_attention_heads"], kw["num_key_value_heads"], kw["head_dim"],
+           kw["intermediate_size"], kw["vocab_size"], kw["rope_theta"], threads, ctx, args.batch, args.steps, warmup,
+           0 if args.skip_prefill else 2048, *points]
+    try:
+        r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=3000)
+    except subprocess.TimeoutExpired:
+        return unavailable("the reference did not finish the workload within 50 minutes on this machine's CPU")
+    if r.returncode != 0:
+        return unavailable(f"the reference's harness ended with code {r.returncode}: {r.stderr.strip()[-200:]}")
+    out = json.loads(r.stdout.strip().split("\n")[-1])
+    ms = out["ms_per_step"]
+    value = args.batch / (ms / 1e3)
+    line = {
+        "metric": f"decode tok/s at batch {args.batch}, {ctx:,}-token context ({title})",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights, fp32 compute (the reference's serving mode)",
+        "data": "synthetic: the reference's Model::random weights, zero-filled cache, fixed token ids",
+        "impl": "reference",
+        "config": {"model": title, "layers": full_layers, "layers_run": layers, "hidden": kw["hidden_size"],
+                   "heads": kw["num_attention_heads"], "kv_heads": kw["num_key_value_heads"], "head_dim": kw["head_dim"],
+                   "intermediate": kw["intermediate_size"], "vocab": kw["vocab_size"], "global_batch": args.batch,
+                   "seq_len": ctx, "page_size": 16, "parallelism": f"CPU, {threads} threads",
+                   "build": "AVX-512" if avx else "portable scalar path (this CPU lacks AVX-512)",
+                   "api": "bw::Model::random, bw::Runner::forward, bw::argmax_row", "timing": "host clock"},
+        "clocks": {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["runs on the CPU"]},
+        "gpu_launches": 0,
+        "e2e": {"value": round(args.batch / (out["e2e_ms_per_step"] / 1e3), 2), "unit": "tokens/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "settings": "Runner::forward plus the reference's greedy sampler, host tokens in and out"},
+    }
+    if "prefill_ms" in out:
+        line["prefill"] = {"value": round(2048 / (out["prefill_ms"] / 1e3), 2), "tokens": 2048, "ms": out["prefill_ms"]}
+    pts = {f"decode_b{b}": round(b / (out[f"decode_b{b}_ms"] / 1e3), 2) for b in points if f"decode_b{b}_ms" in out}
+    if pts:
+        line["points"] = pts
+    return line
 
 
 def run_serve(model, title, args, pk):

@@ -228,36 +228,60 @@ BW_API int bw_sample_rows(const float* logits, int rows, int vocab, const float*
 // Logits fingerprint: the reference chains an FNV-style hash over the raw bits of every
 // sampled-from logits row (src/engine.cpp:18-29): for each 8-byte word h = (h ^ w) * prime,
 // trailing bytes one by one, then the splitmix64 finaliser.  The chain is serial by
-// definition; one thread per row walks it.  state[slot[r]] holds the running hash.
+// definition.  state[slot[r]] holds the running hash.
 __device__ __forceinline__ uint64_t mix64(uint64_t z) {
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
   return z ^ (z >> 31);
 }
 
-__global__ void fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab,
-                                        const int* __restrict__ slot, unsigned long long* __restrict__ state) {
+// One warp per row: the lanes fetch 32 consecutive words at a time (one coalesced read, the
+// next group already on its way) and every lane runs the same chain over them, taking word j
+// from lane j; no lane waits for memory inside the chain.
+__global__ void __launch_bounds__(32)
+fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab, const int* __restrict__ slot,
+                        unsigned long long* __restrict__ state) {
   bw::pdl_enter();
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = blockIdx.x, lane = threadIdx.x;
   if (r >= rows) return;
   const uint32_t* w = reinterpret_cast<const uint32_t*>(logits + static_cast<size_t>(r) * vocab);
   uint64_t h = state[slot[r]];
   const uint64_t prime = 1099511628211ull;
-  int i = 0;
-  for (; i + 2 <= vocab; i += 2) {
-    const uint64_t word = static_cast<uint64_t>(w[i]) | (static_cast<uint64_t>(w[i + 1]) << 32);
-    h = (h ^ word) * prime;
+  const int words = vocab / 2;  // whole 8-byte words
+  auto fetch = [&](int base) -> uint64_t {
+    const int i = base + lane;
+    if (i >= words) return 0;
+    const uint2 v = *reinterpret_cast<const uint2*>(w + 2 * i);  // rows of an even vocabulary start on 8 bytes
+    return static_cast<uint64_t>(v.x) | (static_cast<uint64_t>(v.y) << 32);
+  };
+  const bool aligned8 = (reinterpret_cast<uintptr_t>(w) & 7) == 0;
+  if (aligned8) {
+    uint64_t cur = fetch(0);
+    for (int base = 0; base < words; base += 32) {
+      const uint64_t nxt = fetch(base + 32);
+      const int count = min(32, words - base);
+      if (count == 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) h = (h ^ __shfl_sync(0xffffffffu, cur, j)) * prime;
+      } else {
+        for (int j = 0; j < count; ++j) h = (h ^ __shfl_sync(0xffffffffu, cur, j)) * prime;
+      }
+      cur = nxt;
+    }
+  } else {
+    for (int i = 0; i < words; ++i)
+      h = (h ^ (static_cast<uint64_t>(w[2 * i]) | (static_cast<uint64_t>(w[2 * i + 1]) << 32))) * prime;
   }
-  if (i < vocab) {
-    const uint32_t v = w[i];
+  if (vocab & 1) {
+    const uint32_t v = w[vocab - 1];
     for (int b = 0; b < 4; ++b) h = (h ^ ((v >> (8 * b)) & 0xffu)) * prime;
   }
-  state[slot[r]] = mix64(h);
+  if (lane == 0) state[slot[r]] = mix64(h);
 }
 
 BW_API int bw_fingerprint_rows(const float* logits, int rows, int vocab, const int* slot,
                                unsigned long long* state, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  bw::launch_pdl(fingerprint_rows_kernel, dim3((rows + 31) / 32), dim3(32), 0, stream, logits, rows, vocab, slot, state);
+  bw::launch_pdl(fingerprint_rows_kernel, dim3(rows), dim3(32), 0, stream, logits, rows, vocab, slot, state);
   return bw::launch_status();
 }

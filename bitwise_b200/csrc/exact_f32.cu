@@ -8,6 +8,8 @@
 //
 // No tensor cores here (tf32 is not float32). Explicit __f*_rn intrinsics keep the compiler
 // from contracting or reassociating anything.
+#include <cuda.h>
+
 #include "bw_common.cuh"
 
 namespace {
@@ -202,69 +204,119 @@ gemm_exact_big_kernel(const float* __restrict__ X, const float* __restrict__ W, 
 
 // ---------------------------------------------------------------------------------------
 // The same product for steps of few rows (decode steps, up to 16 rows), where the weights are
-// all that is read: one chain per output as above (a thread carries two rows of one column,
-// k ascending, fma after fma), but tiles of 16 columns, so that every SM streams weights (a
-// product with 2,048 columns is 128 blocks instead of 32), and the tiles of W and x come
-// through a ring of cp.async stages instead of a load, a barrier, the arithmetic and a
-// barrier in turn. Shared memory holds a stage as [k / 4][column or row][4 values]: a lane's
-// 16-byte read of its column meets no other lane's bank, the rows of x are broadcast.
-constexpr int kRowsBN = 16;      // columns per block
-constexpr int kRowsBK = 64;      // k per stage
-constexpr int kRowsStages = 6;
+// all that is read: one chain per output as above (a worker thread carries two rows of one
+// column, k ascending, fma after fma), but tiles of 16 columns, so that every SM streams
+// weights (a product with 2,048 columns is 128 blocks instead of 32), and the tiles of W and x
+// come through a ring of stages instead of a load, a barrier, the arithmetic and a barrier in
+// turn. A stage is 128 values of k: one TMA box of W ([4 k-tiles][16 columns][32 values], a
+// three-dimensional view of the row-major matrix) and one of x, written with the 128-byte
+// swizzle, so that a lane's 16-byte read of its own column meets no other lane's bank. What
+// lies outside the matrices arrives as zeros, and fma(0, 0, acc) = acc.
+//
+// The block's first kRowsBN * R / 2 threads carry the chains and do nothing else: with so few
+// warps on an SM every instruction's latency shows, and a thread that issued copies between
+// its multiply-adds would stretch the chain that the product's time hangs on. One more warp
+// requests the stages; the workers hand a stage back through a second barrier. Every wait is
+// bounded (bw_common.cuh).
+constexpr int kRowsBN = 16;       // columns per block
+constexpr int kRowsTileK = 32;    // values of k in a 128-byte line
+constexpr int kRowsTiles = 4;     // lines of k per stage
+constexpr int kRowsBK = kRowsTileK * kRowsTiles;
+constexpr int kRowsMaxStages = 16;  // stages of the ring at most (chosen by the host from the grid)
 
-__device__ __forceinline__ void cp_async16_f32(void* dst, const void* src, bool valid) {
-  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
-  const int bytes = valid ? 16 : 0;  // 0: zeros, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_expect(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// one box of the view (32 values, rows, k-tiles): rows from `row` on, k-tiles from `ktile` on
+__device__ __forceinline__ void tma_box3(void* dst, const CUtensorMap* map, int row, int ktile, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(ktile), "r"(smem_addr(bar))
+      : "memory");
 }
 
 template <int R>  // rows of the tile: 8 or 16
-__global__ void __launch_bounds__(kRowsBN * R / 2)
-gemm_exact_rows_kernel(const float* __restrict__ X, const float* __restrict__ W, float* Y, const float* residual, int M,
-                       int N, int K) {
-  constexpr int kThreads = kRowsBN * R / 2;
-  __shared__ __align__(16) float Ws[kRowsStages][kRowsBK / 4][kRowsBN][4];
-  __shared__ __align__(16) float Xs[kRowsStages][kRowsBK / 4][R][4];
-  const int tid = threadIdx.x;
-  const int col = tid % kRowsBN, rp = tid / kRowsBN;  // this thread's column and pair of rows
+__global__ void __launch_bounds__(kRowsBN * R / 2 + 32)
+gemm_exact_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, float* Y,
+                       const float* residual, int M, int N, int K, int stages, int* failure) {
+  const int kRowsStages = stages;  // stages of the ring, chosen by the host
+  constexpr int kWorkers = kRowsBN * R / 2;
+  constexpr int kWBytes = kRowsTiles * kRowsBN * 128, kXBytes = kRowsTiles * R * 128;
+  extern __shared__ __align__(1024) unsigned char rows_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rows_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* Ws = base;                          // [stages][4 k-tiles][16 columns][128 bytes]
+  unsigned char* Xs = base + kRowsStages * kWBytes;  // [stages][4 k-tiles][R rows][128 bytes]
+  uint64_t* full = reinterpret_cast<uint64_t*>(Xs + kRowsStages * kXBytes);
+  uint64_t* empty = full + kRowsStages;
+  volatile unsigned* gave_up = reinterpret_cast<volatile unsigned*>(failure);
+  const int tid = threadIdx.x, lane = tid & 31;
   const int n0 = blockIdx.x * kRowsBN;
   const int stages_total = (K + kRowsBK - 1) / kRowsBK;
-  auto load_stage = [&](int st) {
-    const int slot = st % kRowsStages, k0 = st * kRowsBK;
-    for (int idx = tid; idx < kRowsBN * (kRowsBK / 4); idx += kThreads) {
-      const int c = idx / (kRowsBK / 4), k4 = idx % (kRowsBK / 4);  // a thread walks k: 16 bytes after 16 bytes of a row
-      const int gn = n0 + c, gk = k0 + k4 * 4;
-      const bool ok = gn < N && gk < K;  // K is a multiple of 4
-      cp_async16_f32(&Ws[slot][k4][c][0], W + (ok ? static_cast<size_t>(gn) * K + gk : 0), ok);
+  if (tid == 0) {
+    for (int s2 = 0; s2 < kRowsStages; ++s2) {
+      bar_init(full + s2, 1);
+      bar_init(empty + s2, kWorkers / 32);
     }
-    for (int idx = tid; idx < R * (kRowsBK / 4); idx += kThreads) {
-      const int r = idx / (kRowsBK / 4), k4 = idx % (kRowsBK / 4);
-      const int gk = k0 + k4 * 4;
-      const bool ok = r < M && gk < K;
-      cp_async16_f32(&Xs[slot][k4][r][0], X + (ok ? static_cast<size_t>(r) * K + gk : 0), ok);
-    }
-  };
-  for (int st = 0; st < kRowsStages - 1; ++st) {
-    if (st < stages_total) load_stage(st);
-    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  __syncthreads();
+  if (tid >= kWorkers) {  // the requesting warp
+    if (lane == 0) {
+      for (int st = 0; st < stages_total; ++st) {
+        const int slot = st % kRowsStages;
+        if (st >= kRowsStages && !bw::mbar_wait_bounded(empty + slot, ((st / kRowsStages) - 1) & 1, gave_up)) break;
+        bar_expect(full + slot, kWBytes + kXBytes);
+        tma_box3(Ws + slot * kWBytes, &map_w, n0, st * kRowsTiles, full + slot);
+        tma_box3(Xs + slot * kXBytes, &map_x, 0, st * kRowsTiles, full + slot);
+      }
+    }
+    return;
+  }
+  const int col = tid % kRowsBN, rp = tid / kRowsBN;  // this worker's column and pair of rows
+  const int r0 = 2 * rp, r1 = 2 * rp + 1;
   float acc0 = 0.0f, acc1 = 0.0f;
   for (int st = 0; st < stages_total; ++st) {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(kRowsStages - 2));
-    __syncthreads();  // stage st has landed for every thread; the slot of stage st - 1 is free
-    if (st + kRowsStages - 1 < stages_total) load_stage(st + kRowsStages - 1);
-    asm volatile("cp.async.commit_group;\n" ::);
     const int slot = st % kRowsStages;
+    if (!bw::mbar_wait_bounded(full + slot, (st / kRowsStages) & 1, gave_up)) break;
+    const unsigned char* ws = Ws + slot * kWBytes + col * 128;
+    const unsigned char* xs = Xs + slot * kXBytes;
+    // The reads of a line of k (24 of 16 bytes) are issued a whole line ahead of the chain that
+    // uses them, so that the chain never waits for shared memory.
+    float4 w[8], a[8], b[8];
+    auto read_line = [&](int kt, float4 (&wl)[8], float4 (&al)[8], float4 (&bl)[8]) {
 #pragma unroll
-    for (int k4 = 0; k4 < kRowsBK / 4; ++k4) {
-      const float4 w = *reinterpret_cast<const float4*>(&Ws[slot][k4][col][0]);
-      const float4 a = *reinterpret_cast<const float4*>(&Xs[slot][k4][2 * rp][0]);
-      const float4 b = *reinterpret_cast<const float4*>(&Xs[slot][k4][2 * rp + 1][0]);
-      acc0 = __fmaf_rn(a.x, w.x, acc0), acc1 = __fmaf_rn(b.x, w.x, acc1);
-      acc0 = __fmaf_rn(a.y, w.y, acc0), acc1 = __fmaf_rn(b.y, w.y, acc1);
-      acc0 = __fmaf_rn(a.z, w.z, acc0), acc1 = __fmaf_rn(b.z, w.z, acc1);
-      acc0 = __fmaf_rn(a.w, w.w, acc0), acc1 = __fmaf_rn(b.w, w.w, acc1);
+      for (int q = 0; q < 8; ++q) {  // the 16-byte pieces of a line sit at piece ^ (row % 8)
+        wl[q] = *reinterpret_cast<const float4*>(ws + kt * (kRowsBN * 128) + ((q ^ (col & 7)) << 4));
+        al[q] = *reinterpret_cast<const float4*>(xs + kt * (R * 128) + r0 * 128 + ((q ^ (r0 & 7)) << 4));
+        bl[q] = *reinterpret_cast<const float4*>(xs + kt * (R * 128) + r1 * 128 + ((q ^ (r1 & 7)) << 4));
+      }
+    };
+    read_line(0, w, a, b);
+#pragma unroll
+    for (int kt = 0; kt < kRowsTiles; ++kt) {
+      float4 wn[8], an[8], bn[8];
+      if (kt + 1 < kRowsTiles) read_line(kt + 1, wn, an, bn);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        acc0 = __fmaf_rn(a[q].x, w[q].x, acc0), acc1 = __fmaf_rn(b[q].x, w[q].x, acc1);
+        acc0 = __fmaf_rn(a[q].y, w[q].y, acc0), acc1 = __fmaf_rn(b[q].y, w[q].y, acc1);
+        acc0 = __fmaf_rn(a[q].z, w[q].z, acc0), acc1 = __fmaf_rn(b[q].z, w[q].z, acc1);
+        acc0 = __fmaf_rn(a[q].w, w[q].w, acc0), acc1 = __fmaf_rn(b[q].w, w[q].w, acc1);
+      }
+      if (kt + 1 < kRowsTiles) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) w[q] = wn[q], a[q] = an[q], b[q] = bn[q];
+      }
     }
+    __syncwarp();
+    if (lane == 0) bar_arrive(empty + slot);  // this warp has read the stage
   }
   const int gn = n0 + col;
   if (gn >= N) return;
@@ -322,142 +374,524 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
 }
 
 // ---------------------------------------------------------------------------------------
-// Attention over the cache, one block per (row, head): scores s_j = dot16(q, K_j) * scale
-// with the global maximum, then in key order e_j = exp(s_j - max), sum += e_j,
-// acc[d] = fma(e_j, V_j[d], acc[d]); finally o[d] = acc[d] * (1 / sum)
-// (src/kernels.cpp:312-338,361-364). `window` > 0 limits the keys to the last `window`
-// positions. Every thread carries the running sum itself, so all hold the same value.
-constexpr int kAttnThreads = 128;
-constexpr int kAttnTileKeys = 64;  // keys per tile of values in shared memory
+// Attention over the cache (src/kernels.cpp:312-338,361-364). For a query at position p of a
+// sequence and a head h (key/value head g = h / (heads / kv_heads)):
+//   pass 1   s_j = dot16(q, K_j) * scale for the keys j = lo .. p, mx = max_j s_j
+//   pass 2   in key order: e_j = exp(s_j - mx); sum += e_j; acc[d] = fma(e_j, V_j[d], acc[d])
+//   out[d] = acc[d] * (1 / sum)
+// lo = max(0, p - window + 1) when window > 0, else 0. Which thread computes which score, and
+// how many queries share a block, is free: a score is one dot16, the maximum does not depend
+// on the order, and the chains of pass 2 (one per output element, plus the sum) are walked by
+// one thread each, in key order. Two forms:
+//   * tiles of up to 16 consecutive query rows of a sequence (prompt portions): a block per
+//     (tile, head) walks the keys twice in tiles that all its rows share; the scores are
+//     computed again in the second walk (the same instructions, so the same bits) instead of
+//     being kept, so that the context is not limited by shared memory;
+//   * single rows (decode steps): the scores of a row are spread over many blocks and stored,
+//     a second kernel streams the values through a ring in shared memory.
 
-template <bool STAGED>
-__global__ void __launch_bounds__(kAttnThreads)
-attention_exact_kernel(const float* __restrict__ qkv, int q_stride, const float* __restrict__ kcache,
-                       const float* __restrict__ vcache, const int* __restrict__ block_table,
-                       int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos,
-                       float* __restrict__ out, int out_stride, int heads, int kv_heads, int hd, int page,
-                       int window, float scale, int score_floats) {
+// 16 lane-wise chains of a dot product, kept apart: lane[i % 16] = fma(a[i], b[i], lane[i % 16])
+// for i ascending (src/kernels.cpp:86-100); bw::tree16 folds them.
+constexpr int kTileRows = 16;       // query rows of a tile
+constexpr int kTileThreads = 128;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  const int bytes = valid ? 16 : 0;  // 0: zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+
+template <int HD>
+struct TileGeometry {
+  static constexpr int KT = HD <= 64 ? 64 : 32;         // keys per tile
+  static constexpr int KPT = KT / 32;                   // keys per thread when scores are computed
+  static constexpr int KStride = HD + 4;                // floats per key row in shared memory: a lane's 16-byte
+                                                        // read of its key meets no other lane's bank
+  static constexpr int HDP = HD <= 16 ? 16 : HD <= 32 ? 32 : HD <= 64 ? 64 : HD <= 128 ? 128 : 256;
+  static constexpr int TD = HDP < kTileThreads ? HDP : kTileThreads;  // threads side by side along d in pass 2
+  static constexpr int DPT = HDP / TD;                  // output columns per thread
+  static constexpr int RG = kTileThreads / TD;          // groups of rows
+  static constexpr int RPT = kTileRows / RG;            // rows per thread
+  static constexpr int QFloats = kTileRows * HD;
+  static constexpr int KFloats = KT * KStride;
+  static constexpr int VFloats = KT * HD;
+  static constexpr int EFloats = KT * kTileRows;
+  static constexpr int SmemFloats = QFloats + 2 * KFloats + 2 * VFloats + EFloats + 2 * kTileRows;
+};
+
+// Scores of this thread's pairs (4 rows of its warp x KPT keys of its lane) against the tile in
+// shared memory: s[rr][c] = dot16(Q[4 w + rr], K[lane + 32 c]) * scale.
+template <int HD>
+__device__ __forceinline__ void tile_scores(const float* __restrict__ qs, const float* __restrict__ ks, int warp, int lane,
+                                            float scale, float (&s)[4][TileGeometry<HD>::KPT]) {
+  using G = TileGeometry<HD>;
+  float acc[4][G::KPT][16];
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+    for (int c = 0; c < G::KPT; ++c)
+#pragma unroll
+      for (int l = 0; l < 16; ++l) acc[rr][c][l] = 0.0f;
+#pragma unroll
+  for (int i4 = 0; i4 < HD / 4; ++i4) {
+    float4 q[4], k[G::KPT];
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) q[rr] = *reinterpret_cast<const float4*>(qs + (4 * warp + rr) * HD + 4 * i4);
+#pragma unroll
+    for (int c = 0; c < G::KPT; ++c) k[c] = *reinterpret_cast<const float4*>(ks + (lane + 32 * c) * G::KStride + 4 * i4);
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+      for (int c = 0; c < G::KPT; ++c) {
+        float* a = acc[rr][c] + 4 * (i4 & 3);
+        a[0] = __fmaf_rn(q[rr].x, k[c].x, a[0]);
+        a[1] = __fmaf_rn(q[rr].y, k[c].y, a[1]);
+        a[2] = __fmaf_rn(q[rr].z, k[c].z, a[2]);
+        a[3] = __fmaf_rn(q[rr].w, k[c].w, a[3]);
+      }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+    for (int c = 0; c < G::KPT; ++c) s[rr][c] = __fmul_rn(bw::tree16(acc[rr][c]), scale);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kTileThreads)
+attention_tiles_exact_kernel(const float* __restrict__ qkv, int q_stride, const float* __restrict__ kcache,
+                             const float* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
+                             const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
+                             const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
+                             const int* __restrict__ seq_row0, float* __restrict__ out, int out_stride, int heads,
+                             int kv_heads, int page, int window, float scale) {
+  using G = TileGeometry<HD>;
   extern __shared__ __align__(16) float smem[];
-  float* q = smem;          // [hd]
-  float* scores = smem + hd;  // [len]
-  __shared__ float red[kAttnThreads / 32];
-  const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  float* qs = smem;                       // [16][HD]
+  float* kbuf = qs + G::QFloats;          // [2][KT][KStride]
+  float* vbuf = kbuf + 2 * G::KFloats;    // [2][KT][HD]
+  float* es = vbuf + 2 * G::VFloats;      // [KT][16]: weights of the tile in hand, by key
+  float* row_max = es + G::EFloats;       // [16]
+  float* row_inv = row_max + kTileRows;   // [16]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile = blockIdx.y, h = blockIdx.x;  // heads fastest: the host lists the longest tiles first
+  const int g = h / (heads / kv_heads);
+  const int seq = tile_seq[tile], row0 = tile_row0[tile], nrows = tile_rows[tile];
+  const int p_first = seq_pos0[seq] + (row0 - seq_row0[seq]);  // position of the tile's first query row
+  const int p_last = p_first + nrows - 1;
+  const int* table = block_table + static_cast<size_t>(seq) * max_blocks;
+  auto first_key = [&](int p) { return (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0; };
+  const int kv_lo = (first_key(p_first) / G::KT) * G::KT;
+  const int ntiles = (p_last + 1 - kv_lo + G::KT - 1) / G::KT;
+
+  for (int idx = tid; idx < kTileRows * (HD / 4); idx += kTileThreads) {
+    const int r = idx / (HD / 4), piece = idx - r * (HD / 4);
+    const bool ok = r < nrows;
+    cp_async16(qs + r * HD + 4 * piece, qkv + static_cast<size_t>(row0 + (ok ? r : 0)) * q_stride + h * HD + 4 * piece, ok);
+  }
+  // keys (and values) of tile t into buffer t % 2; keys beyond the last query's position are zeros.
+  // A thread keeps its 16-byte piece of a row and walks the keys.
+  const int page_shift = (page & (page - 1)) == 0 ? __ffs(page) - 1 : -1;
+  constexpr int kPieces = HD / 4, kKeysPerPass = kTileThreads / kPieces;
+  const int my_piece = tid % kPieces, my_key0 = tid / kPieces;
+  auto load_tile = [&](int t, bool with_values) {
+    if (my_key0 >= kKeysPerPass) return;  // threads beyond a whole number of keys sit out
+    float* kd = kbuf + (t & 1) * G::KFloats;
+    float* vd = vbuf + (t & 1) * G::VFloats;
+    for (int key = my_key0; key < G::KT; key += kKeysPerPass) {
+      const int j = kv_lo + t * G::KT + key;
+      const bool ok = j <= p_last;
+      size_t off = 0;
+      if (ok) {
+        const int blk = page_shift >= 0 ? j >> page_shift : j / page;
+        off = ((static_cast<size_t>(table[blk]) * kv_heads + g) * page + (j - blk * page)) * HD + 4 * my_piece;
+      }
+      cp_async16(kd + key * G::KStride + 4 * my_piece, kcache + off, ok);
+      if (with_values) cp_async16(vd + key * HD + 4 * my_piece, vcache + off, ok);
+    }
+  };
+  // this thread's rows when scores are computed, their positions and first keys
+  int pos_r[4], lo_r[4];
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+    const int r = 4 * warp + rr;
+    pos_r[rr] = r < nrows ? p_first + r : -1;  // a row beyond the tile sees no key
+    lo_r[rr] = first_key(pos_r[rr]);
+  }
+
+  // ---- first walk: the maximum of every row's scores
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  load_tile(0, false);
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (int t = 0; t < ntiles; ++t) {
+    if (t + 1 < ntiles) load_tile(t + 1, false);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 1;\n" ::);
+    __syncthreads();
+    float s[4][G::KPT];
+    tile_scores<HD>(qs, kbuf + (t & 1) * G::KFloats, warp, lane, scale, s);
+    const int j0 = kv_lo + t * G::KT;
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+      for (int c = 0; c < G::KPT; ++c) {
+        const int j = j0 + lane + 32 * c;
+        if (j >= lo_r[rr] && j <= pos_r[rr]) mx[rr] = fmaxf(mx[rr], s[rr][c]);
+      }
+    __syncthreads();  // the buffer may be refilled
+  }
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], o));
+  }
+
+  // ---- second walk: weights, their sum and the weighted values, in key order
+  const int dcol = tid % G::TD, rg = tid / G::TD;  // pass 2: this thread's first output column and group of rows
+  float acc[G::RPT][G::DPT];
+#pragma unroll
+  for (int i = 0; i < G::RPT; ++i)
+#pragma unroll
+    for (int dd = 0; dd < G::DPT; ++dd) acc[i][dd] = 0.0f;
+  float sum = 0.0f;                                 // of row rg * RPT + dcol, for dcol < RPT
+  const int sum_row = rg * G::RPT + (dcol < G::RPT ? dcol : 0);
+  const int sum_pos = sum_row < nrows ? p_first + sum_row : -1, sum_lo = first_key(sum_pos);
+  int pos2[G::RPT], lo2[G::RPT];
+#pragma unroll
+  for (int i = 0; i < G::RPT; ++i) {
+    const int r = rg * G::RPT + i;
+    pos2[i] = r < nrows ? p_first + r : -1;
+    lo2[i] = first_key(pos2[i]);
+  }
+  const int lo_all = first_key(p_last);  // a key from here on is in every row's window
+  load_tile(0, true);
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (int t = 0; t < ntiles; ++t) {
+    if (t + 1 < ntiles) load_tile(t + 1, true);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 1;\n" ::);
+    __syncthreads();
+    const int j0 = kv_lo + t * G::KT;
+    {
+      float s[4][G::KPT];
+      tile_scores<HD>(qs, kbuf + (t & 1) * G::KFloats, warp, lane, scale, s);
+#pragma unroll
+      for (int c = 0; c < G::KPT; ++c) {
+        float4 e;
+        e.x = bw::det_expf(__fsub_rn(s[0][c], mx[0]));
+        e.y = bw::det_expf(__fsub_rn(s[1][c], mx[1]));
+        e.z = bw::det_expf(__fsub_rn(s[2][c], mx[2]));
+        e.w = bw::det_expf(__fsub_rn(s[3][c], mx[3]));
+        *reinterpret_cast<float4*>(es + (lane + 32 * c) * kTileRows + 4 * warp) = e;
+      }
+    }
+    __syncthreads();
+    const float* vt = vbuf + (t & 1) * G::VFloats;
+    const int keys = min(G::KT, p_last + 1 - j0);
+    const bool all_in = nrows == kTileRows && j0 >= lo_all && j0 + G::KT - 1 <= p_first;
+    if (dcol < HD || G::TD * (G::DPT - 1) + dcol < HD || dcol < G::RPT) {
+      if (all_in) {
+#pragma unroll 4
+        for (int kk = 0; kk < G::KT; ++kk) {
+          float e[G::RPT], v[G::DPT];
+#pragma unroll
+          for (int i = 0; i < G::RPT; ++i) e[i] = es[kk * kTileRows + rg * G::RPT + i];
+#pragma unroll
+          for (int dd = 0; dd < G::DPT; ++dd) v[dd] = (dcol + G::TD * dd < HD) ? vt[kk * HD + dcol + G::TD * dd] : 0.0f;
+          if (dcol < G::RPT) sum = __fadd_rn(sum, es[kk * kTileRows + sum_row]);
+#pragma unroll
+          for (int i = 0; i < G::RPT; ++i)
+#pragma unroll
+            for (int dd = 0; dd < G::DPT; ++dd) acc[i][dd] = __fmaf_rn(e[i], v[dd], acc[i][dd]);
+        }
+      } else {
+        for (int kk = 0; kk < keys; ++kk) {
+          const int j = j0 + kk;
+          float v[G::DPT];
+#pragma unroll
+          for (int dd = 0; dd < G::DPT; ++dd) v[dd] = (dcol + G::TD * dd < HD) ? vt[kk * HD + dcol + G::TD * dd] : 0.0f;
+          if (dcol < G::RPT && j >= sum_lo && j <= sum_pos) sum = __fadd_rn(sum, es[kk * kTileRows + sum_row]);
+#pragma unroll
+          for (int i = 0; i < G::RPT; ++i) {
+            if (j < lo2[i] || j > pos2[i]) continue;
+            const float e = es[kk * kTileRows + rg * G::RPT + i];
+#pragma unroll
+            for (int dd = 0; dd < G::DPT; ++dd) acc[i][dd] = __fmaf_rn(e, v[dd], acc[i][dd]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // the buffers and the weights may be overwritten
+  }
+  if (dcol < G::RPT) row_inv[rg * G::RPT + dcol] = __fdiv_rn(1.0f, sum);
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < G::RPT; ++i) {
+    const int r = rg * G::RPT + i;
+    if (r >= nrows) continue;
+#pragma unroll
+    for (int dd = 0; dd < G::DPT; ++dd) {
+      const int d = dcol + G::TD * dd;
+      if (d < HD) out[static_cast<size_t>(row0 + r) * out_stride + h * HD + d] = __fmul_rn(acc[i][dd], row_inv[r]);
+    }
+  }
+}
+
+// ---- single rows: scores by many blocks -------------------------------------------------------
+// A block takes kScoreKeys consecutive keys of one (row, head): a thread per key computes
+// s_j = dot16(q, K_j) * scale and stores it; the block's maximum goes to its own place.
+// scores[(row * heads + h) * score_stride + j], chunk_max[(row * heads + h) * chunks + chunk].
+constexpr int kScoreThreads = 128;
+constexpr int kScoreKeys = 256;
+
+__global__ void __launch_bounds__(kScoreThreads)
+attention_scores_exact_kernel(const float* __restrict__ qkv, int q_stride, const float* __restrict__ kcache,
+                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq,
+                              const int* __restrict__ pos, int heads, int kv_heads, int hd, int page, int window,
+                              float scale, float* __restrict__ scores, int score_stride,
+                              float* __restrict__ chunk_max, int chunks) {
+  extern __shared__ __align__(16) float smem[];
+  float* q = smem;  // [hd]
+  __shared__ float red[kScoreThreads / 32];
+  const int r = blockIdx.x, h = blockIdx.y, chunk = blockIdx.z, tid = threadIdx.x;
   const int p = pos[r];
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-  const int len = p - lo + 1;
+  const int c0 = chunk * kScoreKeys;
+  if (c0 > p || c0 + kScoreKeys <= lo) return;  // no key of the row's range in this chunk
   const int g = h / (heads / kv_heads);
   const int* table = block_table + static_cast<size_t>(row_seq[r]) * max_blocks;
   const float* qg = qkv + static_cast<size_t>(r) * q_stride + h * hd;
-  for (int i = tid; i < hd; i += kAttnThreads) q[i] = qg[i];
+  for (int i = tid; i < hd; i += kScoreThreads) q[i] = qg[i];
   __syncthreads();
-
+  float* out = scores + (static_cast<size_t>(r) * heads + h) * score_stride;
   float mx = -INFINITY;
-  for (int j = lo + tid; j <= p; j += kAttnThreads) {
+  for (int j = c0 + tid; j < c0 + kScoreKeys; j += kScoreThreads) {
+    if (j < lo || j > p) continue;
     const float* kp = kcache + ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + j % page) * hd;
     float lane[16];
 #pragma unroll
     for (int l = 0; l < 16; ++l) lane[l] = 0.0f;
     for (int i = 0; i < hd; i += 16) {
       const float4* k4 = reinterpret_cast<const float4*>(kp + i);
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        const float4 kk = k4[v];
-        lane[4 * v + 0] = __fmaf_rn(q[i + 4 * v + 0], kk.x, lane[4 * v + 0]);
-        lane[4 * v + 1] = __fmaf_rn(q[i + 4 * v + 1], kk.y, lane[4 * v + 1]);
-        lane[4 * v + 2] = __fmaf_rn(q[i + 4 * v + 2], kk.z, lane[4 * v + 2]);
-        lane[4 * v + 3] = __fmaf_rn(q[i + 4 * v + 3], kk.w, lane[4 * v + 3]);
-      }
+      const float4 k0 = k4[0], k1 = k4[1], k2 = k4[2], k3 = k4[3];
+      lane[0] = __fmaf_rn(q[i + 0], k0.x, lane[0]), lane[1] = __fmaf_rn(q[i + 1], k0.y, lane[1]);
+      lane[2] = __fmaf_rn(q[i + 2], k0.z, lane[2]), lane[3] = __fmaf_rn(q[i + 3], k0.w, lane[3]);
+      lane[4] = __fmaf_rn(q[i + 4], k1.x, lane[4]), lane[5] = __fmaf_rn(q[i + 5], k1.y, lane[5]);
+      lane[6] = __fmaf_rn(q[i + 6], k1.z, lane[6]), lane[7] = __fmaf_rn(q[i + 7], k1.w, lane[7]);
+      lane[8] = __fmaf_rn(q[i + 8], k2.x, lane[8]), lane[9] = __fmaf_rn(q[i + 9], k2.y, lane[9]);
+      lane[10] = __fmaf_rn(q[i + 10], k2.z, lane[10]), lane[11] = __fmaf_rn(q[i + 11], k2.w, lane[11]);
+      lane[12] = __fmaf_rn(q[i + 12], k3.x, lane[12]), lane[13] = __fmaf_rn(q[i + 13], k3.y, lane[13]);
+      lane[14] = __fmaf_rn(q[i + 14], k3.z, lane[14]), lane[15] = __fmaf_rn(q[i + 15], k3.w, lane[15]);
     }
-    const float s = __fmul_rn(bw::tree16(lane), scale);
-    scores[j - lo] = s;
-    mx = fmaxf(mx, s);
+    const float sc = __fmul_rn(bw::tree16(lane), scale);
+    out[j] = sc;
+    mx = fmaxf(mx, sc);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   if ((tid & 31) == 0) red[tid >> 5] = mx;
   __syncthreads();
-  mx = red[0];
+  if (tid == 0) {
+    float m = red[0];
 #pragma unroll
-  for (int w = 1; w < kAttnThreads / 32; ++w) mx = fmaxf(mx, red[w]);
-  for (int j = tid; j < len; j += kAttnThreads) scores[j] = bw::det_expf(__fsub_rn(scores[j], mx));
-  __syncthreads();
-
-  // Second pass, in key order: thread d walks the keys for output element d: sum += e,
-  // acc = fma(e, v, acc). With many blocks (prefill) it reads the values straight from the
-  // cache: other blocks hide the latency of its loads.
-  if (!STAGED) {
-    for (int d = tid; d < hd; d += kAttnThreads) {
-      float acc = 0.0f, sum = 0.0f;
-      int j = lo;
-      while (j <= p) {
-        const int b = j / page;
-        const int first = j - b * page;
-        const int last = (p - b * page < page - 1) ? p - b * page : page - 1;
-        const float* vp = vcache + ((static_cast<size_t>(table[b]) * kv_heads + g) * page) * hd + d;
-#pragma unroll 4
-        for (int s = first; s <= last; ++s) {
-          const float e = scores[j - lo + (s - first)];
-          sum = __fadd_rn(sum, e);
-          acc = __fmaf_rn(e, vp[static_cast<size_t>(s) * hd], acc);
-        }
-        j += last - first + 1;
-      }
-      out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc, __fdiv_rn(1.0f, sum));
-    }
-    return;
+    for (int w = 1; w < kScoreThreads / 32; ++w) m = fmaxf(m, red[w]);
+    chunk_max[(static_cast<size_t>(r) * heads + h) * chunks + chunk] = m;
   }
-  // With few blocks (decode steps) a walk through the cache is a chain of load latencies. The
-  // values then come through shared memory in tiles of 64 keys that all threads fetch
-  // together (cp.async, the next tile on its way while this one is used); the same operations
-  // in the same order.
-  float* vt = scores + score_floats;  // [2][kAttnTileKeys][hd]
-  constexpr int kMaxD = 256 / kAttnThreads;  // output elements per thread (head sizes up to 256)
-  float acc[kMaxD], sum = 0.0f;
+}
+
+// ---- single rows: the chains of pass 2 -------------------------------------------------------
+// A block per (row, head, slice of the output columns): the weights e_j = exp(s_j - mx) of
+// the whole row are put into shared memory first (all threads, any order: each is a function
+// of its own score), then the values stream through a ring of tiles of 64 keys and thread d
+// walks the keys in order: sum += e_j, acc = fma(e_j, V_j[d], acc). Every chain thread carries
+// the sum itself. The warps that hold chain threads do nothing but walk the chains: a thread
+// that also computed addresses and issued copies would stretch the chain that the kernel's time
+// hangs on. Two forms of the copying:
+//   * by pages (whole value rows, a page size that divides 64, no window): one more warp
+//     requests a page of a head, which lies in one piece, as one bulk copy counted on the
+//     tile's barrier; the chain warps hand a tile back through a second barrier;
+//   * by 16-byte pieces (any page size, slices of the rows, windows): the block's other warps
+//     copy with cp.async, a thread keeps its piece of a row and walks the keys.
+constexpr int kValueTile = 64;
+constexpr int kValueMaxStages = 6;
+constexpr int kValueMaxSlice = 128;  // output columns per block at most
+constexpr int kValueStages = 4;      // of the form that copies by pieces
+constexpr int kValueThreads = 256;   // of the form that copies by pieces: the first `dslice` walk the chains
+
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+
+// the keys of one tile for output column d: `e_t` the tile's weights, `v` the tile's values at column d
+__device__ __forceinline__ void value_chain(const float* __restrict__ e_t, const float* __restrict__ v, int dslice, int keys,
+                                            float& sum, float& acc) {
+  if (keys == kValueTile) {
+    // eight keys' weights and values are read while the eight before them are chained in
+    float4 e0 = *reinterpret_cast<const float4*>(e_t), e1 = *reinterpret_cast<const float4*>(e_t + 4);  // tiles start on 16 bytes
+    float vv[8];
 #pragma unroll
-  for (int i = 0; i < kMaxD; ++i) acc[i] = 0.0f;
-  const int tiles = (len + kAttnTileKeys - 1) / kAttnTileKeys;
-  const int pieces = hd / 4;  // 16-byte pieces of a value row
-  auto fetch = [&](int t) {
-    float* dst = vt + (t & 1) * kAttnTileKeys * hd;
-    for (int idx = tid; idx < kAttnTileKeys * pieces; idx += kAttnThreads) {
-      const int key = idx / pieces, piece = idx - key * pieces;
-      const int j = lo + t * kAttnTileKeys + key;
-      const bool ok = j <= p;
-      const float* src = vcache;
-      if (ok) src += ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + j % page) * hd + piece * 4;
-      const unsigned d32 = static_cast<unsigned>(__cvta_generic_to_shared(dst + key * hd + piece * 4));
-      const int bytes = ok ? 16 : 0;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d32), "l"(src), "r"(bytes));
+    for (int i = 0; i < 8; ++i) vv[i] = v[i * dslice];
+#pragma unroll
+    for (int s8 = 0; s8 < kValueTile; s8 += 8) {
+      float4 n0 = e0, n1 = e1;
+      float vn[8];
+      if (s8 + 8 < kValueTile) {
+        n0 = *reinterpret_cast<const float4*>(e_t + s8 + 8), n1 = *reinterpret_cast<const float4*>(e_t + s8 + 12);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vn[i] = v[(s8 + 8 + i) * dslice];
+      }
+      sum = __fadd_rn(sum, e0.x), acc = __fmaf_rn(e0.x, vv[0], acc);
+      sum = __fadd_rn(sum, e0.y), acc = __fmaf_rn(e0.y, vv[1], acc);
+      sum = __fadd_rn(sum, e0.z), acc = __fmaf_rn(e0.z, vv[2], acc);
+      sum = __fadd_rn(sum, e0.w), acc = __fmaf_rn(e0.w, vv[3], acc);
+      sum = __fadd_rn(sum, e1.x), acc = __fmaf_rn(e1.x, vv[4], acc);
+      sum = __fadd_rn(sum, e1.y), acc = __fmaf_rn(e1.y, vv[5], acc);
+      sum = __fadd_rn(sum, e1.z), acc = __fmaf_rn(e1.z, vv[6], acc);
+      sum = __fadd_rn(sum, e1.w), acc = __fmaf_rn(e1.w, vv[7], acc);
+      if (s8 + 8 < kValueTile) {
+        e0 = n0, e1 = n1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vv[i] = vn[i];
+      }
     }
-  };
-  fetch(0);
-  asm volatile("cp.async.commit_group;\n" ::);
-  for (int t = 0; t < tiles; ++t) {
-    if (t + 1 < tiles) fetch(t + 1);
-    asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 1;\n" ::);
-    __syncthreads();
-    const float* v = vt + (t & 1) * kAttnTileKeys * hd;
-    const int keys = min(kAttnTileKeys, len - t * kAttnTileKeys);
-    const float* e_t = scores + t * kAttnTileKeys;
-#pragma unroll 8
+  } else {
     for (int s2 = 0; s2 < keys; ++s2) {
       const float e = e_t[s2];
       sum = __fadd_rn(sum, e);
-#pragma unroll
-      for (int i = 0; i < kMaxD; ++i) {
-        const int d = tid + i * kAttnThreads;
-        if (d < hd) acc[i] = __fmaf_rn(e, v[s2 * hd + d], acc[i]);
+      acc = __fmaf_rn(e, v[s2 * dslice], acc);
+    }
+  }
+}
+
+// the weights of a row into shared memory, by `count` threads of which this is number `tid`
+__device__ __forceinline__ void row_weights(float* es, const float* __restrict__ scores, const float* __restrict__ cm,
+                                            int lo, int p, int tid, int count) {
+  float mx = -INFINITY;
+  for (int c = lo / kScoreKeys; c <= p / kScoreKeys; ++c) mx = fmaxf(mx, cm[c]);
+  for (int j = tid; j <= p - lo; j += count) es[j] = bw::det_expf(__fsub_rn(scores[lo + j], mx));
+}
+
+__global__ void __launch_bounds__(kValueMaxSlice + 32)
+attention_values_paged_exact_kernel(const float* __restrict__ scores, int score_stride, const float* __restrict__ chunk_max,
+                                    int chunks, const float* __restrict__ vcache, const int* __restrict__ block_table,
+                                    int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos,
+                                    float* __restrict__ out, int out_stride, int heads, int kv_heads, int hd, int page,
+                                    int weight_floats, int stages, int* failure) {
+  extern __shared__ __align__(16) float smem[];
+  float* es = smem;                    // [len] weights of the row
+  float* vt = smem + weight_floats;    // [stages][kValueTile][hd]
+  uint64_t* full = reinterpret_cast<uint64_t*>(vt + stages * kValueTile * hd);
+  uint64_t* empty = full + stages;
+  volatile unsigned* gave_up = reinterpret_cast<volatile unsigned*>(failure);
+  const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+  const int workers = static_cast<int>(blockDim.x) - 32;  // whole warps of chain threads, then the requesting warp
+  const int p = pos[r];
+  const int len = p + 1;
+  const int g = h / (heads / kv_heads);
+  const int* table = block_table + static_cast<size_t>(row_seq[r]) * max_blocks;
+  const int tiles = (len + kValueTile - 1) / kValueTile;
+  if (tid == 0) {
+    for (int s2 = 0; s2 < stages; ++s2) {
+      bar_init(full + s2, 1);
+      bar_init(empty + s2, workers / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (tid >= workers) {
+    // the requesting warp: lane l brings page l of a tile (a page of a head lies in one piece)
+    const int pages_per_tile = kValueTile / page;
+    const unsigned page_bytes = static_cast<unsigned>(page) * hd * 4u;
+    for (int t = 0; t < tiles; ++t) {
+      const int slot = t % stages;
+      if (t >= stages && !bw::mbar_wait_bounded(empty + slot, ((t / stages) - 1) & 1, gave_up)) break;
+      const int keys = min(kValueTile, len - t * kValueTile);
+      const int pages = (keys + page - 1) / page;  // the last page is copied whole: it is the request's own
+      if (lane == 0) bar_expect(full + slot, page_bytes * pages);
+      __syncwarp();
+      for (int pg = lane; pg < pages; pg += 32) {
+        const int blk = t * pages_per_tile + pg;
+        const size_t off = (static_cast<size_t>(table[blk]) * kv_heads + g) * page * hd;
+        bulk_copy(vt + (slot * kValueTile + pg * page) * hd, vcache + off, page_bytes, full + slot);
       }
     }
-    __syncthreads();  // the tile may be overwritten by the fetch after next
+    return;
   }
-  const float inv = __fdiv_rn(1.0f, sum);
-#pragma unroll
-  for (int i = 0; i < kMaxD; ++i) {
-    const int d = tid + i * kAttnThreads;
-    if (d < hd) out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc[i], inv);
+  row_weights(es, scores + (static_cast<size_t>(r) * heads + h) * score_stride,
+              chunk_max + (static_cast<size_t>(r) * heads + h) * chunks, 0, p, tid, workers);
+  asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");  // the chain warps only: the requesting warp is elsewhere
+  const int d = tid;
+  float acc = 0.0f, sum = 0.0f;
+  for (int t = 0; t < tiles; ++t) {
+    const int slot = t % stages;
+    if (!bw::mbar_wait_bounded(full + slot, (t / stages) & 1, gave_up)) break;
+    if (d < hd) value_chain(es + t * kValueTile, vt + slot * kValueTile * hd + d, hd, min(kValueTile, len - t * kValueTile), sum, acc);
+    __syncwarp();
+    if (lane == 0) bar_arrive(empty + slot);  // this warp has read the tile
   }
+  if (d < hd) out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc, __fdiv_rn(1.0f, sum));
+}
+
+__global__ void __launch_bounds__(kValueThreads)
+attention_values_exact_kernel(const float* __restrict__ scores, int score_stride, const float* __restrict__ chunk_max,
+                              int chunks, const float* __restrict__ vcache, const int* __restrict__ block_table,
+                              int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos,
+                              float* __restrict__ out, int out_stride, int heads, int kv_heads, int hd, int dslice,
+                              int page, int window, int weight_floats) {
+  extern __shared__ __align__(16) float smem[];
+  float* es = smem;                    // [len] weights of the row
+  float* vt = smem + weight_floats;    // [kValueStages][kValueTile][dslice]
+  const int r = blockIdx.x, h = blockIdx.y, d0 = blockIdx.z * dslice, tid = threadIdx.x;
+  const int p = pos[r];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int len = p - lo + 1;
+  const int g = h / (heads / kv_heads);
+  const int* table = block_table + static_cast<size_t>(row_seq[r]) * max_blocks;
+  const int pieces = dslice / 4;  // 16-byte pieces of this block's part of a value row
+  const int tiles = (len + kValueTile - 1) / kValueTile;
+  const int workers = (dslice + 31) / 32 * 32, copiers = kValueThreads - workers;
+  const bool copier = tid >= workers;
+  const int ctid = tid - workers;
+  const int page_shift = (page & (page - 1)) == 0 ? __ffs(page) - 1 : -1;
+  const int keys_per_pass = copiers / pieces, my_piece = ctid % pieces, my_key0 = ctid / pieces;
+  auto fetch = [&](int t) {
+    if (!copier || my_key0 >= keys_per_pass) return;  // threads beyond a whole number of keys sit out
+    float* dst = vt + (t % kValueStages) * kValueTile * dslice + 4 * my_piece;
+    for (int key = my_key0; key < kValueTile; key += keys_per_pass) {
+      const int j = lo + t * kValueTile + key;
+      const bool ok = j <= p;
+      size_t off = 0;
+      if (ok) {
+        const int blk = page_shift >= 0 ? j >> page_shift : j / page;
+        off = ((static_cast<size_t>(table[blk]) * kv_heads + g) * page + (j - blk * page)) * hd + d0 + 4 * my_piece;
+      }
+      cp_async16(dst + key * dslice, vcache + off, ok);
+    }
+  };
+  // the values do not wait for the weights: the ring is filled first
+  for (int t = 0; t < kValueStages - 1; ++t) {
+    if (t < tiles) fetch(t);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  row_weights(es, scores + (static_cast<size_t>(r) * heads + h) * score_stride,
+              chunk_max + (static_cast<size_t>(r) * heads + h) * chunks, lo, p, tid, kValueThreads);
+  const int d = tid;  // column d0 + d of the output, for d < dslice
+  float acc = 0.0f, sum = 0.0f;
+  for (int t = 0; t < tiles; ++t) {
+    if (copier) asm volatile("cp.async.wait_group %0;\n" ::"n"(kValueStages - 2));
+    __syncthreads();  // tile t has landed (every copier waited for its own copies) and, at t = 0, the
+                      // weights are written; the buffer of tile t - 1 is free
+    if (copier) {
+      if (t + kValueStages - 1 < tiles) fetch(t + kValueStages - 1);
+      asm volatile("cp.async.commit_group;\n" ::);
+      continue;
+    }
+    if (d < dslice)
+      value_chain(es + t * kValueTile, vt + (t % kValueStages) * kValueTile * dslice + d, dslice,
+                  min(kValueTile, len - t * kValueTile), sum, acc);
+  }
+  if (d < dslice) out[static_cast<size_t>(r) * out_stride + h * hd + d0 + d] = __fmul_rn(acc, __fdiv_rn(1.0f, sum));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -475,6 +909,38 @@ __global__ void swiglu_exact_kernel(const float* __restrict__ gate_up, float* __
   }
 }
 
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Tensor maps for the streaming tile of few rows: a row-major float32 matrix [rows][k] seen as
+// (32 values, rows, k / 32 lines), boxes of 4 lines x box_rows rows, 128-byte swizzle, zeros
+// outside.
+namespace {
+typedef CUresult (*EncodeTiledF32)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledF32 f32_encoder() {
+  static EncodeTiledF32 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledF32>(p);
+  }
+  return fn;
+}
+bool f32_rows_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+  EncodeTiledF32 enc = f32_encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[3] = {kRowsTileK, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(k / kRowsTileK)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 4, kRowsTileK * 4};
+  const cuuint32_t box[3] = {kRowsTileK, static_cast<cuuint32_t>(box_rows), kRowsTiles};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
@@ -500,12 +966,42 @@ BW_API int bw_f32_linear(const float* x, const float* w, float* y, const float* 
     return -1;
   }
   const unsigned gx = (n + kGemmBN - 1) / kGemmBN;
-  if (m <= 16 && k % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
-    const unsigned blocks = (n + kRowsBN - 1) / kRowsBN;  // rows that start on 16 bytes: the streaming tile
+  if (m <= 16 && k % kRowsTileK == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+      f32_encoder() != nullptr) {
+    // rows that are whole 128-byte lines: the streaming tile
+    const unsigned blocks = (n + kRowsBN - 1) / kRowsBN;
+    // A product with few tiles (one block on an SM) keeps more stages on their way than one whose
+    // blocks share the SMs: what counts is the bytes an SM has in flight.
+    const int rows_per = m <= 8 ? 8 : 16;
+    const int stage_bytes = kRowsTiles * (kRowsBN + rows_per) * 128 + 16;
+    int stages = blocks <= 160 ? kRowsMaxStages : blocks <= 320 ? 8 : 4;
+    while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
+    const int smem_bytes = stages * stage_bytes + 1024;
+    constexpr int smem8 = kRowsMaxStages * (kRowsTiles * (kRowsBN + 8) * 128 + 16) + 1024;
+    constexpr int smem16 = 200 * 1024;
+    int* word = bw::failure_word();
+    if (!word) return -1;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_exact_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem8);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_exact_rows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem16);
+      if (e != cudaSuccess) {
+        bw::set_error("linear (32-bit): cannot raise shared memory: %s", cudaGetErrorString(e));
+        return static_cast<int>(e);
+      }
+      configured = true;
+    }
+    const int rows = m <= 8 ? 8 : 16;
+    CUtensorMap map_x, map_w;
+    if (!f32_rows_map(&map_x, x, m, k, rows) || !f32_rows_map(&map_w, w, n, k, kRowsBN)) {
+      bw::set_error("linear (32-bit): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
+      return -1;
+    }
     if (m <= 8)
-      gemm_exact_rows_kernel<8><<<blocks, kRowsBN * 4, 0, stream>>>(x, w, y, residual, m, n, k);
+      gemm_exact_rows_kernel<8><<<blocks, kRowsBN * 4 + 32, smem_bytes, stream>>>(map_x, map_w, y, residual, m, n, k, stages, word);
     else
-      gemm_exact_rows_kernel<16><<<blocks, kRowsBN * 8, 0, stream>>>(x, w, y, residual, m, n, k);
+      gemm_exact_rows_kernel<16><<<blocks, kRowsBN * 8 + 32, smem_bytes, stream>>>(map_x, map_w, y, residual, m, n, k, stages, word);
   } else if (m <= 16) {
     gemm_exact_kernel<16><<<dim3(gx, (m + 15) / 16), 256, 0, stream>>>(x, w, y, residual, m, n, k);
   } else if (m > 64 && k % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
@@ -540,54 +1036,174 @@ BW_API int bw_f32_rope_cache(float* qkv, int row_stride, const int* pos, const i
   return bw::launch_status();
 }
 
-BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache, const float* vcache,
-                            const int* block_table, int max_blocks, const int* row_seq, const int* pos,
-                            float* out, int out_stride, int n, int heads, int kv_heads, int hd, int page,
-                            int window, int max_keys, float scale, cudaStream_t stream) {
-  if (n <= 0) return 0;
-  if (hd % 16 || hd <= 0) {
-    bw::set_error("attention: head size %d is not a multiple of 16", hd);
-    return -1;
-  }
-  if (heads % kv_heads) {
-    bw::set_error("attention: %d heads are not a multiple of %d key/value heads", heads, kv_heads);
-    return -1;
-  }
-  if (hd > 256) {
-    bw::set_error("attention (32-bit): head size %d exceeds 256", hd);
-    return -1;
-  }
-  const int score_floats = (max_keys + 3) / 4 * 4;  // keeps the value tiles behind the scores on 16 bytes
-  const bool staged = static_cast<long long>(n) * heads <= 148 * 16;  // few blocks: a decode step
-  const size_t smem = (static_cast<size_t>(hd) + score_floats + (staged ? 2 * kAttnTileKeys * hd : 0)) * sizeof(float);
-  if (smem > 220 * 1024) {
-    bw::set_error("attention (32-bit): %d keys exceed the shared-memory score buffer", max_keys);
-    return -1;
-  }
-  if (heads > 65535) {
-    bw::set_error("attention: %d heads exceed the grid limit", heads);
-    return -1;
-  }
+// Floats of scratch that a step of single rows needs (scores and the chunks' maxima).
+BW_API long long bw_f32_attention_scratch_floats(int n, int heads, int max_keys) {
+  const long long stride = (static_cast<long long>(max_keys) + kScoreKeys - 1) / kScoreKeys * kScoreKeys;
+  return static_cast<long long>(n) * heads * (stride + stride / kScoreKeys);
+}
+
+namespace {
+
+template <int HD>
+int launch_attention_tiles(const float* qkv, int q_stride, const float* kcache, const float* vcache, const int* block_table,
+                           int max_blocks, const int* tile_seq, const int* tile_row0, const int* tile_rows, int num_tiles,
+                           const int* seq_pos0, const int* seq_row0, float* out, int out_stride, int heads, int kv_heads,
+                           int page, int window, float scale, cudaStream_t stream) {
+  using G = TileGeometry<HD>;
+  constexpr int smem = G::SmemFloats * static_cast<int>(sizeof(float));
+  static_assert(smem <= 227 * 1024, "the tiles do not fit into shared memory");
   static bool configured = false;
-  if (smem > 48 * 1024 && !configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_exact_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         220 * 1024);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_exact_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tiles_exact_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) {
-      bw::set_error("attention: cannot raise shared memory: %s", cudaGetErrorString(e));
+      bw::set_error("attention (32-bit): cannot raise shared memory to %d: %s", smem, cudaGetErrorString(e));
       return static_cast<int>(e);
     }
     configured = true;
   }
-  if (staged)
-    attention_exact_kernel<true><<<dim3(n, heads), kAttnThreads, smem, stream>>>(
-        qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads, kv_heads, hd,
-        page, window, scale, score_floats);
-  else
-    attention_exact_kernel<false><<<dim3(n, heads), kAttnThreads, smem, stream>>>(
-        qkv, q_stride, kcache, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads, kv_heads, hd,
-        page, window, scale, score_floats);
+  attention_tiles_exact_kernel<HD><<<dim3(heads, num_tiles), kTileThreads, smem, stream>>>(
+      qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out,
+      out_stride, heads, kv_heads, page, window, scale);
+  return bw::launch_status();
+}
+
+}  // namespace
+
+// Query rows in a tile of the tiled form (what callers cut a step's rows into).
+BW_API int bw_f32_attention_tile_rows() { return kTileRows; }
+
+// out[r, h] = attention of row r's query over the cached keys of its sequence.
+//   tiles given (num_tiles > 0) and some tile has more than one row: every tile (up to 16
+//     consecutive rows of one sequence) is a block per head;
+//   otherwise (single rows, in any order): scores by many blocks into `scratch`
+//     (bw_f32_attention_scratch_floats), then the chains.
+BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache, const float* vcache,
+                            const int* block_table, int max_blocks, const int* row_seq, const int* pos,
+                            const int* tile_seq, const int* tile_row0, const int* tile_rows, int num_tiles,
+                            const int* seq_pos0, const int* seq_row0, float* out, int out_stride, int n, int heads,
+                            int kv_heads, int hd, int page, int window, int max_keys, float scale, float* scratch,
+                            long long scratch_floats, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (hd % 16 || hd <= 0 || hd > 256) {
+    bw::set_error("attention (32-bit): head size %d is not a multiple of 16 up to 256", hd);
+    return -1;
+  }
+  if (kv_heads <= 0 || heads % kv_heads) {
+    bw::set_error("attention: %d heads are not a multiple of %d key/value heads", heads, kv_heads);
+    return -1;
+  }
+  if (heads > 65535 || page <= 0 || q_stride % 4 || (reinterpret_cast<uintptr_t>(qkv) & 15) ||
+      (reinterpret_cast<uintptr_t>(kcache) & 15) || (reinterpret_cast<uintptr_t>(vcache) & 15)) {
+    bw::set_error("attention (32-bit): %d heads, page %d, row stride %d: rows must start on 16 bytes", heads, page, q_stride);
+    return -1;
+  }
+  if (num_tiles > 0 && num_tiles < n) {  // prompt portions (perhaps beside single rows)
+    if (num_tiles > 65535) {
+      bw::set_error("attention (32-bit): %d query tiles exceed the grid limit", num_tiles);
+      return -1;
+    }
+#define BW_TILES(HD_)                                                                                                  \
+  case HD_:                                                                                                            \
+    return launch_attention_tiles<HD_>(qkv, q_stride, kcache, vcache, block_table, max_blocks, tile_seq, tile_row0,   \
+                                       tile_rows, num_tiles, seq_pos0, seq_row0, out, out_stride, heads, kv_heads,    \
+                                       page, window, scale, stream)
+    switch (hd) {
+      BW_TILES(16);
+      BW_TILES(32);
+      BW_TILES(48);
+      BW_TILES(64);
+      BW_TILES(80);
+      BW_TILES(96);
+      BW_TILES(112);
+      BW_TILES(128);
+      BW_TILES(144);
+      BW_TILES(160);
+      BW_TILES(176);
+      BW_TILES(192);
+      BW_TILES(208);
+      BW_TILES(224);
+      BW_TILES(240);
+      BW_TILES(256);
+    }
+#undef BW_TILES
+    return -1;
+  }
+  // single rows
+  const int score_stride = (max_keys + kScoreKeys - 1) / kScoreKeys * kScoreKeys;
+  const int chunks = score_stride / kScoreKeys;
+  if (!scratch || scratch_floats < bw_f32_attention_scratch_floats(n, heads, max_keys)) {
+    bw::set_error("attention (32-bit): %lld floats of scratch for %d rows, %d heads, %d keys are too few", scratch_floats,
+                  n, heads, max_keys);
+    return -1;
+  }
+  if (chunks > 65535) {
+    bw::set_error("attention (32-bit): %d keys exceed the grid limit", max_keys);
+    return -1;
+  }
+  float* scores = scratch;
+  float* chunk_max = scratch + static_cast<size_t>(n) * heads * score_stride;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  attention_scores_exact_kernel<<<dim3(n, heads, chunks), kScoreThreads, hd * sizeof(float), stream>>>(
+      qkv, q_stride, kcache, block_table, max_blocks, row_seq, pos, heads, kv_heads, hd, page, window, scale, scores,
+      score_stride, chunk_max, chunks);
+  const int weight_floats = (max_keys + 3) / 4 * 4;  // keeps the value tiles behind the weights on 16 bytes
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_values_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_values_paged_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) {
+      bw::set_error("attention (32-bit): cannot raise shared memory: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    configured = true;
+  }
+  // Whole value rows by pages, when there are (row, head) pairs enough to give every SM a stream
+  // of values, a page of a head is a piece of a kilobyte or more, pages divide a tile, and no
+  // window cuts into a page.
+  const bool by_page = static_cast<long long>(n) * heads >= sms && hd <= kValueMaxSlice && window <= 0 &&
+                       kValueTile % page == 0 && static_cast<long long>(page) * hd * 4 >= 1024;
+  if (by_page) {
+    // as many tiles on their way as 96 KB hold, six at most, two at least
+    int stages = (96 * 1024) / (kValueTile * hd * static_cast<int>(sizeof(float)));
+    stages = stages > kValueMaxStages ? kValueMaxStages : stages < 2 ? 2 : stages;
+    const size_t smem = (static_cast<size_t>(weight_floats) + static_cast<size_t>(stages) * kValueTile * hd) * sizeof(float) +
+                        2 * stages * sizeof(uint64_t);
+    int* word = bw::failure_word();
+    if (!word) return -1;
+    if (smem <= 220 * 1024) {
+      attention_values_paged_exact_kernel<<<dim3(n, heads), (hd + 31) / 32 * 32 + 32, smem, stream>>>(
+          scores, score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads,
+          kv_heads, hd, page, weight_floats, stages, word);
+      return bw::launch_status();
+    }
+  }
+  // columns of the output per block: all of them, or fewer when there are too few (row, head)
+  // pairs to give every SM a stream of values, and never more than a block has chain threads
+  int dsplit = 1;
+  while (hd / dsplit > kValueMaxSlice) dsplit *= 2;
+  while (dsplit < 4 && static_cast<long long>(n) * heads * dsplit < sms && (hd / (2 * dsplit)) % 4 == 0 &&
+         hd % (2 * dsplit) == 0)
+    dsplit *= 2;
+  if (hd % dsplit || (hd / dsplit) % 4) {
+    bw::set_error("attention (32-bit): head size %d cannot be cut into %d slices of whole 16 bytes", hd, dsplit);
+    return -1;
+  }
+  const int dslice = hd / dsplit;
+  const size_t smem = (static_cast<size_t>(weight_floats) + static_cast<size_t>(kValueStages) * kValueTile * dslice) * sizeof(float);
+  if (smem > 220 * 1024) {
+    bw::set_error("attention (32-bit): %d keys exceed the shared-memory buffer of a row's weights", max_keys);
+    return -1;
+  }
+  attention_values_exact_kernel<<<dim3(n, heads, dsplit), kValueThreads, smem, stream>>>(
+      scores, score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads,
+      kv_heads, hd, dslice, page, window, weight_floats);
   return bw::launch_status();
 }
 

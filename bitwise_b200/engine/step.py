@@ -42,13 +42,16 @@ class OutOfPages(StepError):
     pass
 
 
-def query_tile_rows(model) -> List[int]:
-    """The distinct query-tile heights that the model's mixers ask for."""
+def query_tile_rows(model, ops=None) -> List[int]:
+    """The distinct query-tile heights that the model's mixers ask for on the kernel library ``ops``."""
     sizes = set()
     for b in model.blocks:
         fn = getattr(b.mixer, "query_tile_rows", None)
         if fn is not None:
-            got = fn()
+            try:
+                got = fn(ops)
+            except TypeError:  # a mixer that takes no argument
+                got = fn()
             sizes.update(int(v) for v in (got if isinstance(got, (list, tuple, set)) else [got]))
     return sorted(sizes) or [16]
 
@@ -96,7 +99,7 @@ class Stepper:
         self.max_rows, self.max_seqs = max_rows, max_seqs
         page = manager.page_size
         mb = (max_tokens_per_request + page - 1) // page
-        self.layout = _Layout(max_rows, max_seqs, [mb] * len(manager.groups), query_tile_rows(model))
+        self.layout = _Layout(max_rows, max_seqs, [mb] * len(manager.groups), query_tile_rows(model, ops))
         pin = self.device is not None and torch.device(self.device).type == "cuda"
         self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=pin)
         self._host_np = self.host.numpy()

@@ -338,6 +338,17 @@ class KernelOps:
             return 16
         return max(1, 64 // max(1, heads // kv_heads))
 
+    def attention_tile_heights(self, heads: int, kv_heads: int, head_dim: int):
+        """The heights of query tiles (rows of one sequence per thread block) that this
+        precision's attention kernels want prepared for a step."""
+        if self.kind == "f32":
+            return [16]
+        group = max(1, heads // kv_heads)
+        rows = [max(1, 64 // group)]
+        if 128 % group == 0:
+            rows.append(128 // group)  # the tcgen05 prefill kernel stacks 128 rows per block
+        return rows
+
     def _attention_scratch(self, lib, device, n: int, heads: int, max_keys: int) -> torch.Tensor:
         """Scratch of the split attention: one (output, maximum, sum) record per row, head and
         tile of 64 keys.  Sized for contexts rounded up to 2048 keys so that it seldom grows."""
@@ -457,10 +468,26 @@ class KernelOps:
             raise KernelError("attention: output shape is not [rows, heads * head_dim]")
         page = kcache.shape[2]
         if self.kind == "f32":
+            # prompt portions run as tiles of 16 query rows that share their keys; a step of single
+            # rows (a decode step, or a call without the step's arrays) spreads a row's scores over
+            # many blocks and needs scratch for them
+            tiles = batch.query_tiles(16) if batch is not None and 16 in getattr(batch, "tile_sets", {}) else None
+            scratch, floats, launches = None, 0, 1
+            if tiles is None or tiles[3] >= n:
+                tiles = None
+                self.lib.bw_f32_attention_scratch_floats.restype = ctypes.c_longlong
+                floats = int(self.lib.bw_f32_attention_scratch_floats(_c_int(n), _c_int(heads), _c_int(max_keys)))
+                if self._attn_scratch is None or self._attn_scratch.numel() < floats:
+                    self._attn_scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+                scratch, launches = self._attn_scratch, 2
+            t_seq, t_row0, t_rows, t_count = tiles if tiles is not None else (None, None, None, 0)
             self._call("bw_f32_attention", _p(qkv), _c_int(qkv.shape[1]), _p(kcache), _p(vcache), _p(block_table),
-                       _c_int(block_table.shape[1]), _p(row_seq), _p(pos), _p(out), _c_int(out.shape[1]), _c_int(n),
+                       _c_int(block_table.shape[1]), _p(row_seq), _p(pos), _p(t_seq), _p(t_row0), _p(t_rows),
+                       _c_int(t_count), _p(batch.seq_pos0) if tiles is not None else None,
+                       _p(batch.seq_row0) if tiles is not None else None, _p(out), _c_int(out.shape[1]), _c_int(n),
                        _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page), _c_int(window),
-                       _c_int(max_keys), _c_float(scale), self._stream())
+                       _c_int(max_keys), _c_float(scale), _p(scratch), ctypes.c_longlong(floats), self._stream(),
+                       launches=launches)
         else:
             if batch is None:
                 raise KernelError("attention (bfloat16): the step's sequence arrays are required")

@@ -44,14 +44,12 @@ class GQAAttention(Mixer):
     def cache_need(self):
         return PagedKVNeed(self.kv_heads, self.head_dim, self.window)
 
-    def query_tile_rows(self, ops=None) -> int:
-        """Height of the query tiles this mixer's attention kernel wants (rows of one
-        sequence per thread block); the stepper prepares tiles of every height asked for."""
-        group = self.heads // self.kv_heads
-        rows = [max(1, 64 // group)]
-        if 128 % group == 0:
-            rows.append(128 // group)  # the tcgen05 prefill kernel stacks 128 rows per block
-        return rows
+    def query_tile_rows(self, ops=None):
+        """Heights of the query tiles this mixer's attention kernels want (rows of one sequence
+        per thread block); the stepper prepares tiles of every height asked for."""
+        if ops is not None and hasattr(ops, "attention_tile_heights"):
+            return list(ops.attention_tile_heights(self.heads, self.kv_heads, self.head_dim))
+        return [max(1, 64 // (self.heads // self.kv_heads))]
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
         q, k, v, o = self.names

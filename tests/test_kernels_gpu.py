@@ -450,8 +450,14 @@ def test_bf16_rmsnorm_and_swiglu():
 
 
 def _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window):
-    """rows_by_seq: list of (first position, count) per sequence; q: [rows, heads, hd] (bfloat16 values)."""
-    ops = _ops("bfloat16")
+    return _run_attention("bfloat16", q, rows_by_seq, k, v, table, heads, kv_heads, hd, window)
+
+
+def _run_attention(dtype, q, rows_by_seq, k, v, table, heads, kv_heads, hd, window):
+    """rows_by_seq: list of (first position, count) per sequence; q: [rows, heads, hd] (bfloat16 values
+    for the serving kernels)."""
+    ops = _ops(dtype)
+    td = torch.bfloat16 if dtype == "bfloat16" else torch.float32
     n = q.shape[0]
     qkv = np.zeros((n, (heads + 2 * kv_heads) * hd), dtype=np.float32)
     qkv[:, :heads * hd] = q.reshape(n, -1)
@@ -478,10 +484,79 @@ def _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window
                 tiles.append((s, seq_row0[s] + a, min(rows, cnt - a)))
         return I([x[0] for x in tiles]), I([x[1] for x in tiles]), I([x[2] for x in tiles]), len(tiles)
     b.query_tiles = query_tiles
-    out = torch.empty(n, heads * hd, device=DEV, dtype=torch.bfloat16)
-    ops.attention(t(qkv, torch.bfloat16), t(k, torch.bfloat16), t(v, torch.bfloat16), I(table), I(row_seq), I(pos),
-                  out, heads, kv_heads, hd, window, max(pos) + 1, 1.0 / float(np.sqrt(hd)), batch=b)
+    b.tile_sets = {rows: None for rows in ops.attention_tile_heights(heads, kv_heads, hd)}  # heights on offer
+    out = torch.empty(n, heads * hd, device=DEV, dtype=td)
+    ops.attention(t(qkv, td), t(k, td), t(v, td), I(table), I(row_seq), I(pos),
+                  out, heads, kv_heads, hd, window, max(pos) + 1, 1.0 / np.sqrt(np.float32(hd)).item(), batch=b)
     return out.float().cpu().numpy().reshape(n, heads, hd), pos, row_seq
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 8, 0), (5, 5, 48, 16, 0),
+                                                           (8, 2, 64, 64, 0), (2, 2, 128, 32, 0), (6, 2, 64, 16, 50),
+                                                           (4, 4, 80, 16, 0), (2, 1, 256, 16, 0), (4, 2, 96, 4, 21)])
+def test_f32_attention_in_tiles_of_rows(heads, kv_heads, hd, page, window):
+    """Prompt portions on the 32-bit path run as tiles of up to 16 query rows that share their
+    keys, and single rows as two kernels (scores by many blocks, then the chains): both equal the
+    plain attention bit for bit, for whole prompts, late portions, first tokens and decoded rows,
+    alone and side by side in one step."""
+    rng = np.random.default_rng(heads * 100 + hd + window)
+    lens = [150, 1, 70, 200, 333]
+    k, v, table, seq_k, seq_v = _paged(rng, lens, kv_heads, hd, page)
+    for rows_by_seq in ([(0, 150), (0, 1), (69, 1), (130, 70), (300, 33)],   # a step of portions and single rows
+                        [(149, 1), (0, 1), (69, 1), (199, 1), (332, 1)]):    # a step of single rows
+        n = sum(c for _, c in rows_by_seq)
+        q = rnd(rng, n, heads, hd)
+        got, pos, row_seq = _run_attention("float32", q, rows_by_seq, k, v, table, heads, kv_heads, hd, window)
+        r = 0
+        for s, (p0, cnt) in enumerate(rows_by_seq):
+            T = p0 + cnt
+            qq = np.zeros((T, heads, hd), dtype=np.float32)
+            qq[p0:] = q[r:r + cnt]
+            want = P.attention(qq, seq_k[s][:T], seq_v[s][:T], exp="det", window=window)[p0:]
+            assert_same_bits(got[r:r + cnt], want, f"sequence {s} rows {p0}..{T - 1}")
+            r += cnt
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page", [(8, 2, 64, 16), (8, 8, 16, 16), (4, 4, 48, 8), (8, 4, 128, 4), (6, 2, 96, 64)])
+def test_f32_attention_of_many_single_rows_by_pages(heads, kv_heads, hd, page):
+    """A decode step with (row, head) pairs enough for every SM takes the form that brings the
+    values page by page: same bits as the plain attention, at context lengths on and beside the
+    edges of pages and of tiles of 64 keys."""
+    rng = np.random.default_rng(heads + hd + page)
+    lens = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 200, 255, 256, 257, 300, 64 * 5, 64 * 5 + 1, 333, 31, 33, 48,
+            100, 191, 192, 193, 7, 70, 140, 210, 280, 350, 420, 21, 42, 84, 168, 336]
+    assert len(lens) * heads >= 148
+    k, v, table, seq_k, seq_v = _paged(rng, lens, kv_heads, hd, page)
+    rows_by_seq = [(n - 1, 1) for n in lens]
+    q = rnd(rng, len(lens), heads, hd)
+    got, _, _ = _run_attention("float32", q, rows_by_seq, k, v, table, heads, kv_heads, hd, 0)
+    for s, n in enumerate(lens):
+        qq = np.zeros((n, heads, hd), dtype=np.float32)
+        qq[n - 1] = q[s]
+        want = P.attention(qq, seq_k[s], seq_v[s], exp="det")[n - 1]
+        assert_same_bits(got[s], want, f"sequence {s} of {n} keys")
+    assert not _ops("float32").device_failure()
+
+
+def test_f32_attention_finds_a_far_key_and_the_window_edge():
+    """One key among hundreds carries the weight (its score stands out), once far back and once
+    just inside or just outside the window: random inputs would hide a wrong key range."""
+    heads, kv_heads, hd, page, L = 2, 1, 64, 16, 600
+    rng = np.random.default_rng(4)
+    for far, window, inside in ((3, 0, True), (L - 100, 100, True), (L - 101, 100, False), (L - 17, 0, True)):
+        k, v, table, seq_k, seq_v = _paged(rng, [L], kv_heads, hd, page)
+        q = rnd(rng, 16, heads, hd) * 0.1
+        blk, slot = table[0, far // page], far % page
+        k[blk, 0, slot] = 160.0 * q[15, 0] / np.linalg.norm(q[15, 0])   # stands out for the last row, head 0
+        v[blk, 0, slot] = 100.0
+        seq_k[0][far] = k[blk, 0, slot]
+        seq_v[0][far] = v[blk, 0, slot]
+        got, _, _ = _run_attention("float32", q, [(L - 16, 16)], k, v, table, heads, kv_heads, hd, window)
+        qq = np.zeros((L, heads, hd), dtype=np.float32)
+        qq[L - 16:] = q
+        want = P.attention(qq, seq_k[0], seq_v[0], exp="det", window=window)[L - 16:]
+        assert_same_bits(got, want, f"far key {far}, window {window}")
+        assert (np.abs(want[15, 0]).max() > 50.0) == inside
 
 
 @pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(4, 2, 16, 16, 0), (3, 1, 32, 8, 0), (5, 5, 48, 16, 0),
