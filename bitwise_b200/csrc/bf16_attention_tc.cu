@@ -1,4 +1,4 @@
-// Prefill attention on the fifth-generation tensor cores, for head size 64.
+// Prefill attention on the fifth-generation tensor cores, for head sizes 64 and 128.
 //
 // Same arithmetic, in the same order, as attention_whole_kernel / attention_split_kernel in
 // bf16_attention.cu (key tiles of 64 at fixed positions; per tile and row the maximum, the sum
@@ -13,8 +13,13 @@
 //              maximum, weights, sum; write the bfloat16 weights as the next A operand into
 //              shared memory; later read the O_t row and merge it into the running state in
 //              registers; finally normalise and store
-// Two blocks share an SM (256 tensor-memory columns and about 100 KB each), so one block's
-// softmax overlaps the other's MMAs. Every mbarrier wait is bounded (see bf16_gemm_tc.cu).
+// A head of 128 is two pieces of 64 along d: Q, K and V tiles are kept piece by piece (a row of
+// a piece is one 128-byte swizzled line), the scores add up over the pieces' k-steps in order,
+// and the output takes one MMA per piece (64 columns of the O buffer each).
+// At head size 64 two blocks share an SM (256 tensor-memory columns and about 100 KB each), so
+// one block's softmax overlaps the other's MMAs; at 128 a block has the SM to itself (384 of
+// the 512 columns, 170 KB) and overlaps its own stages. Every mbarrier wait is bounded
+// (bw_common.cuh).
 #include <cuda.h>
 
 #include "bw_common.cuh"
@@ -23,19 +28,23 @@
 #error "compile with -DBW_HEAD_DIM=<head size>"
 #endif
 
-#if BW_HEAD_DIM == 64
+#if BW_HEAD_DIM == 64 || BW_HEAD_DIM == 128
 
 namespace {
 
-constexpr int HD = 64;
+constexpr int HD = BW_HEAD_DIM;
+constexpr int kPieces = HD / 64;  // 64-wide pieces of a head along d
 constexpr int kTileM = 128;   // stacked rows per block
 constexpr int kTileKV = 64;   // keys per tile
 constexpr int kStages = 3;    // key/value tiles in flight
 constexpr int kThreads = 192;
-constexpr int kQBytes = kTileM * 128;          // 16 KB
-constexpr int kKBytes = kTileKV * 128;         // 8 KB
+constexpr int kQPiece = kTileM * 128;          // 16 KB: one piece of the Q tile
+constexpr int kKPiece = kTileKV * 128;         // 8 KB: one piece of a K (or V) tile
+constexpr int kQBytes = kPieces * kQPiece;
+constexpr int kKBytes = kPieces * kKPiece;
 constexpr int kPBytes = kTileM * 128;          // 16 KB per weight buffer
-constexpr int kTmemCols = 256;                 // S0 S1 O0 O1, 64 columns each
+constexpr int kOCol = 128;                     // S0 S1 at columns 0 and 64, O0 O1 at 128 and 128 + HD
+constexpr int kTmemCols = HD == 64 ? 256 : 512;
 
 struct __align__(8) Barriers {
   uint64_t q_full;
@@ -139,7 +148,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sq = base;
-  unsigned char* skv = sq + kQBytes;                    // stage s: K at skv + s * 16 KB, V 8 KB behind
+  unsigned char* skv = sq + kQBytes;                    // stage s: K at skv + s * 2 * kKBytes, V kKBytes behind
   unsigned char* sp = skv + kStages * 2 * kKBytes;      // two weight buffers
   Barriers* bars = reinterpret_cast<Barriers*>(sp + 2 * kPBytes);
   int* spages = reinterpret_cast<int*>(bars + 1);
@@ -198,7 +207,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncwarp();
     if (lane == 0) {
       mbar_expect_tx(&bars->q_full, kQBytes);
-      tma_load_4d(sq, &map_q, 0, 0, g, row0, &bars->q_full);
+      for (int i = 0; i < kPieces; ++i) tma_load_4d(sq + i * kQPiece, &map_q, 64 * i, 0, g, row0, &bars->q_full);
       for (int t = 0; t < ntiles; ++t) {
         const int s = t % kStages;
         if (t >= kStages && !mbar_wait(&bars->kv_empty[s], ((t / kStages) - 1) & 1, failed)) break;
@@ -210,8 +219,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           // pages wholly beyond the last key are not in the table: any valid page will do, its keys are masked
           const int pi = min(j / page, last_page) - first_page;
           const int blk = pi < staged ? spages[pi] : table[first_page + pi];
-          tma_load_4d(k + pg * page * 128, &map_k, 0, 0, g, blk, &bars->kv_full[s]);
-          tma_load_4d(k + kKBytes + pg * page * 128, &map_v, 0, 0, g, blk, &bars->kv_full[s]);
+          for (int i = 0; i < kPieces; ++i) {
+            tma_load_4d(k + i * kKPiece + pg * page * 128, &map_k, 64 * i, 0, g, blk, &bars->kv_full[s]);
+            tma_load_4d(k + kKBytes + i * kKPiece + pg * page * 128, &map_v, 64 * i, 0, g, blk, &bars->kv_full[s]);
+          }
         }
       }
     }
@@ -219,15 +230,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (lane == 0) {
       bool ok = mbar_wait(&bars->q_full, 0, failed);
       fence_after_sync();
-      const uint64_t qdesc = make_desc(smem_u32(sq));
+      const uint32_t q_addr = smem_u32(sq);
       auto issue_qk = [&](int t) -> bool {
         const int s = t % kStages, b = t & 1;
         if (!mbar_wait(&bars->kv_full[s], (t / kStages) & 1, failed)) return false;
         if (t >= 2 && !mbar_wait(&bars->s_empty[b], ((t >> 1) - 1) & 1, failed)) return false;
         fence_after_sync();
-        const uint64_t kdesc = make_desc(smem_u32(skv + s * 2 * kKBytes));
+        const uint32_t k_addr = smem_u32(skv + s * 2 * kKBytes);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma(tmem_base + b * 64, qdesc + 2 * k, kdesc + 2 * k, kDescQK, k > 0 ? 1u : 0u);
+        for (int i = 0; i < kPieces; ++i) {  // d ascending: piece after piece, 16 values a step
+          const uint64_t qdesc = make_desc(q_addr + i * kQPiece), kdesc = make_desc(k_addr + i * kKPiece);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma(tmem_base + b * 64, qdesc + 2 * k, kdesc + 2 * k, kDescQK, (i | k) > 0 ? 1u : 0u);
+        }
         umma_commit(&bars->s_full[b]);
         return true;
       };
@@ -240,10 +255,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (t >= 2 && !mbar_wait(&bars->o_empty[b], ((t >> 1) - 1) & 1, failed)) break;
         fence_after_sync();
         const uint64_t pdesc = make_desc(smem_u32(sp + b * kPBytes));
-        const uint64_t vdesc = make_desc(smem_u32(skv + s * 2 * kKBytes + kKBytes));
+        const uint32_t v_addr = smem_u32(skv + s * 2 * kKBytes + kKBytes);
 #pragma unroll
-        for (int k = 0; k < kTileKV / 16; ++k)  // 16 keys: 32 bytes along a row of P, two 8-key groups (2048 bytes) of V
-          umma(tmem_base + 128 + b * 64, pdesc + 2 * k, vdesc + 128 * k, kDescPV, k > 0 ? 1u : 0u);
+        for (int i = 0; i < kPieces; ++i) {  // 64 output columns per piece of V
+          const uint64_t vdesc = make_desc(v_addr + i * kKPiece);
+#pragma unroll
+          for (int k = 0; k < kTileKV / 16; ++k)  // 16 keys: 32 bytes along a row of P, two 8-key groups (2048 bytes) of V
+            umma(tmem_base + kOCol + b * HD + 64 * i, pdesc + 2 * k, vdesc + 128 * k, kDescPV, k > 0 ? 1u : 0u);
+        }
         umma_commit(&bars->o_full[b]);
         umma_commit(&bars->kv_empty[s]);
       }
@@ -334,11 +353,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const MergeWeights w = merge_weights(M, prev_max);
         M = w.mx;
         L = merge_value(L, prev_sum, w);
-        {
-          float v[HD];
-          tmem_ld64(lane_addr + 128 + pb * 64, v);
 #pragma unroll
-          for (int i = 0; i < HD; ++i) o_tot[i] = merge_value(o_tot[i], v[i], w);
+        for (int pc = 0; pc < kPieces; ++pc) {
+          float v[64];
+          tmem_ld64(lane_addr + kOCol + pb * HD + 64 * pc, v);
+#pragma unroll
+          for (int i = 0; i < 64; ++i) o_tot[64 * pc + i] = merge_value(o_tot[64 * pc + i], v[i], w);
         }
         fence_before_sync();
         __syncwarp();
@@ -354,11 +374,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const MergeWeights w = merge_weights(M, prev_max);
         M = w.mx;
         L = merge_value(L, prev_sum, w);
-        {
-          float v[HD];
-          tmem_ld64(lane_addr + 128 + pb * 64, v);
 #pragma unroll
-          for (int i = 0; i < HD; ++i) o_tot[i] = merge_value(o_tot[i], v[i], w);
+        for (int pc = 0; pc < kPieces; ++pc) {
+          float v[64];
+          tmem_ld64(lane_addr + kOCol + pb * HD + 64 * pc, v);
+#pragma unroll
+          for (int i = 0; i < 64; ++i) o_tot[64 * pc + i] = merge_value(o_tot[64 * pc + i], v[i], w);
         }
       } else {
         ok = false;
@@ -416,7 +437,7 @@ bool make_map4(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], 
 
 }  // namespace
 
-// Query rows per block, or 0 when this kernel cannot take the shape: head size 64, a page size
+// Query rows per block, or 0 when this kernel cannot take the shape: head size 64 or 128, a page size
 // that divides 64, a group of heads that divides 128, rows that start on 16 bytes.
 BW_API int bw_bf16_attention_tc_tile_rows(int heads, int kv_heads, int hd, int page, int q_stride) {
   if (hd != HD || kv_heads <= 0 || heads % kv_heads) return 0;
@@ -458,7 +479,7 @@ BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __
     const cuuint64_t dims[4] = {HD, static_cast<cuuint64_t>(group), static_cast<cuuint64_t>(kv_heads),
                                 static_cast<cuuint64_t>(n)};
     const cuuint64_t strides[3] = {HD * 2, static_cast<cuuint64_t>(group) * HD * 2, static_cast<cuuint64_t>(q_stride) * 2};
-    const cuuint32_t box[4] = {HD, static_cast<cuuint32_t>(group), 1, static_cast<cuuint32_t>(kTileM / group)};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(group), 1, static_cast<cuuint32_t>(kTileM / group)};  // one piece
     if (!make_map4(&map_q, qkv, dims, strides, box)) {
       bw::set_error("attention (tcgen05): cuTensorMapEncodeTiled refused the query map");
       return -1;
@@ -469,7 +490,7 @@ BW_API int bw_bf16_attention_tc(const __nv_bfloat16* qkv, int q_stride, const __
                                 static_cast<cuuint64_t>(num_pages)};
     const cuuint64_t strides[3] = {HD * 2, static_cast<cuuint64_t>(page) * HD * 2,
                                    static_cast<cuuint64_t>(kv_heads) * page * HD * 2};
-    const cuuint32_t box[4] = {HD, static_cast<cuuint32_t>(page), 1, 1};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(page), 1, 1};  // one piece of a page
     if (!make_map4(&map_k, kcache, dims, strides, box) || !make_map4(&map_v, vcache, dims, strides, box)) {
       bw::set_error("attention (tcgen05): cuTensorMapEncodeTiled refused the cache map");
       return -1;

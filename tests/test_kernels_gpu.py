@@ -675,12 +675,16 @@ def test_bf16_attention_streaming_decode_kernel_gives_the_same_bits():
 
 
 def test_bf16_attention_tensor_core_generations_agree_bit_for_bit():
-    """The tcgen05 prefill kernel (head size 64) and the mma.sync kernels give the same bits:
-    whole prompts, late portions, with a window, grouped heads, several sequences in a step."""
+    """The tcgen05 prefill kernel (head sizes 64 and 128) and the mma.sync kernels give the same
+    bits: whole prompts, late portions, with a window, grouped heads, several sequences in a step."""
     rng = np.random.default_rng(16)
     ops = _ops("bfloat16")
-    for heads, kv_heads, page, window in ((4, 4, 16, 0), (8, 2, 16, 0), (2, 1, 32, 0), (4, 2, 64, 90), (16, 2, 16, 0)):
-        hd = 64
+    for hd, heads, kv_heads, page, window in ((64, 4, 4, 16, 0), (64, 8, 2, 16, 0), (64, 2, 1, 32, 0), (64, 4, 2, 64, 90),
+                                              (64, 16, 2, 16, 0), (128, 4, 1, 16, 0), (128, 2, 2, 32, 0), (128, 8, 2, 16, 75),
+                                              (128, 3, 1, 8, 0)):
+        lib = ops._attention_lib(hd)
+        rows_tc = lib.bw_bf16_attention_tc_tile_rows(heads, kv_heads, hd, page, (heads + 2 * kv_heads) * hd)
+        assert (rows_tc > 0) == (128 % (heads // kv_heads) == 0), "the tcgen05 kernel takes groups that divide 128"
         lens = [333, 70, 129]
         k, v, table, _, _ = _paged(rng, lens, kv_heads, hd, page)
         k, v = bf(k), bf(v)
@@ -693,7 +697,7 @@ def test_bf16_attention_tensor_core_generations_agree_bit_for_bit():
             old, _, _ = _run_bf16_attention(q, rows_by_seq, k, v, table, heads, kv_heads, hd, window)
         finally:
             ops.legacy_attention = False
-        assert_same_bits(new, old, f"heads {heads}/{kv_heads} page {page} window {window}")
+        assert_same_bits(new, old, f"head size {hd} heads {heads}/{kv_heads} page {page} window {window}")
     assert not ops.device_failure()
 
 
