@@ -521,9 +521,19 @@ def run_serve(model, title, args, pk):
             dt = time.perf_counter() - t0
             made = sum(len(r) for r in res)
             out = {"value": made / dt, "seconds": dt, "steps": eng.stats.steps, "generated": made,
-                   "prompt_tokens": int(plen.sum()), "launches": model.ops.launches}
+                   "prompt_tokens": int(plen.sum()), "launches": model.ops.launches,
+                   "graph_replays": eng.stepper.graph_replays, "preemptions": eng.stats.preemptions}
             del eng
             torch.cuda.empty_cache()
+    # what the crowd generated must be what each request generates alone (the reference's oracle,
+    # sim/simulate.cpp:102-118): five of the requests are run again, each on an idle engine
+    checked, wrong = 0, 0
+    for i in (0, 13, 27, 41, 63):
+        solo = Engine(model, EngineConfig(num_blocks=(int(plen[i]) + int(olen[i]) + page) // page + 1, block_size=page,
+                                          max_batched_tokens=512, max_num_seqs=1, fingerprint_logits=False))
+        checked += 1
+        wrong += int(solo.generate([prompts[i]], [params[i]])[0] != res[i])
+        del solo
     return {
         "metric": f"generated tok/s, 64 mixed requests under a 512-token budget ({title})",
         "value": round(out["value"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": out["steps"], "warmup": 1,
@@ -535,7 +545,9 @@ def run_serve(model, title, args, pk):
                    "intermediate": c.intermediate_size, "vocab": c.vocab_size, "requests": n,
                    "prompt_tokens": out["prompt_tokens"], "generated_tokens": out["generated"],
                    "token_budget": 512, "page_size": page, "parallelism": "single GPU",
-                   "timing": "host clock around Engine.generate, second of two passes"},
+                   "timing": "host clock around Engine.generate, second of two passes",
+                   "steps_replayed_as_graphs": out["graph_replays"], "preemptions": out["preemptions"],
+                   "requests_checked_against_solo_runs": checked, "requests_that_differ": wrong},
         "clocks": clocks.summary(), "gpu_launches": out["launches"],
         "total_tokens_per_s": round((out["prompt_tokens"] + out["generated"]) / out["seconds"], 1),
     }

@@ -7,6 +7,10 @@ group at once, as the reference's block id indexes every layer (src/model.h:69-7
 Slot state is ``[slots, *shape]`` per entry that asks for it, plus one 64-bit word per
 slot for the request's logits fingerprint.  Nothing is zeroed on reuse: reads are limited
 to the positions a request has written.
+
+Behind the pages and slots that the manager hands out lies one more of each
+(``pad_pages[g]``, ``pad_slot``): where the rows of a step that fills its batch up to a round
+size write and read, so that they touch nothing of a request.
 """
 from __future__ import annotations
 
@@ -36,14 +40,16 @@ class CacheStorage:
         for e, need in enumerate(needs):
             if isinstance(need, PagedKVNeed):
                 pages = pages_per_group[self.group_of_entry[e]]
-                shape = (max(pages, 1), need.kv_heads, page_size, need.head_dim)
+                shape = (max(pages, 1) + 1, need.kv_heads, page_size, need.head_dim)
                 self.k[e] = torch.zeros(shape, dtype=dtype, device=device)
                 self.v[e] = torch.zeros(shape, dtype=dtype, device=device)
             elif isinstance(need, SlotStateNeed):
-                self.state[e] = torch.zeros((max(num_slots, 1),) + tuple(need.shape), dtype=need.dtype, device=device)
+                self.state[e] = torch.zeros((max(num_slots, 1) + 1,) + tuple(need.shape), dtype=need.dtype, device=device)
             elif need is not None:
                 raise TypeError(f"cache entry {e}: unknown need {need!r}")
-        self.fingerprints = torch.zeros(max(num_slots, 1), dtype=torch.int64, device=device)
+        self.fingerprints = torch.zeros(max(num_slots, 1) + 1, dtype=torch.int64, device=device)
+        self.pad_pages = [max(int(p), 1) for p in pages_per_group]  # per group: the page no request ever holds
+        self.pad_slot = max(num_slots, 1)
 
     def nbytes(self) -> int:
         ts = [t for t in self.k + self.v + self.state if t is not None]

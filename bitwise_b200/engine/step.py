@@ -91,6 +91,11 @@ class Stepper:
 
     GRAPH_MAX_ROWS = 256   # steps up to this many rows are replayed as CUDA graphs
     GRAPH_CACHE = 256      # graphs kept (one per batch shape and bound on the context length)
+    # A decode step of more than PAD_FROM rows is filled up to a multiple of PAD_TO with rows of
+    # no request (token 0 at position 0 of a page and slot that no request ever holds), so that
+    # batches whose size drifts as requests come and go meet a graph captured earlier.
+    PAD_TO = 8
+    PAD_FROM = 8
 
     def __init__(self, model, manager: CacheManager, storage: CacheStorage, ops, max_rows: int,
                  max_seqs: int, max_tokens_per_request: int, use_graphs: Optional[bool] = None):
@@ -99,7 +104,9 @@ class Stepper:
         self.max_rows, self.max_seqs = max_rows, max_seqs
         page = manager.page_size
         mb = (max_tokens_per_request + page - 1) // page
-        self.layout = _Layout(max_rows, max_seqs, [mb] * len(manager.groups), query_tile_rows(model, ops))
+        pad = self.PAD_TO - 1
+        self._fill_seq0 = max_seqs + 1  # first sequence index of the filling rows (behind the end mark of seq_row0)
+        self.layout = _Layout(max_rows + pad, max_seqs + 1 + pad, [mb] * len(manager.groups), query_tile_rows(model, ops))
         pin = self.device is not None and torch.device(self.device).type == "cuda"
         self.host = torch.zeros(self.layout.total, dtype=torch.int32, pin_memory=pin)
         self._host_np = self.host.numpy()
@@ -114,8 +121,17 @@ class Stepper:
         self._table_offsets = (ctypes.c_int * max(groups, 1))(*self.layout.tables)
         self._max_blocks_buf = (ctypes.c_int * max(groups, 1))(*self.layout.max_blocks)
         self._views: Dict[tuple, dict] = {}        # step sizes -> views of the device buffer
+        # the sequences of filling rows sit behind the real ones: their rows of the block tables
+        # name the spare page, their slot is the spare slot, and nothing else ever writes there
+        L = self.layout
+        f0 = self._fill_seq0
+        for g, off in enumerate(L.tables):
+            rows0 = off + f0 * L.max_blocks[g]
+            self._host_np[rows0:rows0 + pad * L.max_blocks[g]] = storage.pad_pages[g] if hasattr(storage, "pad_pages") else 0
+        self._host_np[L.seq_slot + f0:L.seq_slot + f0 + pad] = getattr(storage, "pad_slot", 0)
+        self._host_np[L.seq_pos0 + f0:L.seq_pos0 + f0 + pad] = 0
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
-        self.workspace = Workspace(self.device, max_rows)
+        self.workspace = Workspace(self.device, max_rows + pad)
         self.vocab = model.head.vocab
         model.reserve_positions(mb * page)
         self.steps = 0
@@ -219,6 +235,18 @@ class Stepper:
         # under which a step's graph is kept.  Rows are bounded on the device by their own position.
         granule = self.key_granule
         max_keys = (max_keys + granule - 1) // granule * granule
+        # filling rows (see PAD_TO): one row each of sequences _fill_seq0, _fill_seq0 + 1, ...
+        n_real, c_real = n, len(logit_rows)
+        fill = 0
+        if self.use_graphs and n == num_seqs and self.PAD_FROM < n <= self.GRAPH_MAX_ROWS and hasattr(self.storage, "pad_pages"):
+            fill = (-n) % self.PAD_TO
+            for i in range(fill):
+                all_tokens.append(0)
+                all_pos.append(0)
+                all_row_seq.append(self._fill_seq0 + i)
+                h[L.seq_row0 + self._fill_seq0 + i] = n
+                logit_rows.append(n)
+                n += 1
         h[L.tokens:L.tokens + n] = all_tokens
         h[L.pos:L.pos + n] = all_pos
         h[L.row_seq:L.row_seq + n] = all_row_seq
@@ -239,6 +267,8 @@ class Stepper:
                     listed.append((-(seq_pos0[s] + a + rows_here), s, r0 + a, rows_here))
             if len(listed) > 1:
                 listed.sort()
+            for i in range(fill):  # one key each: they come last
+                listed.append((-1, self._fill_seq0 + i, n_real + i, 1))
             t = len(listed)
             if t:
                 h[o_seq:o_seq + t] = [x[1] for x in listed]
@@ -274,6 +304,7 @@ class Stepper:
             seq_pos0=views["seq_pos0"], seq_slot=views["seq_slot"], logit_rows=views["logit_rows"],
             num_logit_rows=c, max_keys=max_keys,
             host_seq_rows=seq_rows, host_seq_pos0=seq_pos0, host_seq_slot=seq_slot)
+        ctx.wanted_rows = c_real  # logits rows that belong to requests (the rest belong to filling rows)
         ctx.tile_sets = views["tile_sets"]
         ctx.tile_seq, ctx.tile_row0, ctx.tile_rows, ctx.num_tiles = ctx.tile_sets[first_tr]
         ctx.block_tables = views["block_tables"]
@@ -292,8 +323,9 @@ class Stepper:
         if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:
             # everything a launcher computes on the host is a function of these: the step's sizes,
             # the (rounded) bound on the context and the numbers of query tiles
-            key = (ctx.n, ctx.num_seqs, ctx.num_logit_rows, ctx.max_keys) + tuple(
-                t[3] for t in ctx.tile_sets.values())
+            # (a step with filling rows is the same step whatever share of its rows is filling)
+            seqs = ctx.num_seqs if ctx.wanted_rows == ctx.num_logit_rows else -1
+            key = (ctx.n, seqs, ctx.num_logit_rows, ctx.max_keys) + tuple(t[3] for t in ctx.tile_sets.values())
         if key is not None and key in self._graphs:
             graph, logits, launches = self._graphs[key]
             graph.replay()
@@ -324,6 +356,8 @@ class Stepper:
             self.manager.advance(rid, length)
         self.steps += 1
         self.last_context = ctx
+        if logits is not None and ctx.wanted_rows < ctx.num_logit_rows:
+            return logits[:ctx.wanted_rows] if ctx.wanted_rows else None
         return logits
 
     def finish(self, rid: Hashable) -> None:

@@ -124,6 +124,7 @@ class StepContext:
     tile_sets: Dict[int, tuple] = field(default_factory=dict)
     block_tables: List[torch.Tensor] = field(default_factory=list)
     cache_views: List[object] = field(default_factory=list)  # one per cache entry, as the model's forward takes them
+    wanted_rows: int = 0         # of num_logit_rows, how many belong to requests (the stepper may add rows of no request)
 
     def query_tiles(self, rows_per_tile: int):
         """(tile_seq, tile_row0, tile_rows, count) for tiles of at most ``rows_per_tile`` rows."""
