@@ -113,6 +113,22 @@ BW_API int bw_embed_rows(const void* table, int table_is_bf16, const int* tokens
 }
 
 // ---------------------------------------------------------------------------------------
+// Tokens that the step before sampled and the host has not read yet go from the sampler's
+// output straight into this step's token list: tokens[rows[i]] = values[src[i]].
+__global__ void patch_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ rows, const int* __restrict__ src,
+                                    const int* __restrict__ values, int count) {
+  bw::pdl_enter();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) tokens[rows[i]] = values[src[i]];
+}
+
+BW_API int bw_patch_tokens(int* tokens, const int* rows, const int* src, const int* values, int count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  bw::launch_pdl(patch_tokens_kernel, dim3((count + 127) / 128), dim3(128), 0, stream, tokens, rows, src, values, count);
+  return bw::launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
 // Sampling. One block per logits row.
 //   temperature <= 0: the first index of the maximum (src/engine.cpp:40-45).
 //   otherwise: w_i = exp((l_i - max) / T) in 32-bit, total and running sums in 64-bit in
@@ -237,7 +253,19 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 
 // One warp per row: the lanes fetch 32 consecutive words at a time (one coalesced read, the
 // next group already on its way) and every lane runs the same chain over them, taking word j
-// from lane j; no lane waits for memory inside the chain.
+// from lane j; no lane waits for memory inside the chain. The chain itself is written in 32-bit
+// halves: the prime is 2^40 + 0x1B3, so with t = h ^ w the new low half is t.lo * 0x1B3 and the
+// new high half hi(t.lo * 0x1B3) + t.hi * 0x1B3 + (t.lo << 8): two dependent instructions a
+// word on each half instead of the chain of a general 64-bit product.
+struct Hash64 {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ void hash_step(Hash64& h, uint32_t w_lo, uint32_t w_hi) {
+  const uint32_t t_lo = h.lo ^ w_lo, t_hi = h.hi ^ w_hi;
+  h.lo = t_lo * 0x1B3u;
+  h.hi = __umulhi(t_lo, 0x1B3u) + (t_lo << 8) + t_hi * 0x1B3u;
+}
+
 __global__ void __launch_bounds__(32)
 fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab, const int* __restrict__ slot,
                         unsigned long long* __restrict__ state) {
@@ -245,38 +273,36 @@ fingerprint_rows_kernel(const float* __restrict__ logits, int rows, int vocab, c
   const int r = blockIdx.x, lane = threadIdx.x;
   if (r >= rows) return;
   const uint32_t* w = reinterpret_cast<const uint32_t*>(logits + static_cast<size_t>(r) * vocab);
-  uint64_t h = state[slot[r]];
-  const uint64_t prime = 1099511628211ull;
+  const uint64_t h0 = state[slot[r]];
+  Hash64 h{static_cast<uint32_t>(h0), static_cast<uint32_t>(h0 >> 32)};
   const int words = vocab / 2;  // whole 8-byte words
-  auto fetch = [&](int base) -> uint64_t {
+  auto fetch = [&](int base) -> uint2 {
     const int i = base + lane;
-    if (i >= words) return 0;
-    const uint2 v = *reinterpret_cast<const uint2*>(w + 2 * i);  // rows of an even vocabulary start on 8 bytes
-    return static_cast<uint64_t>(v.x) | (static_cast<uint64_t>(v.y) << 32);
+    if (i >= words) return make_uint2(0u, 0u);
+    return *reinterpret_cast<const uint2*>(w + 2 * i);  // rows of an even vocabulary start on 8 bytes
   };
   const bool aligned8 = (reinterpret_cast<uintptr_t>(w) & 7) == 0;
   if (aligned8) {
-    uint64_t cur = fetch(0);
+    uint2 cur = fetch(0);
     for (int base = 0; base < words; base += 32) {
-      const uint64_t nxt = fetch(base + 32);
+      const uint2 nxt = fetch(base + 32);
       const int count = min(32, words - base);
       if (count == 32) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) h = (h ^ __shfl_sync(0xffffffffu, cur, j)) * prime;
+        for (int j = 0; j < 32; ++j) hash_step(h, __shfl_sync(0xffffffffu, cur.x, j), __shfl_sync(0xffffffffu, cur.y, j));
       } else {
-        for (int j = 0; j < count; ++j) h = (h ^ __shfl_sync(0xffffffffu, cur, j)) * prime;
+        for (int j = 0; j < count; ++j) hash_step(h, __shfl_sync(0xffffffffu, cur.x, j), __shfl_sync(0xffffffffu, cur.y, j));
       }
       cur = nxt;
     }
   } else {
-    for (int i = 0; i < words; ++i)
-      h = (h ^ (static_cast<uint64_t>(w[2 * i]) | (static_cast<uint64_t>(w[2 * i + 1]) << 32))) * prime;
+    for (int i = 0; i < words; ++i) hash_step(h, w[2 * i], w[2 * i + 1]);
   }
   if (vocab & 1) {
     const uint32_t v = w[vocab - 1];
-    for (int b = 0; b < 4; ++b) h = (h ^ ((v >> (8 * b)) & 0xffu)) * prime;
+    for (int b = 0; b < 4; ++b) hash_step(h, (v >> (8 * b)) & 0xffu, 0u);
   }
-  if (lane == 0) state[slot[r]] = mix64(h);
+  if (lane == 0) state[slot[r]] = mix64(static_cast<uint64_t>(h.lo) | (static_cast<uint64_t>(h.hi) << 32));
 }
 
 BW_API int bw_fingerprint_rows(const float* logits, int rows, int vocab, const int* slot,

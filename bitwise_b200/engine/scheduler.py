@@ -47,6 +47,13 @@ class Sequence:
     computed: int = 0          # tokens whose keys/values are in the cache
     running: bool = False
     done: bool = False
+    # An engine that runs a step ahead of its reads: the index in ``tokens`` of a sampled token
+    # that the host has not read yet (a stand-in until then; -1: none), where it lies in the
+    # sampler's output, and whether the request has left the scheduler because its last token
+    # is sampled (it is closed when that token is read).
+    pending: int = -1
+    pending_src: int = -1
+    closing: bool = False
 
     @property
     def generated(self) -> int:

@@ -78,6 +78,8 @@ class _Layout:
         self.seq_pos0 = take(max_seqs)
         self.seq_slot = take(max_seqs)
         self.logit_rows = take(max_rows)
+        self.patch_rows = take(max_seqs)   # rows whose token the step before sampled, and where it lies
+        self.patch_src = take(max_seqs)
         self.tiles = {}
         for tr in self.tile_rows:
             cap = max_rows // tr + max_seqs + 1
@@ -157,9 +159,12 @@ class Stepper:
     def _section(self, t: torch.Tensor, start: int, n: int) -> torch.Tensor:
         return t[start:start + n]
 
-    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+    def prepare(self, entries: Sequence[StepEntry], patches: Sequence[Tuple[int, int]] = (),
+                patch_values: Optional[torch.Tensor] = None) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
         """Allocate pages, fill the packed buffer, copy it, and return the step's context
-        together with (request, new length) for the bookkeeping after the run."""
+        together with (request, new length) for the bookkeeping after the run.  ``patches``:
+        (row, index) pairs: the token of that row is ``patch_values[index]`` on the device (what
+        the step before sampled and the host has not read)."""
         L, mgr = self.layout, self.manager
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -184,7 +189,7 @@ class Stepper:
             if rows_total > self.max_rows:
                 raise StepError(f"step of more than {self.max_rows} rows")
             toks = e.tokens
-            if min(toks) < 0 or max(toks) >= vocab:
+            if min(toks) < 0 or max(toks) >= vocab:  # (a token still on the device stands as 0 here)
                 bad = next(t for t in toks if not (0 <= t < vocab))
                 raise StepError(f"token id {bad} outside the vocabulary of {vocab}")
             for w in e.want:
@@ -275,10 +280,17 @@ class Stepper:
                 h[o_row0:o_row0 + t] = [x[2] for x in listed]
                 h[o_rows:o_rows + t] = [x[3] for x in listed]
             tiles[tr] = t
+        if patches:
+            h[L.patch_rows:L.patch_rows + len(patches)] = [r for r, _ in patches]
+            h[L.patch_src:L.patch_src + len(patches)] = [i for _, i in patches]
         self.dev.copy_(self.host, non_blocking=True)
         if self._copy_done is not None:
             self._copy_done.record()
             self._copy_pending = True
+        if patches:
+            d = self.dev
+            self.ops.patch_tokens(d[L.tokens:L.tokens + n], d[L.patch_rows:L.patch_rows + len(patches)],
+                                  d[L.patch_src:L.patch_src + len(patches)], patch_values, len(patches))
         self.h2d_bytes = self.host.numel() * 4
         # The views of the device buffer depend on the step's sizes only: steps of a shape seen
         # before take them from a small cache (slicing a tensor costs microseconds, a dozen each step).
@@ -314,10 +326,11 @@ class Stepper:
         return ctx, after
 
     # -- running -----------------------------------------------------------------------
-    def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def run(self, entries: Sequence[StepEntry], patches: Sequence[Tuple[int, int]] = (),
+            patch_values: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one step; returns float32 logits [wanted, vocab] on the device (a view of
         the stepper's buffer, valid until the next step) or None when nothing is wanted."""
-        ctx, after = self.prepare(entries)
+        ctx, after = self.prepare(entries, patches, patch_values)
         views = ctx.cache_views
         key = None
         if self.use_graphs and ctx.n <= self.GRAPH_MAX_ROWS:

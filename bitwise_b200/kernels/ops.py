@@ -130,6 +130,14 @@ class KernelOps:
         self._call("bw_embed_rows", _p(table), _c_int(int(table.dtype == torch.bfloat16)), _p(tokens), _p(out),
                    _c_int(n), _c_int(width), self._stream())
 
+    def patch_tokens(self, tokens: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, values: torch.Tensor,
+                     count: int) -> None:
+        """tokens[rows[i]] = values[src[i]] for i < count: tokens that the step before sampled go
+        into this step's token list on the device, unread by the host."""
+        for t_, what in ((tokens, "tokens"), (rows, "rows"), (src, "src"), (values, "values")):
+            _need(t_, torch.int32, "patch_tokens " + what)
+        self._call("bw_patch_tokens", _p(tokens), _p(rows), _p(src), _p(values), _c_int(count), self._stream())
+
     def sample_rows(self, logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
                     out_tokens: torch.Tensor) -> None:
         rows, vocab = logits.shape

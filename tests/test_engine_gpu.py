@@ -208,6 +208,51 @@ def test_engine_stops_on_a_raised_failure_word(tiny_folders):
     eng.add_request(prompt, sp)
     assert model.ops.selftest_bounded_wait(polls=2000) == 2   # a wait ran out somewhere on the device
     with pytest.raises(DeviceFailure):
-        eng.step()
+        for _ in range(3):   # an engine that runs a step ahead reads the word with the step's tokens, a call later
+            eng.step()
     assert not model.ops.device_failure()                     # read and cleared by the engine
     assert Engine(model, EngineConfig(num_blocks=8)).generate([prompt], sp) == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_a_step_ahead_changes_no_token(dtype, tiny_folders):
+    """The engine launches a step before it has read the tokens of the one before (they go from
+    the sampler into the next batch on the device).  Tokens, fingerprints, preemptions and the
+    end by an end-of-sequence token are those of the engine that reads every step at once."""
+    from bitwise_b200 import Engine, EngineConfig, SamplingParams
+    name = "tiny_b"
+    model = _model(tiny_folders[name], dtype)
+    prompts = [tiny_tokens(name, n, salt=70 + i) for i, n in enumerate((1, 9, 40, 100, 23, 64))]
+    params = [SamplingParams(0.0 if i % 2 else 0.9, 5 + i, 10 + 3 * i, True) for i in range(len(prompts))]
+
+    def run(lookahead, eos=None, blocks=10):
+        if eos is not None:
+            model.decoder.config = type(model.config).from_json(dict(model.config.to_json(), eos_token_id=eos))
+        eng = Engine(model, EngineConfig(num_blocks=blocks, max_batched_tokens=24, max_num_seqs=4, lookahead=lookahead))
+        assert eng._lookahead == lookahead
+        ids = [eng.add_request(p, q) for p, q in zip(prompts, params)]
+        steps = 0
+        while not eng.idle():
+            eng.step()
+            steps += 1
+            assert steps < 5000
+        assert eng.free_blocks == blocks and eng.manager.all_free()
+        return [(eng.result(i).tokens, eng.result(i).logits_fingerprint) for i in ids], eng.stats.preemptions
+
+    plain, preempted = run(False)
+    ahead, preempted_ahead = run(True)
+    assert ahead == plain and preempted > 0 and preempted_ahead == preempted
+    # a token that ends requests early: the most frequent one of the free runs
+    flat = [t for toks, _ in plain for t in toks]
+    eos = max(set(flat), key=flat.count)
+    old = model.config.eos_token_id
+    try:
+        stop = [SamplingParams(q.temperature, q.seed, q.max_new_tokens, False) for q in params]
+        params, keep = stop, params
+        a, _ = run(False, eos)
+        b, _ = run(True, eos)
+        params = keep
+    finally:
+        model.decoder.config = type(model.config).from_json(dict(model.config.to_json(), eos_token_id=old))
+    assert a == b
+    assert any(toks and toks[-1] == eos and len(toks) < q.max_new_tokens for (toks, _), q in zip(a, keep))
