@@ -17,17 +17,31 @@ namespace {
 // ---------------------------------------------------------------------------------------
 // RMSNorm: ss = dot16(x, x); inv = 1 / sqrt(ss / width + eps); y = (x * inv) * w
 // (src/kernels.cpp:264-271). One warp per output row; lanes 0..15 run the 16 chains.
+// The row is brought into shared memory by the whole warp first (whole lines, all loads in
+// flight together), so that the chains, which are what the time of a step of few rows hangs on,
+// read shared memory instead of waiting for global memory eight values at a time.
 constexpr int kNormWarps = 4;
+constexpr int kNormStaged = 4096;  // widths up to this are staged; wider rows are read in place
 
 __global__ void __launch_bounds__(kNormWarps * 32)
 rmsnorm_exact_kernel(const float* __restrict__ x, const float* __restrict__ w, float* y,
                      const int* __restrict__ rows, int n, int width, float eps) {
-  const int r = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
+  extern __shared__ __align__(16) float norm_rows[];  // [kNormWarps][width] when the width is staged
+  const int warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * (static_cast<int>(blockDim.x) >> 5) + warp;
   if (r >= n) return;
   const int lane = threadIdx.x & 31;
   const int src = rows ? rows[r] : r;
   const float* xr = x + static_cast<size_t>(src) * width;
   float* yr = y + static_cast<size_t>(r) * width;
+  const bool staged = width <= kNormStaged;
+  if (staged) {
+    float* mine = norm_rows + warp * width;
+#pragma unroll 16
+    for (int i = lane; i < width; i += 32) mine[i] = xr[i];
+    __syncwarp();
+    xr = mine;
+  }
   float acc = 0.0f;
   if (lane < 16) {
 #pragma unroll 8
@@ -42,7 +56,45 @@ rmsnorm_exact_kernel(const float* __restrict__ x, const float* __restrict__ w, f
   acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1, 16));
   const float ss = __shfl_sync(0xffffffffu, acc, 0);
   const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(width)), eps)));
+#pragma unroll 4
   for (int i = lane; i < width; i += 32) yr[i] = __fmul_rn(__fmul_rn(xr[i], inv), w[i]);
+}
+
+// The same for steps of few rows: a block per row. All threads bring the row into shared memory
+// (every load of the row in flight at once), lanes 0..15 of the first warp run the chains, all
+// threads write the result: the row's time is one trip to memory and the chain.
+constexpr int kNormRowThreads = 128;
+
+__global__ void __launch_bounds__(kNormRowThreads)
+rmsnorm_exact_row_kernel(const float* __restrict__ x, const float* __restrict__ w, float* y,
+                         const int* __restrict__ rows, int width, float eps) {
+  extern __shared__ __align__(16) float norm_row[];  // [width], then the scale
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * width;
+  float* yr = y + static_cast<size_t>(r) * width;
+#pragma unroll 8
+  for (int i = tid; i < width; i += kNormRowThreads) norm_row[i] = xr[i];
+  __syncthreads();
+  if (tid < 32) {
+    float acc = 0.0f;
+    if (tid < 16) {
+#pragma unroll 8
+      for (int i = tid; i < width; i += 16) {
+        const float v = norm_row[i];
+        acc = __fmaf_rn(v, v, acc);
+      }
+    }
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8, 16));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4, 16));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2, 16));
+    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1, 16));
+    if (tid == 0)
+      norm_row[width] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(acc, static_cast<float>(width)), eps)));
+  }
+  __syncthreads();
+  const float inv = norm_row[width];
+#pragma unroll 8
+  for (int i = tid; i < width; i += kNormRowThreads) yr[i] = __fmul_rn(__fmul_rn(norm_row[i], inv), w[i]);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -348,13 +400,29 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
   const bool rotate = cos_t != nullptr;  // a null table leaves q and k as they are
   const float* c = rotate ? cos_t + static_cast<size_t>(p) * half : nullptr;
   const float* s = rotate ? sin_t + static_cast<size_t>(p) * half : nullptr;
+  // A thread's pairs are read four at a time before any of them is written: the row is rotated
+  // in place, and a write between the reads would keep them from being in flight together.
   const int q_items = rotate ? heads * half : 0;
-  for (int it = threadIdx.x; it < q_items; it += blockDim.x) {
-    const int h = it / half, i = it - h * half;
-    float* v = row + h * hd;
-    const float x1 = v[i], x2 = v[i + half];
-    v[i] = __fsub_rn(__fmul_rn(x1, c[i]), __fmul_rn(x2, s[i]));
-    v[i + half] = __fadd_rn(__fmul_rn(x2, c[i]), __fmul_rn(x1, s[i]));
+  const int step = static_cast<int>(blockDim.x);
+  for (int it0 = threadIdx.x; it0 < q_items; it0 += 4 * step) {
+    float x1[4], x2[4], cc[4], ss[4];
+    int at[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int it = it0 + u * step;
+      at[u] = -1;
+      if (it < q_items) {
+        const int h = it / half, i = it - h * half;
+        at[u] = h * hd + i;
+        x1[u] = row[at[u]], x2[u] = row[at[u] + half], cc[u] = c[i], ss[u] = s[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (at[u] < 0) continue;
+      row[at[u]] = __fsub_rn(__fmul_rn(x1[u], cc[u]), __fmul_rn(x2[u], ss[u]));
+      row[at[u] + half] = __fadd_rn(__fmul_rn(x2[u], cc[u]), __fmul_rn(x1[u], ss[u]));
+    }
   }
   if (!write_kv) return;
   const int blk = block_table[static_cast<size_t>(row_seq[r]) * max_blocks + p / page];
@@ -362,14 +430,30 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
   const float* k = row + heads * hd;
   const float* vv = k + kv_heads * hd;
   const int k_items = kv_heads * half;
-  for (int it = threadIdx.x; it < k_items; it += blockDim.x) {
-    const int h = it / half, i = it - h * half;
-    const size_t dst = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd;
-    const float x1 = k[h * hd + i], x2 = k[h * hd + i + half];
-    kcache[dst + i] = rotate ? __fsub_rn(__fmul_rn(x1, c[i]), __fmul_rn(x2, s[i])) : x1;
-    kcache[dst + i + half] = rotate ? __fadd_rn(__fmul_rn(x2, c[i]), __fmul_rn(x1, s[i])) : x2;
-    vcache[dst + i] = vv[h * hd + i];
-    vcache[dst + i + half] = vv[h * hd + i + half];
+  for (int it0 = threadIdx.x; it0 < k_items; it0 += 4 * step) {
+    float x1[4], x2[4], v1[4], v2[4], cc[4], ss[4];
+    size_t dst[4];
+    bool ok[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int it = it0 + u * step;
+      ok[u] = it < k_items;
+      if (ok[u]) {
+        const int h = it / half, i = it - h * half;
+        dst[u] = ((static_cast<size_t>(blk) * kv_heads + h) * page + slot) * hd + i;
+        x1[u] = k[h * hd + i], x2[u] = k[h * hd + i + half];
+        v1[u] = vv[h * hd + i], v2[u] = vv[h * hd + i + half];
+        cc[u] = rotate ? c[i] : 1.0f, ss[u] = rotate ? s[i] : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (!ok[u]) continue;
+      kcache[dst[u]] = rotate ? __fsub_rn(__fmul_rn(x1[u], cc[u]), __fmul_rn(x2[u], ss[u])) : x1[u];
+      kcache[dst[u] + half] = rotate ? __fadd_rn(__fmul_rn(x2[u], cc[u]), __fmul_rn(x1[u], ss[u])) : x2[u];
+      vcache[dst[u]] = v1[u];
+      vcache[dst[u] + half] = v2[u];
+    }
   }
 }
 
@@ -953,8 +1037,21 @@ BW_API int bw_f32_rmsnorm(const float* x, const float* weight, float* y, const i
     bw::set_error("rmsnorm: width %d", width);
     return -1;
   }
-  rmsnorm_exact_kernel<<<(n + kNormWarps - 1) / kNormWarps, kNormWarps * 32, 0, stream>>>(x, weight, y, rows, n,
-                                                                                          width, eps);
+  const size_t smem = width <= kNormStaged ? static_cast<size_t>(kNormWarps) * width * sizeof(float) : 0;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kNormWarps * kNormStaged * static_cast<int>(sizeof(float)));
+    if (e != cudaSuccess) {
+      bw::set_error("rmsnorm: cannot raise shared memory: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    configured = true;
+  }
+  if (n <= 64 && width < 12000)  // few rows (a decode step): a block per row
+    rmsnorm_exact_row_kernel<<<n, kNormRowThreads, (width + 4) * sizeof(float), stream>>>(x, weight, y, rows, width, eps);
+  else
+    rmsnorm_exact_kernel<<<(n + kNormWarps - 1) / kNormWarps, kNormWarps * 32, smem, stream>>>(x, weight, y, rows, n, width, eps);
   return bw::launch_status();
 }
 
