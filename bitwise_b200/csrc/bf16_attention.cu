@@ -473,7 +473,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         int page, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles,
                         int* failure) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* smem = bw::smem_align_1024(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = heads / kv_heads;
   unsigned char* ring = smem + warp * (kStreamStages * kStreamItemBytes);

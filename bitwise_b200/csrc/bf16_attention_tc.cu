@@ -146,7 +146,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const int* __restrict__ seq_row0, __nv_bfloat16* __restrict__ out, int out_stride, int heads,
                     int kv_heads, int page, int window, float scale_log2, int* error_flag) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* base = bw::smem_align_1024(smem_raw);
   unsigned char* sq = base;
   unsigned char* skv = sq + kQBytes;                    // stage s: K at skv + s * 2 * kKBytes, V kKBytes behind
   unsigned char* sp = skv + kStages * 2 * kKBytes;      // two weight buffers

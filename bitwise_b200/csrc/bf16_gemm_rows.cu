@@ -112,7 +112,7 @@ linear_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
   constexpr int kOutputs = R * NT * 8;                                // outputs of a tile, chunk sums of one chunk
   constexpr int kMine = (kOutputs + kThreads - 1) / kThreads;         // outputs per thread in the epilogue
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* smem = bw::smem_align_1024(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp_all = tid >> 5;
   const int grp = warp_all / kWarps, warp = warp_all % kWarps;  // group of 8 columns; which chunks of it
   const int num_chunks = (K + kChunk - 1) / kChunk;

@@ -332,7 +332,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials, int bn) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzled tiles want 1024-byte alignment
-  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* tiles = bw::smem_align_1024(smem_raw);
   static_assert(!PAIR || (WIDE && !SPLIT && A_ROWS == BM), "a pair works on wide tiles in whole mode");
   constexpr int BNT = WIDE ? 2 * BN : BN;   // columns of this block's accumulators
   constexpr int BNW = PAIR ? BN : BNT;      // W rows this block loads per stage

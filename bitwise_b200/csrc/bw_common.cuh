@@ -78,6 +78,14 @@ inline cudaError_t launch_pdl_cluster2(void (*kernel)(KArgs...), dim3 grid, dim3
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The first address at or after `raw` (the block's dynamic shared memory) that is a multiple of
+// 1,024, found by pointer arithmetic. A pointer that went through an integer on its way is no
+// longer known to point into shared memory, and every access through it becomes a generic load
+// or store, which costs a chain of dependent reads twice the cycles.
+__device__ __forceinline__ unsigned char* smem_align_1024(unsigned char* raw) {
+  return raw + ((1024u - (static_cast<uint32_t>(__cvta_generic_to_shared(raw)) & 1023u)) & 1023u);
+}
+
 // ---- bounded waits and the failure word --------------------------------------------------
 // No wait in these libraries is endless. A thread that polls an mbarrier gives up after
 // kSpinLimit polls (about a second); it then raises a word, the kernel drains and returns, and
@@ -104,6 +112,30 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         : "memory");
     if (done) return true;
     if ((spin & 1023u) == 1023u && *gave_up) return false;
+  }
+  *gave_up = 1;
+  return false;
+}
+
+// The same for a thread with time to spare (a warp that requests copies several stages ahead of
+// the warps that use them): between two polls it sleeps, so that its polling takes no issue slots
+// and no shared-memory cycles from the warp that shares its scheduler. At most `limit` polls of
+// about `nanos` each (about a second with the defaults).
+__device__ __forceinline__ bool mbar_wait_bounded_idle(uint64_t* bar, uint32_t parity, volatile uint32_t* gave_up,
+                                                       uint32_t nanos = 256u, uint32_t limit = 4000000u) {
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(bar));
+  for (uint32_t spin = 0; spin < limit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && *gave_up) return false;
+    __nanosleep(nanos);
   }
   *gave_up = 1;
   return false;

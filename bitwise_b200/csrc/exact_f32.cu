@@ -256,25 +256,45 @@ gemm_exact_big_kernel(const float* __restrict__ X, const float* __restrict__ W, 
 
 // ---------------------------------------------------------------------------------------
 // The same product for steps of few rows (decode steps, up to 16 rows), where the weights are
-// all that is read: one chain per output as above (a worker thread carries two rows of one
-// column, k ascending, fma after fma), but tiles of 16 columns, so that every SM streams
-// weights (a product with 2,048 columns is 128 blocks instead of 32), and the tiles of W and x
-// come through a ring of stages instead of a load, a barrier, the arithmetic and a barrier in
-// turn. A stage is 128 values of k: one TMA box of W ([4 k-tiles][16 columns][32 values], a
-// three-dimensional view of the row-major matrix) and one of x, written with the 128-byte
-// swizzle, so that a lane's 16-byte read of its own column meets no other lane's bank. What
-// lies outside the matrices arrives as zeros, and fma(0, 0, acc) = acc.
+// all that is read: one chain per output as above (k ascending, fma after fma). The tiles of W
+// and x come through a ring of stages that a warp of its own requests; blocks stay for the
+// whole launch, one on an SM, and walk tiles of TC columns one after the other, the ring
+// running on from tile to tile.
 //
-// The block's first kRowsBN * R / 2 threads carry the chains and do nothing else: with so few
-// warps on an SM every instruction's latency shows, and a thread that issued copies between
-// its multiply-adds would stretch the chain that the product's time hangs on. One more warp
-// requests the stages; the workers hand a stage back through a second barrier. Every wait is
-// bounded (bw_common.cuh).
-constexpr int kRowsBN = 16;       // columns per block
+// What bounds such a product on an SM, beside the weights' way from memory, is the way from
+// shared memory into registers: 32 bytes a cycle for each of the SM's four schedulers, so that
+// a warp's read of 16 bytes per lane takes 16 cycles (8 when all lanes read one address), far
+// more than the multiply-adds it feeds unless a lane keeps several outputs: with RM rows and
+// CN columns per lane, CN reads of W and RM reads of x feed 4 RM CN multiply-adds. And a chain
+// takes 4 cycles per value of k whatever else happens. So the shape follows the product's
+// width (the host's choice, see rows_plan): a narrow product is cut into tiles of 16 columns,
+// one output per lane (lanes 0-15 and 16-31 of a warp carry two rows of the same 16 columns),
+// so that every SM has a tile and the time is the chains' own; a wide one into tiles of 128
+// columns with 4 rows x 2 columns per lane, which reads each value of W from shared memory
+// once per 4 rows. A tile is carried by one chain warp per scheduler (two with 16 rows).
+//
+// A stage is LINES lines of 32 values of k: one TMA box of W ([LINES][TC columns][32 values],
+// a three-dimensional view of the row-major matrix, written with the 128-byte swizzle so that
+// the lanes of a quarter warp meet in no bank) and one of x ([LINES][R rows][32 values],
+// plain: a warp reads one or two addresses of it at a time). What lies outside the matrices
+// arrives as zeros; lines beyond k are not walked. The chain warps ask for the next stage's
+// barrier before they start on this one, so that the answer (some hundred cycles even when the
+// stage is there) comes while they compute. Every wait is bounded (bw_common.cuh).
 constexpr int kRowsTileK = 32;    // values of k in a 128-byte line
-constexpr int kRowsTiles = 4;     // lines of k per stage
-constexpr int kRowsBK = kRowsTileK * kRowsTiles;
-constexpr int kRowsMaxStages = 16;  // stages of the ring at most (chosen by the host from the grid)
+
+template <int R, int RM, int CN, bool HALF, int CG, int LINES>
+struct RowsShape {
+  static constexpr int kLaneCols = HALF ? 16 : 32;           // columns that the lanes of a warp spread over
+  static constexpr int kWarpRows = HALF ? 2 * RM : RM;       // rows that a warp carries
+  static constexpr int kRowGroups = R / kWarpRows;
+  static constexpr int kChainWarps = CG * kRowGroups;
+  static constexpr int kTileCols = CG * CN * kLaneCols;
+  static constexpr int kWBytes = LINES * kTileCols * 128, kXBytes = LINES * R * 128;
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kThreads = (kChainWarps + 1) * 32;
+  static_assert(R % kWarpRows == 0 && kTileCols % 8 == 0 && kTileCols <= 256, "tile shape");
+  static_assert(kStageBytes % 1024 == 0, "the swizzle of W wants stages that start on 1,024 bytes");
+};
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void bar_init(uint64_t* bar, unsigned count) {
@@ -286,99 +306,140 @@ __device__ __forceinline__ void bar_expect(uint64_t* bar, unsigned bytes) {
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
-// one box of the view (32 values, rows, k-tiles): rows from `row` on, k-tiles from `ktile` on
-__device__ __forceinline__ void tma_box3(void* dst, const CUtensorMap* map, int row, int ktile, uint64_t* bar) {
+// asks once whether phase `parity` of the barrier is over
+__device__ __forceinline__ bool bar_try(uint64_t* bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// one box of the view (32 values, rows, lines): rows from `row` on, lines from `line` on
+__device__ __forceinline__ void tma_box3(void* dst, const CUtensorMap* map, int row, int line, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(ktile), "r"(smem_addr(bar))
+      ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(line), "r"(smem_addr(bar))
       : "memory");
 }
 
-template <int R>  // rows of the tile: 8 or 16
-__global__ void __launch_bounds__(kRowsBN * R / 2 + 32)
+// the multiply-adds of one line of k: 8 pieces of 16 bytes of this lane's CN columns against its RM rows
+template <int RM, int CN>
+__device__ __forceinline__ void rows_line(const unsigned char* wl, const unsigned char* xl, unsigned swz, float (&acc)[RM][CN]) {
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {  // the 16-byte pieces of a swizzled line sit at piece ^ (row % 8)
+    float4 w[CN], x[RM];
+#pragma unroll
+    for (int c = 0; c < CN; ++c) w[c] = *reinterpret_cast<const float4*>(wl + c * (32 * 128) + ((p << 4) ^ swz));
+#pragma unroll
+    for (int r = 0; r < RM; ++r) x[r] = *reinterpret_cast<const float4*>(xl + r * 128 + p * 16);
+#pragma unroll
+    for (int r = 0; r < RM; ++r)
+#pragma unroll
+      for (int c = 0; c < CN; ++c) acc[r][c] = __fmaf_rn(x[r].x, w[c].x, acc[r][c]);
+#pragma unroll
+    for (int r = 0; r < RM; ++r)
+#pragma unroll
+      for (int c = 0; c < CN; ++c) acc[r][c] = __fmaf_rn(x[r].y, w[c].y, acc[r][c]);
+#pragma unroll
+    for (int r = 0; r < RM; ++r)
+#pragma unroll
+      for (int c = 0; c < CN; ++c) acc[r][c] = __fmaf_rn(x[r].z, w[c].z, acc[r][c]);
+#pragma unroll
+    for (int r = 0; r < RM; ++r)
+#pragma unroll
+      for (int c = 0; c < CN; ++c) acc[r][c] = __fmaf_rn(x[r].w, w[c].w, acc[r][c]);
+  }
+}
+
+template <int R, int RM, int CN, bool HALF, int CG, int LINES>
+__global__ void __launch_bounds__(RowsShape<R, RM, CN, HALF, CG, LINES>::kThreads)
 gemm_exact_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, float* Y,
                        const float* residual, int M, int N, int K, int stages, int* failure) {
-  const int kRowsStages = stages;  // stages of the ring, chosen by the host
-  constexpr int kWorkers = kRowsBN * R / 2;
-  constexpr int kWBytes = kRowsTiles * kRowsBN * 128, kXBytes = kRowsTiles * R * 128;
+  using S = RowsShape<R, RM, CN, HALF, CG, LINES>;
   extern __shared__ __align__(1024) unsigned char rows_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rows_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* Ws = base;                          // [stages][4 k-tiles][16 columns][128 bytes]
-  unsigned char* Xs = base + kRowsStages * kWBytes;  // [stages][4 k-tiles][R rows][128 bytes]
-  uint64_t* full = reinterpret_cast<uint64_t*>(Xs + kRowsStages * kXBytes);
-  uint64_t* empty = full + kRowsStages;
+  unsigned char* base = bw::smem_align_1024(rows_raw);
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + stages * S::kStageBytes);  // a stage: W, then x
+  uint64_t* empty = full + stages;
   volatile unsigned* gave_up = reinterpret_cast<volatile unsigned*>(failure);
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int n0 = blockIdx.x * kRowsBN;
-  const int stages_total = (K + kRowsBK - 1) / kRowsBK;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lines_total = K / kRowsTileK;
+  const int stages_per_tile = (lines_total + LINES - 1) / LINES;
+  const int tiles = (N + S::kTileCols - 1) / S::kTileCols;
+  const int my_tiles = (tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
   if (tid == 0) {
-    for (int s2 = 0; s2 < kRowsStages; ++s2) {
+    for (int s2 = 0; s2 < stages; ++s2) {
       bar_init(full + s2, 1);
-      bar_init(empty + s2, kWorkers / 32);
+      bar_init(empty + s2, S::kChainWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  if (tid >= kWorkers) {  // the requesting warp
+  if (warp == S::kChainWarps) {  // the requesting warp
     if (lane == 0) {
-      for (int st = 0; st < stages_total; ++st) {
-        const int slot = st % kRowsStages;
-        if (st >= kRowsStages && !bw::mbar_wait_bounded(empty + slot, ((st / kRowsStages) - 1) & 1, gave_up)) break;
-        bar_expect(full + slot, kWBytes + kXBytes);
-        tma_box3(Ws + slot * kWBytes, &map_w, n0, st * kRowsTiles, full + slot);
-        tma_box3(Xs + slot * kXBytes, &map_x, 0, st * kRowsTiles, full + slot);
+      int slot = 0, round = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * S::kTileCols;
+        for (int st = 0; st < stages_per_tile; ++st) {
+          if (round > 0 && !bw::mbar_wait_bounded_idle(empty + slot, (round - 1) & 1, gave_up)) return;
+          unsigned char* stage = base + slot * S::kStageBytes;
+          bar_expect(full + slot, S::kStageBytes);
+          tma_box3(stage, &map_w, n0, st * LINES, full + slot);
+          tma_box3(stage + S::kWBytes, &map_x, 0, st * LINES, full + slot);
+          if (++slot == stages) slot = 0, ++round;
+        }
       }
     }
     return;
   }
-  const int col = tid % kRowsBN, rp = tid / kRowsBN;  // this worker's column and pair of rows
-  const int r0 = 2 * rp, r1 = 2 * rp + 1;
-  float acc0 = 0.0f, acc1 = 0.0f;
-  for (int st = 0; st < stages_total; ++st) {
-    const int slot = st % kRowsStages;
-    if (!bw::mbar_wait_bounded(full + slot, (st / kRowsStages) & 1, gave_up)) break;
-    const unsigned char* ws = Ws + slot * kWBytes + col * 128;
-    const unsigned char* xs = Xs + slot * kXBytes;
-    // The reads of a line of k (24 of 16 bytes) are issued a whole line ahead of the chain that
-    // uses them, so that the chain never waits for shared memory.
-    float4 w[8], a[8], b[8];
-    auto read_line = [&](int kt, float4 (&wl)[8], float4 (&al)[8], float4 (&bl)[8]) {
+  const int cg = warp % CG, rg = warp / CG;
+  const int col = cg * (CN * S::kLaneCols) + (HALF ? (lane & 15) : lane);      // this lane's first column of the tile
+  const int row0 = rg * S::kWarpRows + (HALF ? (lane >> 4) * RM : 0);            // and its first row
+  const unsigned w_lane = col * 128, swz = (col & 7) << 4;
+  if (!bw::mbar_wait_bounded(full, 0, gave_up)) return;
+  int slot = 0, round = 0;
+  for (int t = 0; t < my_tiles; ++t) {
+    float acc[RM][CN];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {  // the 16-byte pieces of a line sit at piece ^ (row % 8)
-        wl[q] = *reinterpret_cast<const float4*>(ws + kt * (kRowsBN * 128) + ((q ^ (col & 7)) << 4));
-        al[q] = *reinterpret_cast<const float4*>(xs + kt * (R * 128) + r0 * 128 + ((q ^ (r0 & 7)) << 4));
-        bl[q] = *reinterpret_cast<const float4*>(xs + kt * (R * 128) + r1 * 128 + ((q ^ (r1 & 7)) << 4));
+    for (int r = 0; r < RM; ++r)
+#pragma unroll
+      for (int c = 0; c < CN; ++c) acc[r][c] = 0.0f;
+    for (int st = 0; st < stages_per_tile; ++st) {
+      int next = slot + 1, next_round = round;
+      if (next == stages) next = 0, ++next_round;
+      const bool more = st + 1 < stages_per_tile || t + 1 < my_tiles;
+      const bool next_there = more && bar_try(full + next, next_round & 1);  // answered while this stage is walked
+      const unsigned char* wl = base + slot * S::kStageBytes + w_lane;
+      const unsigned char* xl = base + slot * S::kStageBytes + S::kWBytes + row0 * 128;
+      if (lines_total - st * LINES >= LINES) {
+#pragma unroll
+        for (int line = 0; line < LINES; ++line)
+          rows_line<RM, CN>(wl + line * (S::kTileCols * 128), xl + line * (R * 128), swz, acc);
+      } else {
+        for (int line = 0; line < lines_total - st * LINES; ++line)
+          rows_line<RM, CN>(wl + line * (S::kTileCols * 128), xl + line * (R * 128), swz, acc);
       }
-    };
-    read_line(0, w, a, b);
+      __syncwarp();
+      if (lane == 0) bar_arrive(empty + slot);  // this warp has read the stage
+      if (more && !next_there && !bw::mbar_wait_bounded(full + next, next_round & 1, gave_up)) return;
+      slot = next, round = next_round;
+    }
+    const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * S::kTileCols;
 #pragma unroll
-    for (int kt = 0; kt < kRowsTiles; ++kt) {
-      float4 wn[8], an[8], bn[8];
-      if (kt + 1 < kRowsTiles) read_line(kt + 1, wn, an, bn);
+    for (int c = 0; c < CN; ++c) {
+      const int gn = n0 + col + c * 32;
+      if (gn >= N) continue;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        acc0 = __fmaf_rn(a[q].x, w[q].x, acc0), acc1 = __fmaf_rn(b[q].x, w[q].x, acc1);
-        acc0 = __fmaf_rn(a[q].y, w[q].y, acc0), acc1 = __fmaf_rn(b[q].y, w[q].y, acc1);
-        acc0 = __fmaf_rn(a[q].z, w[q].z, acc0), acc1 = __fmaf_rn(b[q].z, w[q].z, acc1);
-        acc0 = __fmaf_rn(a[q].w, w[q].w, acc0), acc1 = __fmaf_rn(b[q].w, w[q].w, acc1);
-      }
-      if (kt + 1 < kRowsTiles) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) w[q] = wn[q], a[q] = an[q], b[q] = bn[q];
+      for (int r = 0; r < RM; ++r) {
+        const int gm = row0 + r;
+        if (gm >= M) continue;
+        const size_t o = static_cast<size_t>(gm) * N + gn;
+        Y[o] = residual ? __fadd_rn(residual[o], acc[r][c]) : acc[r][c];
       }
     }
-    __syncwarp();
-    if (lane == 0) bar_arrive(empty + slot);  // this warp has read the stage
-  }
-  const int gn = n0 + col;
-  if (gn >= N) return;
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int gm = 2 * rp + i;
-    if (gm >= M) continue;
-    const size_t o = static_cast<size_t>(gm) * N + gn;
-    const float v = i ? acc1 : acc0;
-    Y[o] = residual ? __fadd_rn(residual[o], v) : v;
   }
 }
 
@@ -997,8 +1058,8 @@ __global__ void swiglu_exact_kernel(const float* __restrict__ gate_up, float* __
 
 // ---------------------------------------------------------------------------------------
 // Tensor maps for the streaming tile of few rows: a row-major float32 matrix [rows][k] seen as
-// (32 values, rows, k / 32 lines), boxes of 4 lines x box_rows rows, 128-byte swizzle, zeros
-// outside.
+// (32 values, rows, k / 32 lines), boxes of box_lines lines x box_rows rows, with the 128-byte
+// swizzle or plain, zeros outside.
 namespace {
 typedef CUresult (*EncodeTiledF32)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1014,18 +1075,90 @@ EncodeTiledF32 f32_encoder() {
   }
   return fn;
 }
-bool f32_rows_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+bool f32_rows_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows, int box_lines, bool swizzled) {
   EncodeTiledF32 enc = f32_encoder();
   if (!enc) return false;
   const cuuint64_t dims[3] = {kRowsTileK, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(k / kRowsTileK)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 4, kRowsTileK * 4};
-  const cuuint32_t box[3] = {kRowsTileK, static_cast<cuuint32_t>(box_rows), kRowsTiles};
+  const cuuint32_t box[3] = {kRowsTileK, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_lines)};
   const cuuint32_t elem[3] = {1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+// The streaming tile's width for a product (16, 32, 64 or 128 columns; the kernel's shape follows
+// from it) and the stages of its ring.
+struct RowsPlan {
+  int tile_cols, stages;
+};
+int g_forced_tile_cols = 0, g_forced_stages = 0;
+
+// lines of k in a stage, by tile width: stages of 16 to 40 KB
+constexpr int rows_lines(int tile_cols) { return tile_cols == 16 ? 8 : tile_cols == 128 ? 2 : 4; }
+
+RowsPlan rows_plan(int rows, int n, int k) {
+  const int sms = sm_count();
+  // Cycles that a tile's chain warps take per four values of k (measured on a B200, 8 rows; with
+  // 16 rows two warps share a scheduler and all of them double), times the tiles that the
+  // busiest SM walks: the narrowest tile for narrow products, where the chains' own length
+  // counts, the widest where there is a tile or more for every SM.
+  const int widths[4] = {16, 32, 64, 128};
+  const int cycles[4] = {20, 34, 48, 76};
+  int best = 0;
+  long long best_cost = 0;
+  for (int i = 0; i < 4; ++i) {
+    const int tiles = (n + widths[i] - 1) / widths[i];
+    const long long cost = static_cast<long long>((tiles + sms - 1) / sms) * cycles[i];
+    if (i == 0 || cost < best_cost) best = i, best_cost = cost;
+  }
+  RowsPlan p;
+  p.tile_cols = widths[best];
+  if (g_forced_tile_cols == 16 || g_forced_tile_cols == 32 || g_forced_tile_cols == 64 || g_forced_tile_cols == 128)
+    p.tile_cols = g_forced_tile_cols;
+  const int stage_bytes = rows_lines(p.tile_cols) * (p.tile_cols + rows) * 128;
+  p.stages = (225 * 1024) / (stage_bytes + 16);
+  p.stages = p.stages > 12 ? 12 : p.stages;
+  if (g_forced_stages >= 2 && g_forced_stages < p.stages) p.stages = g_forced_stages;
+  return p;
+}
+
+template <int R, int RM, int CN, bool HALF, int CG, int LINES>
+int launch_rows(const CUtensorMap& map_x, const CUtensorMap& map_w, float* y, const float* residual, int m, int n, int k,
+                int stages, int* word, cudaStream_t stream) {
+  using S = RowsShape<R, RM, CN, HALF, CG, LINES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_exact_rows_kernel<R, RM, CN, HALF, CG, LINES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      bw::set_error("linear (32-bit): cannot raise shared memory: %s", cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    configured = true;
+  }
+  const int tiles = (n + S::kTileCols - 1) / S::kTileCols;
+  const int sms = sm_count();
+  const int smem = stages * (S::kStageBytes + 16) + 1024;
+  gemm_exact_rows_kernel<R, RM, CN, HALF, CG, LINES><<<tiles < sms ? tiles : sms, S::kThreads, smem, stream>>>(
+      map_x, map_w, y, residual, m, n, k, stages, word);
+  return bw::launch_status();
 }
 }  // namespace
+
+// For measurements and tests: fixes the streaming tile's width (16, 32, 64 or 128 columns) and
+// the stages of its ring for the products that follow (0: the library's own choice).
+BW_API void bw_f32_force_rows_plan(int tile_cols, int stages) { g_forced_tile_cols = tile_cols, g_forced_stages = stages; }
 
 // ---------------------------------------------------------------------------------------
 // Exported entry points.
@@ -1066,39 +1199,31 @@ BW_API int bw_f32_linear(const float* x, const float* w, float* y, const float* 
   if (m <= 16 && k % kRowsTileK == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
       f32_encoder() != nullptr) {
     // rows that are whole 128-byte lines: the streaming tile
-    const unsigned blocks = (n + kRowsBN - 1) / kRowsBN;
-    // A product with few tiles (one block on an SM) keeps more stages on their way than one whose
-    // blocks share the SMs: what counts is the bytes an SM has in flight.
-    const int rows_per = m <= 8 ? 8 : 16;
-    const int stage_bytes = kRowsTiles * (kRowsBN + rows_per) * 128 + 16;
-    int stages = blocks <= 160 ? kRowsMaxStages : blocks <= 320 ? 8 : 4;
-    while (stages > 2 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
-    const int smem_bytes = stages * stage_bytes + 1024;
-    constexpr int smem8 = kRowsMaxStages * (kRowsTiles * (kRowsBN + 8) * 128 + 16) + 1024;
-    constexpr int smem16 = 200 * 1024;
+    const int rows = m <= 8 ? 8 : 16;
+    const RowsPlan plan = rows_plan(rows, n, k);
+    const int lines = rows_lines(plan.tile_cols);
     int* word = bw::failure_word();
     if (!word) return -1;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_exact_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem8);
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_exact_rows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem16);
-      if (e != cudaSuccess) {
-        bw::set_error("linear (32-bit): cannot raise shared memory: %s", cudaGetErrorString(e));
-        return static_cast<int>(e);
-      }
-      configured = true;
-    }
-    const int rows = m <= 8 ? 8 : 16;
     CUtensorMap map_x, map_w;
-    if (!f32_rows_map(&map_x, x, m, k, rows) || !f32_rows_map(&map_w, w, n, k, kRowsBN)) {
+    if (!f32_rows_map(&map_x, x, m, k, rows, lines, false) || !f32_rows_map(&map_w, w, n, k, plan.tile_cols, lines, true)) {
       bw::set_error("linear (32-bit): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d]", m, k, n, k);
       return -1;
     }
-    if (m <= 8)
-      gemm_exact_rows_kernel<8><<<blocks, kRowsBN * 4 + 32, smem_bytes, stream>>>(map_x, map_w, y, residual, m, n, k, stages, word);
-    else
-      gemm_exact_rows_kernel<16><<<blocks, kRowsBN * 8 + 32, smem_bytes, stream>>>(map_x, map_w, y, residual, m, n, k, stages, word);
+    // rows, rows and columns per lane, half-warp layout, column groups of warps, lines per stage
+#define BW_ROWS(TC_, R_, RM_, CN_, HALF_, CG_)                                                                        \
+  if (plan.tile_cols == TC_ && rows == R_)                                                                            \
+    return launch_rows<R_, RM_, CN_, HALF_, CG_, rows_lines(TC_)>(map_x, map_w, y, residual, m, n, k, plan.stages, word, stream);
+    BW_ROWS(16, 8, 1, 1, true, 1)
+    BW_ROWS(32, 8, 2, 1, false, 1)
+    BW_ROWS(64, 8, 4, 1, false, 2)
+    BW_ROWS(128, 8, 4, 2, false, 2)
+    BW_ROWS(16, 16, 1, 1, true, 1)
+    BW_ROWS(32, 16, 2, 1, false, 1)
+    BW_ROWS(64, 16, 4, 1, false, 2)
+    BW_ROWS(128, 16, 4, 2, false, 2)
+#undef BW_ROWS
+    bw::set_error("linear (32-bit): no streaming tile of %d columns for %d rows", plan.tile_cols, rows);
+    return -1;
   } else if (m <= 16) {
     gemm_exact_kernel<16><<<dim3(gx, (m + 15) / 16), 256, 0, stream>>>(x, w, y, residual, m, n, k);
   } else if (m > 64 && k % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {

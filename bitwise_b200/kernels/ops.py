@@ -270,6 +270,13 @@ class KernelOps:
             self._kernel_counts.clear()
             self.lib.bw_bf16_linear_tc_force(_c_int(width), _c_int(mode))
 
+    def force_rows_plan(self, tile_cols: int = 0, stages: int = 0) -> None:
+        """Tests and measurements of the 32-bit path: force the width of the streaming tile that
+        products of up to 16 rows take (16, 32, 64 or 128 columns) and the stages of its ring
+        (0: chosen from the shape).  Every combination gives the same bits."""
+        if self.kind == "f32":
+            self.lib.bw_f32_force_rows_plan(_c_int(tile_cols), _c_int(stages))
+
     def pair_tiles(self, on: bool) -> bool:
         """Large batches run two thread blocks per 256 x 256 tile of a product (the default) or
         one per 128 x 256 tile; same bits either way.  Returns the previous setting."""
