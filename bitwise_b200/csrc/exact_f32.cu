@@ -782,10 +782,14 @@ attention_tiles_exact_kernel(const float* __restrict__ qkv, int q_stride, const 
 }
 
 // ---- single rows: scores by many blocks -------------------------------------------------------
-// A block takes kScoreKeys consecutive keys of one (row, head): a thread per key computes
-// s_j = dot16(q, K_j) * scale and stores it; the block's maximum goes to its own place.
+// A block takes kScoreKeys consecutive keys of one (row, head) and computes
+// s_j = dot16(q, K_j) * scale for each; the block's maximum goes to its own place.
 // scores[(row * heads + h) * score_stride + j], chunk_max[(row * heads + h) * chunks + chunk].
-constexpr int kScoreThreads = 128;
+// Four neighbouring threads share a key: thread c of the four carries the partial sums 4c .. 4c+3
+// of the sixteen (the values of k at 16 i + 4c + {0..3}), so that a warp's load covers eight keys
+// in pieces of 64 consecutive bytes instead of 32 keys in pieces of 16, and the sixteen sums meet
+// through two exchanges in the order of bw::tree16: (l, l + 8), then (l, l + 4), then the last two.
+constexpr int kScoreThreads = 256;
 constexpr int kScoreKeys = 256;
 
 __global__ void __launch_bounds__(kScoreThreads)
@@ -808,28 +812,34 @@ attention_scores_exact_kernel(const float* __restrict__ qkv, int q_stride, const
   for (int i = tid; i < hd; i += kScoreThreads) q[i] = qg[i];
   __syncthreads();
   float* out = scores + (static_cast<size_t>(r) * heads + h) * score_stride;
+  const int c = tid & 3;  // which four of the sixteen partial sums
   float mx = -INFINITY;
-  for (int j = c0 + tid; j < c0 + kScoreKeys; j += kScoreThreads) {
-    if (j < lo || j > p) continue;
-    const float* kp = kcache + ((static_cast<size_t>(table[j / page]) * kv_heads + g) * page + j % page) * hd;
-    float lane[16];
-#pragma unroll
-    for (int l = 0; l < 16; ++l) lane[l] = 0.0f;
+#pragma unroll 2
+  for (int j = c0 + (tid >> 2); j < c0 + kScoreKeys; j += kScoreThreads / 4) {
+    const bool in_range = j >= lo && j <= p;  // the four threads of a key agree, whole warps may not
+    const int jj = in_range ? j : p;
+    const float* kp = kcache + ((static_cast<size_t>(table[jj / page]) * kv_heads + g) * page + jj % page) * hd + 4 * c;
+    float4 part = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int i = 0; i < hd; i += 16) {
-      const float4* k4 = reinterpret_cast<const float4*>(kp + i);
-      const float4 k0 = k4[0], k1 = k4[1], k2 = k4[2], k3 = k4[3];
-      lane[0] = __fmaf_rn(q[i + 0], k0.x, lane[0]), lane[1] = __fmaf_rn(q[i + 1], k0.y, lane[1]);
-      lane[2] = __fmaf_rn(q[i + 2], k0.z, lane[2]), lane[3] = __fmaf_rn(q[i + 3], k0.w, lane[3]);
-      lane[4] = __fmaf_rn(q[i + 4], k1.x, lane[4]), lane[5] = __fmaf_rn(q[i + 5], k1.y, lane[5]);
-      lane[6] = __fmaf_rn(q[i + 6], k1.z, lane[6]), lane[7] = __fmaf_rn(q[i + 7], k1.w, lane[7]);
-      lane[8] = __fmaf_rn(q[i + 8], k2.x, lane[8]), lane[9] = __fmaf_rn(q[i + 9], k2.y, lane[9]);
-      lane[10] = __fmaf_rn(q[i + 10], k2.z, lane[10]), lane[11] = __fmaf_rn(q[i + 11], k2.w, lane[11]);
-      lane[12] = __fmaf_rn(q[i + 12], k3.x, lane[12]), lane[13] = __fmaf_rn(q[i + 13], k3.y, lane[13]);
-      lane[14] = __fmaf_rn(q[i + 14], k3.z, lane[14]), lane[15] = __fmaf_rn(q[i + 15], k3.w, lane[15]);
+      const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
+      const float4 q4 = *reinterpret_cast<const float4*>(q + i + 4 * c);
+      part.x = __fmaf_rn(q4.x, k4.x, part.x), part.y = __fmaf_rn(q4.y, k4.y, part.y);
+      part.z = __fmaf_rn(q4.z, k4.z, part.z), part.w = __fmaf_rn(q4.w, k4.w, part.w);
     }
-    const float sc = __fmul_rn(bw::tree16(lane), scale);
-    out[j] = sc;
-    mx = fmaxf(mx, sc);
+    // sums l and l + 8 lie two threads apart, their sums l and l + 4 one thread apart
+    part.x = __fadd_rn(part.x, __shfl_xor_sync(0xffffffffu, part.x, 2));
+    part.y = __fadd_rn(part.y, __shfl_xor_sync(0xffffffffu, part.y, 2));
+    part.z = __fadd_rn(part.z, __shfl_xor_sync(0xffffffffu, part.z, 2));
+    part.w = __fadd_rn(part.w, __shfl_xor_sync(0xffffffffu, part.w, 2));
+    part.x = __fadd_rn(part.x, __shfl_xor_sync(0xffffffffu, part.x, 1));
+    part.y = __fadd_rn(part.y, __shfl_xor_sync(0xffffffffu, part.y, 1));
+    part.z = __fadd_rn(part.z, __shfl_xor_sync(0xffffffffu, part.z, 1));
+    part.w = __fadd_rn(part.w, __shfl_xor_sync(0xffffffffu, part.w, 1));
+    const float sc = __fmul_rn(__fadd_rn(__fadd_rn(part.x, part.z), __fadd_rn(part.y, part.w)), scale);
+    if (in_range) {
+      if (c == 0) out[j] = sc;
+      mx = fmaxf(mx, sc);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -909,12 +919,69 @@ __device__ __forceinline__ void value_chain(const float* __restrict__ e_t, const
   }
 }
 
+// The same for a thread that carries two neighbouring outputs (a read of 8 bytes per key): two
+// chains that do not wait for one another, half as many warps on the way from shared memory.
+__device__ __forceinline__ void value_chain2(const float* __restrict__ e_t, const float* __restrict__ v, int dslice, int keys,
+                                             float& sum, float2& acc) {
+  if (keys == kValueTile) {
+    float4 e0 = *reinterpret_cast<const float4*>(e_t), e1 = *reinterpret_cast<const float4*>(e_t + 4);
+    float2 vv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vv[i] = *reinterpret_cast<const float2*>(v + i * dslice);
+#pragma unroll
+    for (int s8 = 0; s8 < kValueTile; s8 += 8) {
+      float4 n0 = e0, n1 = e1;
+      float2 vn[8];
+      if (s8 + 8 < kValueTile) {
+        n0 = *reinterpret_cast<const float4*>(e_t + s8 + 8), n1 = *reinterpret_cast<const float4*>(e_t + s8 + 12);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vn[i] = *reinterpret_cast<const float2*>(v + (s8 + 8 + i) * dslice);
+      }
+      const float e[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sum = __fadd_rn(sum, e[i]);
+        acc.x = __fmaf_rn(e[i], vv[i].x, acc.x), acc.y = __fmaf_rn(e[i], vv[i].y, acc.y);
+      }
+      if (s8 + 8 < kValueTile) {
+        e0 = n0, e1 = n1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vv[i] = vn[i];
+      }
+    }
+  } else {
+    for (int s2 = 0; s2 < keys; ++s2) {
+      const float e = e_t[s2];
+      const float2 x = *reinterpret_cast<const float2*>(v + s2 * dslice);
+      sum = __fadd_rn(sum, e);
+      acc.x = __fmaf_rn(e, x.x, acc.x), acc.y = __fmaf_rn(e, x.y, acc.y);
+    }
+  }
+}
+
 // the weights of a row into shared memory, by `count` threads of which this is number `tid`
 __device__ __forceinline__ void row_weights(float* es, const float* __restrict__ scores, const float* __restrict__ cm,
                                             int lo, int p, int tid, int count) {
+  // The chunks' maxima and the scores come from memory that another kernel just wrote: many
+  // loads are asked for before the first is used, or every one of them would cost a round trip.
   float mx = -INFINITY;
-  for (int c = lo / kScoreKeys; c <= p / kScoreKeys; ++c) mx = fmaxf(mx, cm[c]);
-  for (int j = tid; j <= p - lo; j += count) es[j] = bw::det_expf(__fsub_rn(scores[lo + j], mx));
+  for (int c = lo / kScoreKeys + (tid & 31); c <= p / kScoreKeys; c += 32) mx = fmaxf(mx, cm[c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));  // a maximum has no order
+  const int n = p - lo + 1;
+  for (int j0 = tid; j0 < n; j0 += 16 * count) {
+    float s[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int j = j0 + u * count;
+      s[u] = j < n ? scores[lo + j] : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int j = j0 + u * count;
+      if (j < n) es[j] = bw::det_expf(__fsub_rn(s[u], mx));
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kValueMaxSlice + 32)
@@ -950,7 +1017,7 @@ attention_values_paged_exact_kernel(const float* __restrict__ scores, int score_
     const unsigned page_bytes = static_cast<unsigned>(page) * hd * 4u;
     for (int t = 0; t < tiles; ++t) {
       const int slot = t % stages;
-      if (t >= stages && !bw::mbar_wait_bounded(empty + slot, ((t / stages) - 1) & 1, gave_up)) break;
+      if (t >= stages && !bw::mbar_wait_bounded_idle(empty + slot, ((t / stages) - 1) & 1, gave_up)) break;
       const int keys = min(kValueTile, len - t * kValueTile);
       const int pages = (keys + page - 1) / page;  // the last page is copied whole: it is the request's own
       if (lane == 0) bar_expect(full + slot, page_bytes * pages);
@@ -966,16 +1033,20 @@ attention_values_paged_exact_kernel(const float* __restrict__ scores, int score_
   row_weights(es, scores + (static_cast<size_t>(r) * heads + h) * score_stride,
               chunk_max + (static_cast<size_t>(r) * heads + h) * chunks, 0, p, tid, workers);
   asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");  // the chain warps only: the requesting warp is elsewhere
-  const int d = tid;
-  float acc = 0.0f, sum = 0.0f;
+  const int d = 2 * tid;  // this thread's two outputs
+  float2 acc = make_float2(0.0f, 0.0f);
+  float sum = 0.0f;
   for (int t = 0; t < tiles; ++t) {
     const int slot = t % stages;
     if (!bw::mbar_wait_bounded(full + slot, (t / stages) & 1, gave_up)) break;
-    if (d < hd) value_chain(es + t * kValueTile, vt + slot * kValueTile * hd + d, hd, min(kValueTile, len - t * kValueTile), sum, acc);
+    if (d < hd) value_chain2(es + t * kValueTile, vt + slot * kValueTile * hd + d, hd, min(kValueTile, len - t * kValueTile), sum, acc);
     __syncwarp();
     if (lane == 0) bar_arrive(empty + slot);  // this warp has read the tile
   }
-  if (d < hd) out[static_cast<size_t>(r) * out_stride + h * hd + d] = __fmul_rn(acc, __fdiv_rn(1.0f, sum));
+  if (d < hd) {
+    const float inv = __fdiv_rn(1.0f, sum);
+    *reinterpret_cast<float2*>(out + static_cast<size_t>(r) * out_stride + h * hd + d) = make_float2(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
+  }
 }
 
 __global__ void __launch_bounds__(kValueThreads)
@@ -1400,7 +1471,7 @@ BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache,
     int* word = bw::failure_word();
     if (!word) return -1;
     if (smem <= 220 * 1024) {
-      attention_values_paged_exact_kernel<<<dim3(n, heads), (hd + 31) / 32 * 32 + 32, smem, stream>>>(
+      attention_values_paged_exact_kernel<<<dim3(n, heads), (hd / 2 + 31) / 32 * 32 + 32, smem, stream>>>(
           scores, score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads,
           kv_heads, hd, page, weight_floats, stages, word);
       return bw::launch_status();
