@@ -68,6 +68,7 @@ constexpr int kNormRowThreads = 128;
 __global__ void __launch_bounds__(kNormRowThreads)
 rmsnorm_exact_row_kernel(const float* __restrict__ x, const float* __restrict__ w, float* y,
                          const int* __restrict__ rows, int width, float eps) {
+  bw::pdl_enter();
   extern __shared__ __align__(16) float norm_row[];  // [width], then the scale
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * width;
@@ -378,16 +379,33 @@ gemm_exact_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  bw::pdl_launch();
   if (warp == S::kChainWarps) {  // the requesting warp
     if (lane == 0) {
-      int slot = 0, round = 0;
+      // The weights of the ring's first round do not depend on the kernel before this one: they
+      // are asked for at once, the rows of x after the wait for that kernel.
+      const int total = my_tiles * stages_per_tile;
+      const int first = total < stages ? total : stages;
+      {
+        int t = 0, st = 0;
+        for (int i = 0; i < first; ++i) {
+          const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * S::kTileCols;
+          bar_expect(full + i, S::kStageBytes);
+          tma_box3(base + i * S::kStageBytes, &map_w, n0, st * LINES, full + i);
+          if (++st == stages_per_tile) st = 0, ++t;
+        }
+      }
+      bw::pdl_wait();
+      int slot = 0, round = 0, it = 0;
       for (int t = 0; t < my_tiles; ++t) {
         const int n0 = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * S::kTileCols;
-        for (int st = 0; st < stages_per_tile; ++st) {
-          if (round > 0 && !bw::mbar_wait_bounded_idle(empty + slot, (round - 1) & 1, gave_up)) return;
+        for (int st = 0; st < stages_per_tile; ++st, ++it) {
           unsigned char* stage = base + slot * S::kStageBytes;
-          bar_expect(full + slot, S::kStageBytes);
-          tma_box3(stage, &map_w, n0, st * LINES, full + slot);
+          if (it >= first) {
+            if (!bw::mbar_wait_bounded_idle(empty + slot, (round - 1) & 1, gave_up)) return;
+            bar_expect(full + slot, S::kStageBytes);
+            tma_box3(stage, &map_w, n0, st * LINES, full + slot);
+          }
           tma_box3(stage + S::kWBytes, &map_x, 0, st * LINES, full + slot);
           if (++slot == stages) slot = 0, ++round;
         }
@@ -395,6 +413,7 @@ gemm_exact_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     }
     return;
   }
+  bw::pdl_wait();
   const int cg = warp % CG, rg = warp / CG;
   const int col = cg * (CN * S::kLaneCols) + (HALF ? (lane & 15) : lane);      // this lane's first column of the tile
   const int row0 = rg * S::kWarpRows + (HALF ? (lane >> 4) * RM : 0);            // and its first row
@@ -454,6 +473,7 @@ __global__ void rope_cache_exact_kernel(float* qkv, int row_stride, const int* _
                                         const int* __restrict__ block_table, int max_blocks,
                                         float* kcache, float* vcache, int heads, int kv_heads, int hd,
                                         int page, int write_kv) {
+  bw::pdl_enter();
   const int r = blockIdx.x;
   const int half = hd >> 1;
   const int p = pos[r];
@@ -798,6 +818,7 @@ attention_scores_exact_kernel(const float* __restrict__ qkv, int q_stride, const
                               const int* __restrict__ pos, int heads, int kv_heads, int hd, int page, int window,
                               float scale, float* __restrict__ scores, int score_stride,
                               float* __restrict__ chunk_max, int chunks) {
+  bw::pdl_enter();
   extern __shared__ __align__(16) float smem[];
   float* q = smem;  // [hd]
   __shared__ float red[kScoreThreads / 32];
@@ -990,6 +1011,7 @@ attention_values_paged_exact_kernel(const float* __restrict__ scores, int score_
                                     int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos,
                                     float* __restrict__ out, int out_stride, int heads, int kv_heads, int hd, int page,
                                     int weight_floats, int stages, int* failure) {
+  bw::pdl_enter();
   extern __shared__ __align__(16) float smem[];
   float* es = smem;                    // [len] weights of the row
   float* vt = smem + weight_floats;    // [stages][kValueTile][hd]
@@ -1055,6 +1077,7 @@ attention_values_exact_kernel(const float* __restrict__ scores, int score_stride
                               int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos,
                               float* __restrict__ out, int out_stride, int heads, int kv_heads, int hd, int dslice,
                               int page, int window, int weight_floats) {
+  bw::pdl_enter();
   extern __shared__ __align__(16) float smem[];
   float* es = smem;                    // [len] weights of the row
   float* vt = smem + weight_floats;    // [kValueStages][kValueTile][dslice]
@@ -1113,6 +1136,7 @@ attention_values_exact_kernel(const float* __restrict__ scores, int score_stride
 // ---------------------------------------------------------------------------------------
 // SwiGLU on rows laid out [gate | up]: h = (g * (1 / (1 + exp(-g)))) * u (src/kernels.cpp:291-298).
 __global__ void swiglu_exact_kernel(const float* __restrict__ gate_up, float* __restrict__ out, int n, int inter) {
+  bw::pdl_enter();
   const size_t total = static_cast<size_t>(n) * inter;
   for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -1221,8 +1245,12 @@ int launch_rows(const CUtensorMap& map_x, const CUtensorMap& map_w, float* y, co
   const int tiles = (n + S::kTileCols - 1) / S::kTileCols;
   const int sms = sm_count();
   const int smem = stages * (S::kStageBytes + 16) + 1024;
-  gemm_exact_rows_kernel<R, RM, CN, HALF, CG, LINES><<<tiles < sms ? tiles : sms, S::kThreads, smem, stream>>>(
-      map_x, map_w, y, residual, m, n, k, stages, word);
+  cudaError_t le = bw::launch_pdl(gemm_exact_rows_kernel<R, RM, CN, HALF, CG, LINES>, dim3(tiles < sms ? tiles : sms), dim3(S::kThreads),
+                                  static_cast<size_t>(smem), stream, map_x, map_w, y, residual, m, n, k, stages, word);
+  if (le != cudaSuccess) {
+    bw::set_error("linear (32-bit): launch failed: %s", cudaGetErrorString(le));
+    return static_cast<int>(le);
+  }
   return bw::launch_status();
 }
 }  // namespace
@@ -1253,7 +1281,7 @@ BW_API int bw_f32_rmsnorm(const float* x, const float* weight, float* y, const i
     configured = true;
   }
   if (n <= 64 && width < 12000)  // few rows (a decode step): a block per row
-    rmsnorm_exact_row_kernel<<<n, kNormRowThreads, (width + 4) * sizeof(float), stream>>>(x, weight, y, rows, width, eps);
+    bw::launch_pdl(rmsnorm_exact_row_kernel, dim3(n), dim3(kNormRowThreads), (width + 4) * sizeof(float), stream, x, weight, y, rows, width, eps);
   else
     rmsnorm_exact_kernel<<<(n + kNormWarps - 1) / kNormWarps, kNormWarps * 32, smem, stream>>>(x, weight, y, rows, n, width, eps);
   return bw::launch_status();
@@ -1324,8 +1352,13 @@ BW_API int bw_f32_rope_cache(float* qkv, int row_stride, const int* pos, const i
     bw::set_error("rope: head size %d is odd", hd);
     return -1;
   }
-  rope_cache_exact_kernel<<<n, 128, 0, stream>>>(qkv, row_stride, pos, row_seq, cos_t, sin_t, block_table,
-                                                 max_blocks, kcache, vcache, heads, kv_heads, hd, page, write_kv);
+  // a thread per pair of the widest part (at most 1,024): a step of few rows is a chain of round trips to
+  // memory (position, then the row, the table's line and the block, then the writes), not a stream
+  int threads = (heads > kv_heads ? heads : kv_heads) * (hd / 2);
+  threads = threads > 1024 ? 1024 : threads < 128 ? 128 : (threads + 31) / 32 * 32;
+  if (n > 64) threads = 128;
+  bw::launch_pdl(rope_cache_exact_kernel, dim3(n), dim3(threads), 0, stream, qkv, row_stride, pos, row_seq, cos_t, sin_t,
+                 block_table, max_blocks, kcache, vcache, heads, kv_heads, hd, page, write_kv);
   return bw::launch_status();
 }
 
@@ -1442,9 +1475,9 @@ BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache,
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
   }
-  attention_scores_exact_kernel<<<dim3(n, heads, chunks), kScoreThreads, hd * sizeof(float), stream>>>(
-      qkv, q_stride, kcache, block_table, max_blocks, row_seq, pos, heads, kv_heads, hd, page, window, scale, scores,
-      score_stride, chunk_max, chunks);
+  bw::launch_pdl(attention_scores_exact_kernel, dim3(n, heads, chunks), dim3(kScoreThreads), hd * sizeof(float), stream, qkv,
+                 q_stride, kcache, block_table, max_blocks, row_seq, pos, heads, kv_heads, hd, page, window, scale, scores,
+                 score_stride, chunk_max, chunks);
   const int weight_floats = (max_keys + 3) / 4 * 4;  // keeps the value tiles behind the weights on 16 bytes
   static bool configured = false;
   if (!configured) {
@@ -1471,9 +1504,9 @@ BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache,
     int* word = bw::failure_word();
     if (!word) return -1;
     if (smem <= 220 * 1024) {
-      attention_values_paged_exact_kernel<<<dim3(n, heads), (hd / 2 + 31) / 32 * 32 + 32, smem, stream>>>(
-          scores, score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads,
-          kv_heads, hd, page, weight_floats, stages, word);
+      bw::launch_pdl(attention_values_paged_exact_kernel, dim3(n, heads), dim3((hd / 2 + 31) / 32 * 32 + 32), smem, stream,
+                     scores, score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride,
+                     heads, kv_heads, hd, page, weight_floats, stages, word);
       return bw::launch_status();
     }
   }
@@ -1494,9 +1527,9 @@ BW_API int bw_f32_attention(const float* qkv, int q_stride, const float* kcache,
     bw::set_error("attention (32-bit): %d keys exceed the shared-memory buffer of a row's weights", max_keys);
     return -1;
   }
-  attention_values_exact_kernel<<<dim3(n, heads, dsplit), kValueThreads, smem, stream>>>(
-      scores, score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads,
-      kv_heads, hd, dslice, page, window, weight_floats);
+  bw::launch_pdl(attention_values_exact_kernel, dim3(n, heads, dsplit), dim3(kValueThreads), smem, stream, scores,
+                 score_stride, chunk_max, chunks, vcache, block_table, max_blocks, row_seq, pos, out, out_stride, heads,
+                 kv_heads, hd, dslice, page, window, weight_floats);
   return bw::launch_status();
 }
 
@@ -1504,6 +1537,6 @@ BW_API int bw_f32_swiglu(const float* gate_up, float* out, int n, int inter, cud
   if (n <= 0 || inter <= 0) return 0;
   const size_t total = static_cast<size_t>(n) * inter;
   const unsigned blocks = static_cast<unsigned>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
-  swiglu_exact_kernel<<<blocks, 256, 0, stream>>>(gate_up, out, n, inter);
+  bw::launch_pdl(swiglu_exact_kernel, dim3(blocks), dim3(256), 0, stream, gate_up, out, n, inter);
   return bw::launch_status();
 }
