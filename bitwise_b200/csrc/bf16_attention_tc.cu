@@ -4,8 +4,9 @@
 // bf16_attention.cu (key tiles of 64 at fixed positions; per tile and row the maximum, the sum
 // of the weights and the unnormalised output with bfloat16 weights; ordered merge), so the
 // three kernels give the same bits. What changes is where the work runs:
-//   warp 0     one thread brings Q (once) and the key/value tiles of the paged cache into shared
-//              memory with TMA (128-byte swizzle), one box per page
+//   warp 0     brings Q (once) and the key/value tiles of the paged cache into shared memory
+//              with TMA (128-byte swizzle), one box per page and piece, the lanes asking for
+//              one box each
 //   warp 1     one thread issues tcgen05.mma: S = Q K^T (128 stacked rows x 64 keys, K-major
 //              operands) into one of two S buffers in tensor memory, and O_t = P V (P from
 //              shared memory, V as an MN-major operand) into one of two O buffers
@@ -15,7 +16,14 @@
 //              registers; finally normalise and store
 // A head of 128 is two pieces of 64 along d: Q, K and V tiles are kept piece by piece (a row of
 // a piece is one 128-byte swizzled line), the scores add up over the pieces' k-steps in order,
-// and the output takes one MMA per piece (64 columns of the O buffer each).
+// and the output takes one MMA per 16 keys over all 128 columns (the pieces of V are the
+// swizzle atoms of one MN-major operand, a piece apart).
+// What the tensor core does is handed out by one thread, and every instruction or barrier
+// operation costs that thread about a hundred cycles, which is what a tile's time is made of
+// (measured with time stamps: 21 such operations and 2,500 cycles per tile of 64 keys at head
+// size 128, where the arithmetic needs 500). So that thread waits only for what nothing else
+// implies (keys landed, weights written: the buffers of S and O are free by then, see below)
+// and announces the output and the freed stage with one commit.
 // At head size 64 two blocks share an SM (256 tensor-memory columns and about 100 KB each), so
 // one block's softmax overlaps the other's MMAs; at 128 a block has the SM to itself (384 of
 // the 512 columns, 170 KB) and overlaps its own stages. Every mbarrier wait is bounded
@@ -36,7 +44,7 @@ constexpr int HD = BW_HEAD_DIM;
 constexpr int kPieces = HD / 64;  // 64-wide pieces of a head along d
 constexpr int kTileM = 128;   // stacked rows per block
 constexpr int kTileKV = 64;   // keys per tile
-constexpr int kStages = 3;    // key/value tiles in flight
+constexpr int kStages = 3;    // key/value tiles in flight (a fourth at head size 128 fits and was slower end to end)  // key/value tiles in flight (at 64 two blocks share an SM's shared memory)
 constexpr int kThreads = 192;
 constexpr int kQPiece = kTileM * 128;          // 16 KB: one piece of the Q tile
 constexpr int kKPiece = kTileKV * 128;         // 8 KB: one piece of a K (or V) tile
@@ -48,8 +56,8 @@ constexpr int kTmemCols = HD == 64 ? 256 : 512;
 
 struct __align__(8) Barriers {
   uint64_t q_full;
-  uint64_t kv_full[kStages], kv_empty[kStages];
-  uint64_t s_full[2], s_empty[2], p_ready[2], o_full[2], o_empty[2];
+  uint64_t kv_full[kStages], pv_done[kStages];  // a tile's keys and values have landed; its output is formed
+  uint64_t s_full[2], p_ready[2];
   uint32_t tmem_base;
   uint32_t failed;
 };
@@ -90,9 +98,21 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
-// kind::f16, D float32, A and B bfloat16, M 128, N 64; bit 16 set: B is MN-major
+// The same for the whole MN-major V tile of a head wider than 64: its 64-wide pieces lie a piece
+// (kKPiece bytes) apart, which is the leading-dimension offset between the swizzle atoms along d.
+__device__ __forceinline__ uint64_t make_desc_wide(uint32_t smem_addr, uint32_t piece_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(piece_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// kind::f16, D float32, A and B bfloat16, M 128, N 64; bit 16 set: B is MN-major (N = HD: all of
+// a head's columns in one instruction, an instruction's issue costs its thread about a hundred cycles)
 constexpr uint32_t kDescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
-constexpr uint32_t kDescPV = kDescQK | (1u << 16);
+constexpr uint32_t kDescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((static_cast<uint32_t>(HD) >> 3) << 17) | ((128u >> 4) << 24);
 
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -159,14 +179,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+      mbar_init(&bars->pv_done[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->s_full[b], 1);
-      mbar_init(&bars->s_empty[b], 4);
       mbar_init(&bars->p_ready[b], 4);
-      mbar_init(&bars->o_full[b], 1);
-      mbar_init(&bars->o_empty[b], 4);
     }
     bars->failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -208,22 +225,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (lane == 0) {
       mbar_expect_tx(&bars->q_full, kQBytes);
       for (int i = 0; i < kPieces; ++i) tma_load_4d(sq + i * kQPiece, &map_q, 64 * i, 0, g, row0, &bars->q_full);
-      for (int t = 0; t < ntiles; ++t) {
-        const int s = t % kStages;
-        if (t >= kStages && !mbar_wait(&bars->kv_empty[s], ((t / kStages) - 1) & 1, failed)) break;
-        unsigned char* k = skv + s * 2 * kKBytes;
-        const int j0 = kv_lo + t * kTileKV;
-        mbar_expect_tx(&bars->kv_full[s], 2 * kKBytes);
-        for (int pg = 0; pg < pages_per_tile; ++pg) {
-          const int j = j0 + pg * page;
-          // pages wholly beyond the last key are not in the table: any valid page will do, its keys are masked
-          const int pi = min(j / page, last_page) - first_page;
-          const int blk = pi < staged ? spages[pi] : table[first_page + pi];
-          for (int i = 0; i < kPieces; ++i) {
-            tma_load_4d(k + i * kKPiece + pg * page * 128, &map_k, 64 * i, 0, g, blk, &bars->kv_full[s]);
-            tma_load_4d(k + kKBytes + i * kKPiece + pg * page * 128, &map_v, 64 * i, 0, g, blk, &bars->kv_full[s]);
-          }
-        }
+    }
+    // A tile of keys and values is pages x pieces x 2 copies (16 at head size 128 with pages of 16),
+    // and the issue of one holds its thread for a hundred cycles or more: the lanes issue one each,
+    // side by side, or the copies of a tile would take longer to ask for than the tile takes to use.
+    const int copies = pages_per_tile * kPieces * 2;
+    for (int t = 0; t < ntiles; ++t) {
+      const int s = t % kStages;
+      int ok = 1;
+      if (lane == 0) {
+        if (t >= kStages && !mbar_wait(&bars->pv_done[s], ((t / kStages) - 1) & 1, failed)) ok = 0;
+        if (ok) mbar_expect_tx(&bars->kv_full[s], 2 * kKBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      unsigned char* k = skv + s * 2 * kKBytes;
+      const int j0 = kv_lo + t * kTileKV;
+      for (int c = lane; c < copies; c += 32) {
+        const int pg = c / (kPieces * 2), i = (c >> 1) % kPieces, is_v = c & 1;
+        const int j = j0 + pg * page;
+        // pages wholly beyond the last key are not in the table: any valid page will do, its keys are masked
+        const int pi = min(j / page, last_page) - first_page;
+        const int blk = pi < staged ? spages[pi] : table[first_page + pi];
+        tma_load_4d(k + is_v * kKBytes + i * kKPiece + pg * page * 128, is_v ? &map_v : &map_k, 64 * i, 0, g, blk,
+                    &bars->kv_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -234,7 +259,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       auto issue_qk = [&](int t) -> bool {
         const int s = t % kStages, b = t & 1;
         if (!mbar_wait(&bars->kv_full[s], (t / kStages) & 1, failed)) return false;
-        if (t >= 2 && !mbar_wait(&bars->s_empty[b], ((t >> 1) - 1) & 1, failed)) return false;
+        // The scores' buffer was read by the softmax of tile t - 2 before that tile's weights were
+        // announced, and this thread saw that announcement before it formed tile t - 2's output:
+        // no barrier of its own (a wait costs this thread a hundred cycles even when it is over,
+        // and the tensor core's work is handed out by this one thread).
         fence_after_sync();
         const uint32_t k_addr = smem_u32(skv + s * 2 * kKBytes);
 #pragma unroll
@@ -252,19 +280,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (t + 1 < ntiles) ok = issue_qk(t + 1);  // the next tile's scores are computed while this one's weights are formed
         if (!ok) break;
         if (!mbar_wait(&bars->p_ready[b], (t >> 1) & 1, failed)) break;
-        if (t >= 2 && !mbar_wait(&bars->o_empty[b], ((t >> 1) - 1) & 1, failed)) break;
+        // the output buffer was merged (tile t - 2) before the softmax of this tile began: same argument
         fence_after_sync();
         const uint64_t pdesc = make_desc(smem_u32(sp + b * kPBytes));
         const uint32_t v_addr = smem_u32(skv + s * 2 * kKBytes + kKBytes);
+        const uint64_t vdesc = kPieces == 1 ? make_desc(v_addr) : make_desc_wide(v_addr, kKPiece);
 #pragma unroll
-        for (int i = 0; i < kPieces; ++i) {  // 64 output columns per piece of V
-          const uint64_t vdesc = make_desc(v_addr + i * kKPiece);
-#pragma unroll
-          for (int k = 0; k < kTileKV / 16; ++k)  // 16 keys: 32 bytes along a row of P, two 8-key groups (2048 bytes) of V
-            umma(tmem_base + kOCol + b * HD + 64 * i, pdesc + 2 * k, vdesc + 128 * k, kDescPV, k > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->o_full[b]);
-        umma_commit(&bars->kv_empty[s]);
+        for (int k = 0; k < kTileKV / 16; ++k)  // 16 keys: 32 bytes along a row of P, two 8-key groups (2048 bytes) of V
+          umma(tmem_base + kOCol + b * HD, pdesc + 2 * k, vdesc + 128 * k, kDescPV, k > 0 ? 1u : 0u);
+        umma_commit(&bars->pv_done[s]);  // the output is there, and the stage may be filled again
       }
     }
   } else {
@@ -290,8 +314,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       float s[kTileKV];
       tmem_ld64(lane_addr + b * 64, s);
       fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[b]);
       // mask, maximum of the raw scores (the mask test is skipped for tiles inside the row's
       // range), then weights e = 2^(s * scale - ref) with one fused multiply-add per key
       float tmax = -INFINITY;
@@ -345,7 +367,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // tile's output from the weights just written
       if (t > 0) {
         const int pb = (t - 1) & 1;
-        if (!mbar_wait(&bars->o_full[pb], ((t - 1) >> 1) & 1, failed)) {
+        if (!mbar_wait(&bars->pv_done[(t - 1) % kStages], ((t - 1) / kStages) & 1, failed)) {
           ok = false;
           break;
         }
@@ -361,15 +383,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           for (int i = 0; i < 64; ++i) o_tot[64 * pc + i] = merge_value(o_tot[64 * pc + i], v[i], w);
         }
         fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->o_empty[pb]);
       }
       prev_max = tmax;
       prev_sum = tsum;
     }
     if (ok && ntiles > 0) {  // the last tile's output
       const int pb = (ntiles - 1) & 1;
-      if (mbar_wait(&bars->o_full[pb], ((ntiles - 1) >> 1) & 1, failed)) {
+      if (mbar_wait(&bars->pv_done[(ntiles - 1) % kStages], ((ntiles - 1) / kStages) & 1, failed)) {
         fence_after_sync();
         const MergeWeights w = merge_weights(M, prev_max);
         M = w.mx;

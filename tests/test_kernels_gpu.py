@@ -70,6 +70,34 @@ def test_f32_linear(m, n, k):
     assert_same_bits(acc.cpu().numpy(), (res + want).astype(np.float32), "linear with residual in place")
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+def test_f32_linear_of_few_rows_every_tile_width_gives_the_chain(m):
+    """Products of up to 16 rows whose k is a multiple of 32 stream the weights through tiles of
+    16, 32, 64 or 128 columns (one to eight outputs per lane); the width is chosen for speed and
+    every one must give the plain chain's bits: widths that cut the matrix's edge, a single
+    line of k, stages that end before their last line, and more tiles than blocks."""
+    rng = np.random.default_rng(40 + m)
+    ops = _ops("float32")
+    try:
+        for n, k in ((1, 32), (50, 96), (333, 416), (200, 1056), (40000, 64)):
+            x, w = rnd(rng, m, k), rnd(rng, n, k, scale=0.1)
+            want = P.linear(x, w)
+            res = rnd(rng, m, n)
+            for width in (0, 16, 32, 64, 128):
+                for stages in (0, 2):
+                    ops.force_rows_plan(width, stages)
+                    out = torch.empty(m, n, device=DEV)
+                    ops.linear(t(x), t(w), out)
+                    assert_same_bits(out.cpu().numpy(), want, f"[{m}x{k}] x [{n}x{k}], tiles of {width}, {stages} stages")
+                    acc = t(res).clone()
+                    ops.linear(t(x), t(w), acc, residual=acc)
+                    assert_same_bits(acc.cpu().numpy(), (res + want).astype(np.float32),
+                                     f"[{m}x{k}] x [{n}x{k}] with residual, tiles of {width}")
+    finally:
+        ops.force_rows_plan(0, 0)
+    assert not ops.device_failure(), "a kernel gave up a bounded wait"
+
+
 def test_f32_linear_row_alone_equals_row_in_batch():
     rng = np.random.default_rng(5)
     x, w = rnd(rng, 50, 200), rnd(rng, 77, 200)
