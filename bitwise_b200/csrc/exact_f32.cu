@@ -1204,10 +1204,12 @@ constexpr int rows_lines(int tile_cols) { return tile_cols == 16 ? 8 : tile_cols
 
 RowsPlan rows_plan(int rows, int n, int k) {
   const int sms = sm_count();
-  // Cycles that a tile's chain warps take per four values of k (measured on a B200, 8 rows; with
-  // 16 rows two warps share a scheduler and all of them double), times the tiles that the
-  // busiest SM walks: the narrowest tile for narrow products, where the chains' own length
-  // counts, the widest where there is a tile or more for every SM.
+  // Cycles that a tile's chain warps take per four values of k (the inner loop alone, measured on
+  // a B200 with 8 rows; with 16 rows two warps share a scheduler and all of them double), times
+  // the tiles that the busiest SM walks: the narrowest tile for narrow products, where the
+  // chains' own length counts, the widest where there is a tile or more for every SM. The
+  // choice this makes was the fastest of the four widths for every product of the two model
+  // shapes that bench.py knows (measured with bw_f32_force_rows_plan).
   const int widths[4] = {16, 32, 64, 128};
   const int cycles[4] = {20, 34, 48, 76};
   int best = 0;
