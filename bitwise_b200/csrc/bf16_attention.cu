@@ -225,25 +225,44 @@ __device__ __forceinline__ void attend_tile(const unsigned char* sq, const unsig
   r.sum_hi = tsum_hi;
 }
 
-// cp.async of `count` threads: one tile of keys and values from the
+// cp.async of `count` threads (whole warps): one tile of keys and values from the
 // paged cache into shared memory; keys at or beyond kv_hi are zero-filled. A thread keeps its
-// 16-byte piece and walks the keys, so that the page lookup happens once per key and thread;
-// page_shift is log2(page) when the page size is a power of two, else -1.
+// 16-byte piece and walks the keys; page_shift is log2(page) when the page size is a power of
+// two, else -1. The page ids of the tile are read first, one per lane, and handed round by
+// shuffle: a table entry read inside the walk would put a round trip to memory (a few hundred
+// cycles, one after the other) before every pair of copies, and the issue of a tile's copies
+// took three times as long as the tile's arithmetic.
 __device__ __forceinline__ void load_kv_tile(unsigned char* sk, unsigned char* sv, const __nv_bfloat16* kcache,
                                              const __nv_bfloat16* vcache, const int* table, int page, int page_shift,
                                              int kv_heads, int g, int j0, int kv_hi, int t, int count) {
   const int piece = t % kPieces;
-  const int keys_per_pass = count / kPieces;  // threads beyond a whole number of keys sit out
-  if (t >= keys_per_pass * kPieces) return;
-  for (int key = t / kPieces; key < kTileKV; key += keys_per_pass) {
-    const int j = j0 + key;
-    const bool ok = j < kv_hi;
-    size_t off = 0;
-    if (ok) {
+  const int keys_per_pass = count / kPieces;  // threads beyond a whole number of keys copy nothing
+  const bool copies = t < keys_per_pass * kPieces;
+  // tiles start on multiples of kTileKV: with a power-of-two page of at most kTileKV keys a tile is
+  // whole pages, at most 32 of them when a page has two keys or more
+  const bool by_lane = page_shift >= 1 && page <= kTileKV;
+  int my_page = 0;
+  if (by_lane) {
+    const int lane = t & 31, first = j0 >> page_shift;
+    if (lane < (kTileKV >> page_shift) && ((first + lane) << page_shift) < kv_hi) my_page = table[first + lane];
+  }
+  const int passes = (kTileKV + keys_per_pass - 1) / keys_per_pass;  // the same for every thread: all lanes meet in the shuffle
+  for (int i = 0; i < passes; ++i) {
+    const int key = t / kPieces + i * keys_per_pass;
+    const bool in_tile = copies && key < kTileKV;
+    const int j = j0 + (in_tile ? key : 0);
+    const bool ok = in_tile && j < kv_hi;
+    int page_id = 0, slot = 0;
+    if (by_lane) {
+      page_id = __shfl_sync(0xffffffffu, my_page, (j - j0) >> page_shift);
+      slot = j & (page - 1);
+    } else if (ok) {
       const int blk = page_shift >= 0 ? j >> page_shift : j / page;
-      const int slot = page_shift >= 0 ? j & (page - 1) : j - blk * page;
-      off = ((static_cast<size_t>(table[blk]) * kv_heads + g) * page + slot) * HD + piece * 8;
+      slot = page_shift >= 0 ? j & (page - 1) : j - blk * page;
+      page_id = table[blk];
     }
+    if (!in_tile) continue;
+    const size_t off = ok ? ((static_cast<size_t>(page_id) * kv_heads + g) * page + slot) * HD + piece * 8 : 0;
     cp_async16(smem_u32(sk + piece_offset(key, piece)), kcache + off, ok);
     cp_async16(smem_u32(sv + piece_offset(key, piece)), vcache + off, ok);
   }
