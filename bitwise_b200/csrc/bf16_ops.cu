@@ -21,10 +21,23 @@ rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __
   const float* xr = x + static_cast<size_t>(src) * width;
   __nv_bfloat16* yr = y + static_cast<size_t>(r) * width;
   __shared__ float red[kNormThreads / 32];
+  // A thread's elements are threadIdx.x, + kNormThreads, ...: eight of them (a row of 2,048 in one
+  // go) are asked for before the first is used, and the weights with them, so that a row costs one
+  // round trip to memory instead of one per element. The sums keep their order.
+  constexpr int kBatch = 8;
   float acc = 0.0f;
-  for (int i = threadIdx.x; i < width; i += kNormThreads) {
-    const float v = xr[i];
-    acc = __fmaf_rn(v, v, acc);
+  float v[kBatch], g[kBatch];
+  const bool one_go = width <= kBatch * kNormThreads;
+  for (int base = 0; base < width; base += kBatch * kNormThreads) {
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = base + threadIdx.x + j * kNormThreads;
+      v[j] = i < width ? xr[i] : 0.0f;
+      if (one_go) g[j] = i < width ? w[i] : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (base + threadIdx.x + j * kNormThreads < width) acc = __fmaf_rn(v[j], v[j], acc);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
@@ -34,7 +47,15 @@ rmsnorm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ w, __
 #pragma unroll
   for (int i = 0; i < kNormThreads / 32; ++i) ss = __fadd_rn(ss, red[i]);
   const float inv = bw::rms_scale(ss, width, eps);
-  for (int i = threadIdx.x; i < width; i += kNormThreads) yr[i] = __float2bfloat16_rn(bw::rms_apply(xr[i], inv, w[i]));
+  if (one_go) {
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      if (i < width) yr[i] = __float2bfloat16_rn(bw::rms_apply(v[j], inv, g[j]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += kNormThreads) yr[i] = __float2bfloat16_rn(bw::rms_apply(xr[i], inv, w[i]));
+  }
 }
 
 // ---------------------------------------------------------------------------------------
