@@ -651,6 +651,85 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
   }
 }
+
+// The per-tile blocks of attention_split_kernel (one warp, one key tile, a dozen blocks on an SM)
+// with the tile's keys and values fetched as TMA boxes: a page of a head is one box, eight
+// boxes a tile, asked for by one lane, instead of 32 warp-wide cp.async of four lines each
+// (whose issue was a third of a block's time). The query row still comes by cp.async, the
+// arithmetic and the record are attend_tile's: same bits. For steps of fewer rows than the
+// streaming kernel above is worth its set-up for.
+__global__ void __launch_bounds__(32)
+attention_tile_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                          const __nv_bfloat16* __restrict__ qkv, int q_stride, const int* __restrict__ block_table,
+                          int max_blocks, const int* __restrict__ row_seq, const int* __restrict__ pos, int heads,
+                          int kv_heads, int page, int window, float scale_log2, float* __restrict__ tile_out, int max_tiles,
+                          int* failure) {
+  extern __shared__ __align__(1024) unsigned char tile_raw[];
+  unsigned char* base = bw::smem_align_1024(tile_raw);
+  unsigned char* sq = base;                  // 16 stacked rows of 128 bytes
+  unsigned char* sk = base + kStreamQBytes;  // the boxes' swizzle is the layout that attend_tile reads
+  unsigned char* sv = sk + kKVBytes;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sv + kKVBytes);
+  const int lane = threadIdx.x;
+  const int row = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+  const int group = heads / kv_heads;
+  const int p = pos[row];
+  const int first = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  if (t * kTileKV > p || (t + 1) * kTileKV <= first) {
+    bw::pdl_enter();
+    return;  // no key of the row's range in this tile
+  }
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const int* table = block_table + static_cast<size_t>(row_seq[row]) * max_blocks;
+  const int pages_per_tile = kTileKV / page;
+  // pages wholly beyond the row's last key are not in the table: the last page stands in, its keys are masked
+  const int my_page = lane < pages_per_tile ? table[min(t * pages_per_tile + lane, p / page)] : 0;
+  const bool settled = (t + 1) * kTileKV <= p;  // all of the tile was stored by earlier steps
+  auto request = [&]() {
+    if (lane == 0) mbar_arrive_expect_tx(bar, 2 * kKVBytes);
+    __syncwarp();
+    for (int pg = 0; pg < pages_per_tile; ++pg) {
+      const int blk = __shfl_sync(0xffffffffu, my_page, pg);
+      if (lane == 0) {
+        tma_box_4d(sk + pg * page * 128, &map_k, g, blk, bar);
+        tma_box_4d(sv + pg * page * 128, &map_v, g, blk, bar);
+      }
+    }
+  };
+  if (settled) request();  // before the wait for the kernel that rotates q and stores this step's key and value
+  bw::pdl_enter();
+  for (int idx = lane; idx < 16 * kPieces; idx += 32) {
+    const int m = idx / kPieces, piece = idx - m * kPieces;
+    const bool ok = m < group;
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(row) * q_stride + (g * group + (ok ? m : 0)) * HD + piece * 8;
+    cp_async16(smem_u32(sq + piece_offset(m, piece)), src, ok);
+  }
+  cp_async_commit();
+  if (!settled) request();
+  cp_async_wait<0>();
+  if (!bw::mbar_wait_bounded(bar, 0, reinterpret_cast<volatile uint32_t*>(failure))) return;
+  __syncwarp();
+
+  TileResult r;
+  attend_tile(sq, sk, sv, lane, t * kTileKV, p, p, first, first, scale_log2, r);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = (lane >> 2) + half * 8;
+    if (m >= group) continue;
+    float* dst = tile_out + ((static_cast<size_t>(row) * heads + (g * group + m)) * max_tiles + t) * (HD + 2);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+      *reinterpret_cast<float2*>(dst + i * 8 + 2 * (lane & 3)) = make_float2(r.o[i][half * 2], r.o[i][half * 2 + 1]);
+    if ((lane & 3) == 0) {
+      dst[HD] = half ? r.max_hi : r.max_lo;
+      dst[HD + 1] = half ? r.sum_hi : r.sum_lo;
+    }
+  }
+}
 #endif  // BW_HEAD_DIM == 64
 
 // Second half of split mode: per (row, head) the tile results are merged in ascending tile
@@ -792,23 +871,22 @@ int g_stream_mode = 1;  // 0 never, 1 for steps of many rows, 2 whenever the sha
 constexpr int kStreamMinRows = 32;
 }  // namespace
 
-// When the streaming decode kernel runs: 0 never, 1 (the default) for steps of 32 rows or more
-// (measured on B200: with fewer rows its set-up per block costs more than its steadier stream
-// of loads gains), 2 whenever the shape allows. Returns the previous setting. Tests compare it
-// with attention_split_kernel bit for bit.
+// How decode steps fetch the cache where the shape allows TMA boxes: 0 never (the cp.async blocks
+// of attention_split_kernel), 1 (the default) the streaming kernel for steps of 32 rows or more
+// and a block per key tile fed by boxes for fewer (measured on B200: with few rows the set-up of
+// a persistent block costs more than its steadier stream of loads gains), 2 the streaming kernel
+// whenever the shape allows. Returns the previous setting. Tests compare the kernels bit for bit.
 BW_API int bw_bf16_attention_stream_mode(int mode) {
   const int before = g_stream_mode;
   if (mode >= 0 && mode <= 2) g_stream_mode = mode;
   return before;
 }
 
-// Whether decode steps of this shape can take the streaming kernel: head size 64, pages of 8
+// Whether decode steps of this shape can take bw_bf16_attention_stream: head size 64, pages of 8
 // keys or more that divide a tile of 64, a group of at most 16 heads, rows that start on 16
 // bytes, and a step of at most 512 rows.
 BW_API int bw_bf16_attention_stream_usable(int n, int heads, int kv_heads, int hd, int page, int q_stride) {
-  if (!g_stream_mode || (g_stream_mode == 1 && n < kStreamMinRows) || hd != HD || kv_heads <= 0 || heads % kv_heads ||
-      n > kStreamMaxRows)
-    return 0;
+  if (!g_stream_mode || hd != HD || kv_heads <= 0 || heads % kv_heads || n > kStreamMaxRows) return 0;
   const int group = heads / kv_heads;
   return group <= 16 && page >= 8 && kTileKV % page == 0 && q_stride % 8 == 0 && stream_encoder() != nullptr;
 }
@@ -873,6 +951,19 @@ BW_API int bw_bf16_attention_stream(const __nv_bfloat16* qkv, int q_stride, cons
   int* word = bw::failure_word();
   if (!word) return -1;
   const float scale_log2 = scale * 1.44269504088896341f;
+  if (g_stream_mode == 1 && n < kStreamMinRows) {  // few rows: a block per key tile, fed by the same boxes
+    constexpr int tile_smem = kStreamItemBytes + 8 + 1024;
+    if (key_tiles > 65535 || kv_heads > 65535) {
+      bw::set_error("attention: %d key tiles or %d key/value heads exceed the grid limit", key_tiles, kv_heads);
+      return -1;
+    }
+    bw::launch_pdl(attention_tile_tma_kernel, dim3(n, kv_heads, key_tiles), dim3(32), tile_smem, stream, map_k, map_v, qkv,
+                   q_stride, block_table, max_blocks, row_seq, pos, heads, kv_heads, page, window, scale_log2, scratch,
+                   key_tiles, word);
+    bw::launch_pdl(merge_tiles_kernel, dim3(dim3(n, heads)), dim3(kMergeThreads), 0, stream, scratch, key_tiles, pos, out,
+                   out_stride, heads, window);
+    return bw::launch_status();
+  }
   const long long warps_needed = (items + 0) / 1;
   const unsigned grid = static_cast<unsigned>(
       warps_needed < static_cast<long long>(sms) * kStreamWarps ? (warps_needed + kStreamWarps - 1) / kStreamWarps : sms);
