@@ -12,9 +12,10 @@
 // sum and output in float32; the weights are rounded to bfloat16 for the value product). The
 // tile results are merged in ascending tile order by one written-down formula (merge_weights
 // / merge_value below). A prefill portion walks its tiles inside one block; a decode step,
-// which has few query rows and long contexts, gives every tile to a warp of its own, four
-// tiles to a block (so that the cache streams from all SMs), and a second kernel merges the
-// stored tile results in the same order. A row's arithmetic depends only on its own query,
+// which has few query rows and long contexts, gives every tile to a block of one warp (so
+// that the cache streams from all SMs; the tile arrives by cp.async, at head size 64 as TMA
+// page boxes, and for steps of many rows through the rings of persistent blocks), and a
+// second kernel merges the stored tile results in the same order. A row's arithmetic depends only on its own query,
 // its position and the cached keys: tiles that lie wholly outside a row's range merge as an
 // exact no-op, so the result does not depend on which other rows share the block, on how the
 // prompt was cut, on the batch, or on which pages hold the keys.
