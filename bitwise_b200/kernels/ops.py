@@ -294,10 +294,11 @@ class KernelOps:
         return bool(self.lib.bw_bf16_linear_rows_enable(_c_int(int(on))))
 
     def stream_attention(self, head_dim: int, mode: int) -> int:
-        """When decode steps with head size 64 read the cache through the streaming kernel
-        (persistent blocks, TMA rings) instead of the kernel that gives every key tile a thread
-        block of its own: 0 never, 1 for steps of 32 rows or more (the default), 2 whenever
-        the shape allows.  Same bits either way.  Returns the previous setting."""
+        """How decode steps with head size 64 fetch the cache where TMA boxes fit (pages of 8 keys
+        or more that divide 64): 0 never (a thread block per key tile that copies with cp.async),
+        1 (the default) the streaming kernel (persistent blocks, TMA rings) for steps of 32 rows
+        or more and a block per key tile fed by TMA boxes for fewer, 2 the streaming kernel
+        whenever the shape allows.  Same bits every way.  Returns the previous setting."""
         if self.kind != "bf16":
             return 0
         return int(self._attention_lib(head_dim).bw_bf16_attention_stream_mode(_c_int(int(mode))))

@@ -678,9 +678,11 @@ def test_bf16_attention_decode_rows_split_over_chunks_give_the_same_bits():
 
 def test_bf16_attention_streaming_decode_kernel_gives_the_same_bits():
     """Head size 64: decode steps read the cache through a persistent kernel whose warps keep
-    rings of key tiles filled by TMA (a page of a head per copy). Same bits as the kernel that
-    gives every key tile a block of its own: groups of 1 .. 16 heads, pages of 8 .. 64 keys, a
-    window, sequences of very different lengths in one step (one shorter than a tile)."""
+    rings of key tiles filled by TMA (a page of a head per copy), or, with few rows, through a
+    block per key tile that gets its tile as TMA boxes. Same bits as the kernel that gives every
+    key tile a block of its own and copies with cp.async: groups of 1 .. 16 heads, pages of
+    8 .. 64 keys, a window, sequences of very different lengths in one step (one shorter than a
+    tile)."""
     rng = np.random.default_rng(17)
     ops = _ops("bfloat16")
     hd = 64
@@ -692,13 +694,14 @@ def test_bf16_attention_streaming_decode_kernel_gives_the_same_bits():
         q = bf(rnd(rng, len(lens), heads, hd))
         rows = [(n - 1, 1) for n in lens]
         outs = {}
-        for mode in (2, 0):
+        for mode in (2, 1, 0):  # persistent blocks; a block per key tile fed by TMA boxes (5 rows); cp.async blocks
             before = ops.stream_attention(hd, mode)
             try:
                 outs[mode], _, _ = _run_bf16_attention(q, rows, k, v, table, heads, kv_heads, hd, window)
             finally:
                 ops.stream_attention(hd, before)
-        assert_same_bits(outs[2], outs[0], f"heads {heads}/{kv_heads} page {page} window {window}")
+        assert_same_bits(outs[2], outs[0], f"streaming: heads {heads}/{kv_heads} page {page} window {window}")
+        assert_same_bits(outs[1], outs[0], f"a block per tile with TMA boxes: heads {heads}/{kv_heads} page {page} window {window}")
     assert not ops.device_failure()
 
 
